@@ -1,0 +1,149 @@
+/*
+ * magnetron_b200.h -- C ABI of the B200 (sm_100a) device implementation of magnetron's MATMUL and
+ * fp32<->bf16/fp16 CAST operators.
+ *
+ * Plain C: pointers, sizes and POD structs only. Every function returns MAGB200_OK (0) or a negative
+ * error code; the text of the last error of the calling thread is available from
+ * magb200_last_error(). Nothing here falls back to the CPU: if no sm_100 device is present the calls
+ * fail with MAGB200_ERR_NO_DEVICE.
+ *
+ * The entry points are what a magnetron backend module binds for this path. A magnetron backend
+ * receives `mag_command_t {op, in[], out[]}` (magnetron/core/mag_backend.h:80-87) whose tensors are
+ * described by (storage base, storage_offset in elements, dtype, rank, shape[16], strides[16])
+ * (magnetron/core/mag_tensor.h:52-68, magnetron/core/mag_coords.h:21-25). `magb200_view_t` carries
+ * exactly those fields.
+ */
+#ifndef MAGNETRON_B200_H
+#define MAGNETRON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
+#endif
+
+#define MAGB200_MAX_DIMS 16 /* MAG_MAX_DIMS, include/magnetron/magnetron.h */
+
+/* Same numeric values as mag_dtype_t (include/magnetron/magnetron.h:171-174). */
+typedef enum magb200_dtype_t {
+    MAGB200_F32  = 0,
+    MAGB200_F16  = 1,
+    MAGB200_BF16 = 2
+} magb200_dtype_t;
+
+typedef enum magb200_status_t {
+    MAGB200_OK                = 0,
+    MAGB200_ERR_NO_DEVICE     = -1,  /* no CUDA device / not sm_100 */
+    MAGB200_ERR_INVALID_ARG   = -2,  /* null pointer, bad rank, dtype outside {f32,f16,bf16}, misaligned base */
+    MAGB200_ERR_SHAPE         = -3,  /* shapes do not form a matmul / cast pair (MAG_STATUS_ERR_OPERATOR_IMPOSSIBLE) */
+    MAGB200_ERR_CUDA          = -4,  /* a CUDA runtime / driver call failed; text in magb200_last_error() */
+    MAGB200_ERR_OOM           = -5,  /* device allocation failed (MAG_STATUS_ERR_MEMORY_ALLOCATION_FAILED) */
+    MAGB200_ERR_TIMEOUT       = -6,  /* a bounded device-side wait ran out; the context stays usable */
+    MAGB200_ERR_TOO_LARGE     = -7   /* a fixed-capacity entry point was given a problem beyond its limit */
+} magb200_status_t;
+
+/* One tensor operand as a backend sees it: mag_tensor_t without the runtime bookkeeping. */
+typedef struct magb200_view_t {
+    void   *base;                          /* device address of the storage buffer (storage->base)     */
+    int64_t offset;                        /* storage_offset, in ELEMENTS                               */
+    int32_t dtype;                         /* magb200_dtype_t                                           */
+    int32_t rank;                          /* 0..16 (0: a scalar, one element)                          */
+    int64_t shape[MAGB200_MAX_DIMS];
+    int64_t strides[MAGB200_MAX_DIMS];     /* in elements; 0 is legal on size-1 (broadcast) dims        */
+} magb200_view_t;
+
+/* Which device kernel a matmul was routed to (for tests, profiles and the bench's launch count). */
+typedef enum magb200_kernel_t {
+    MAGB200_KERNEL_NONE     = 0,
+    MAGB200_KERNEL_TCGEN05  = 1,  /* TMA-fed tcgen05.mma tiles, fp32 accumulators in TMEM               */
+    MAGB200_KERNEL_SKINNY   = 2,  /* M <= 8 weight-streaming kernel (HBM bound)                          */
+    MAGB200_KERNEL_SIMT     = 3,  /* exact-fp32 / arbitrary-stride tiled FFMA kernel                     */
+    MAGB200_KERNEL_SKINNY_SPLITK = 4 /* M <= 8, K split across CTAs with an fp32 scratch reduction       */
+} magb200_kernel_t;
+
+/* ---- library / device ------------------------------------------------------------------------ */
+const char *magb200_last_error(void);
+int  magb200_device_count(void);                          /* visible sm_100 devices (0 if none)        */
+int  magb200_device_name(int device, char *buf, size_t cap);
+int  magb200_device_init(int device);                     /* creates the per-device stream + workspace; idempotent */
+int  magb200_device_shutdown(int device);
+int  magb200_synchronize(int device);
+/* Use an external CUDA stream (a cudaStream_t, e.g. the caller's current stream) for all launches
+ * on `device`; NULL restores the library's own stream. */
+int  magb200_set_stream(int device, void *cuda_stream);
+void *magb200_get_stream(int device);
+
+/* ---- storage: counterpart of mag_device_t::alloc_storage (magnetron/core/mag_backend.h:96) and of
+ * the transfers the reference performs with memcpy on CPU storage (mag_copy_raw_,
+ * magnetron/core/mag_op_stubs.c:1360-1375; mag_tensor_copy_data, magnetron/core/mag_tensor.c:232-250). */
+int  magb200_malloc(int device, void **out, size_t bytes);          /* 256-byte aligned device memory */
+int  magb200_free(int device, void *ptr);
+int  magb200_upload(int device, void *dst_device, const void *src_host, size_t bytes);   /* stream-ordered, then synchronised */
+int  magb200_download(int device, void *dst_host, const void *src_device, size_t bytes); /* stream-ordered, then synchronised */
+int  magb200_upload_async(int device, void *dst_device, const void *src_pinned_host, size_t bytes);
+int  magb200_download_async(int device, void *dst_pinned_host, const void *src_device, size_t bytes);
+int  magb200_host_alloc_pinned(void **out, size_t bytes);
+int  magb200_host_free_pinned(void *ptr);
+
+/* ---- operators --------------------------------------------------------------------------------
+ * All three are stream-ordered on the device's stream and return without synchronising. */
+
+/* MAG_OP_CAST: replaces mag_cast_generic + mag_vcast_* (magnetron/cpu/mag_cpu_impl_cast.inl:482-523)
+ * for dtype pairs within {f32, f16, bf16}. Bit-exact with the reference conversions
+ * (magnetron/core/mag_bfloat16.h:47-65; F16C semantics of magnetron/cpu/mag_cpu_impl_cast.inl:12-46).
+ * `dst` must be contiguous with the same shape as `src`; `src` may be any strided view. */
+int  magb200_cast(int device, const magb200_view_t *src, const magb200_view_t *dst);
+
+/* MAG_OP_CLONE for the same dtypes (strided gather into a contiguous result); what
+ * mag_contiguous / mag_reshape of a strided view dispatch (magnetron/core/mag_op_stubs.c:424-470). */
+int  magb200_clone(int device, const magb200_view_t *src, const magb200_view_t *dst);
+
+/* MAG_OP_FILL with a floating point value (magnetron/cpu/mag_cpu_impl_ops_fill.inl), contiguous dst. */
+int  magb200_fill(int device, const magb200_view_t *dst, double value);
+
+/* MAG_OP_MATMUL: replaces mag_matmul_float32 / _bfloat16 / _float16
+ * (magnetron/cpu/mag_cpu_impl_ops_matmul.inl:2821-2919, :2921-3019, :3062-3116) including the
+ * batch/broadcast index mapping (:2971-2989, :2798-2819) and the rank-1 operand rules of the
+ * operator stub (magnetron/core/mag_op_stubs.c:1249-1310). x and y share one dtype; `r` is the
+ * pre-allocated contiguous result of the shape the stub infers. fp32 accumulation over the whole K,
+ * one rounding to the result dtype. */
+int  magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r);
+
+/* Shape inference of the operator stub (magnetron/core/mag_op_stubs.c:1249-1310) for callers that
+ * allocate `r` themselves. Returns MAGB200_ERR_SHAPE with the reference's message on a mismatch. */
+int  magb200_matmul_result_shape(const magb200_view_t *x, const magb200_view_t *y, int32_t *out_rank, int64_t *out_shape);
+
+/* Kernel that the most recent magb200_matmul on this thread was routed to, and the number of
+ * device kernels launched by this library since magb200_launch_count_reset(). */
+int      magb200_last_kernel(void);
+uint64_t magb200_launch_count(void);
+void     magb200_launch_count_reset(void);
+/* Restrict routing (testing / profiling): 0 = automatic, otherwise a magb200_kernel_t that must be
+ * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
+int  magb200_force_kernel(int kernel);
+
+/* ---- host-buffer convenience: one call = upload operands, matmul, download result ------------
+ * This is the call a CPU-side user of the reference makes (operands and result in host memory,
+ * magnetron/core/mag_op_stubs.c:1249); the views' `base` fields are HOST addresses here. Synchronous. */
+int  magb200_matmul_host(int device, const magb200_view_t *x, size_t x_storage_bytes,
+                         const magb200_view_t *y, size_t y_storage_bytes,
+                         const magb200_view_t *r);
+int  magb200_cast_host(int device, const magb200_view_t *src, size_t src_storage_bytes, const magb200_view_t *dst);
+
+/* ---- timing on the library's stream (CUDA events recorded on the launch stream) --------------- */
+int  magb200_event_create(void **out_event);
+int  magb200_event_destroy(void *event);
+int  magb200_event_record(int device, void *event);
+int  magb200_event_elapsed_ms(void *start, void *stop, float *out_ms); /* synchronises on `stop` */
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAGNETRON_B200_H */

@@ -1,0 +1,570 @@
+// C ABI of the B200 matmul / cast path: device state, operand canonicalisation, kernel routing.
+#include "common.cuh"
+
+#include <mutex>
+#include <stdarg.h>
+#include <stdlib.h>
+#include <atomic>
+
+namespace magb200 {
+
+size_t skinny_scratch_bytes(const GemmProblem &p);  // gemv.cu
+
+// ---- errors / counters --------------------------------------------------------------------------
+static thread_local char g_err[768] = "";
+static thread_local int g_last_kernel = MAGB200_KERNEL_NONE;
+static std::atomic<uint64_t> g_launches{0};
+static std::atomic<int> g_force{0};
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
+    set_error("%s failed: %s (%s:%d)", what, cudaGetErrorString(e), file, line);
+    return e == cudaErrorMemoryAllocation ? MAGB200_ERR_OOM : MAGB200_ERR_CUDA;
+}
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// ---- per-device state ---------------------------------------------------------------------------
+constexpr int kMaxDevices = 16;
+struct DeviceState {
+    bool ready = false;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;   // launch stream (own_stream unless the caller installed one)
+    float *scratch = nullptr;        // split-K partial sums
+    size_t scratch_bytes = 0;
+    int *status = nullptr;           // device word raised by a kernel whose bounded wait ran out
+    void *staging[3] = {nullptr, nullptr, nullptr};  // device buffers of the host-buffer entry points
+    size_t staging_bytes[3] = {0, 0, 0};
+    char name[256] = "";
+};
+static DeviceState g_dev[kMaxDevices];
+static std::mutex g_mu;
+
+static int check_device(int device) {
+    if (device < 0 || device >= kMaxDevices) { set_error("device %d out of range", device); return MAGB200_ERR_INVALID_ARG; }
+    return MAGB200_OK;
+}
+
+static int ensure_device(int device, DeviceState **out) {
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceState &d = g_dev[device];
+    if (!d.ready) {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!d.ready) {
+            int n = 0;
+            cudaError_t e = cudaGetDeviceCount(&n);
+            if (e != cudaSuccess || device >= n) {
+                set_error("no CUDA device %d (%s): this library has no CPU fallback", device,
+                          e != cudaSuccess ? cudaGetErrorString(e) : "ordinal beyond the visible devices");
+                return MAGB200_ERR_NO_DEVICE;
+            }
+            cudaDeviceProp prop;
+            MAGB200_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+            if (prop.major != 10) {
+                set_error("device %d (%s) is sm_%d%d; the kernels are built for sm_100a only", device, prop.name, prop.major, prop.minor);
+                return MAGB200_ERR_NO_DEVICE;
+            }
+            snprintf(d.name, sizeof(d.name), "%s", prop.name);
+            MAGB200_CUDA_TRY(cudaSetDevice(device));
+            MAGB200_CUDA_TRY(cudaStreamCreateWithFlags(&d.own_stream, cudaStreamNonBlocking));
+            d.stream = d.own_stream;
+            MAGB200_CUDA_TRY(cudaMalloc(&d.status, 256));
+            MAGB200_CUDA_TRY(cudaMemset(d.status, 0, 256));
+            d.scratch_bytes = 32ull << 20;
+            MAGB200_CUDA_TRY(cudaMalloc(&d.scratch, d.scratch_bytes));
+            d.ready = true;
+        }
+    }
+    MAGB200_CUDA_TRY(cudaSetDevice(device));
+    *out = &d;
+    return MAGB200_OK;
+}
+
+static int ensure_scratch(DeviceState &d, size_t bytes) {
+    if (bytes <= d.scratch_bytes) return MAGB200_OK;
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    MAGB200_CUDA_TRY(cudaFree(d.scratch));
+    d.scratch = nullptr; d.scratch_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    MAGB200_CUDA_TRY(cudaMalloc(&d.scratch, want));
+    d.scratch_bytes = want;
+    return MAGB200_OK;
+}
+
+static int check_status_word(DeviceState &d) {
+    int h = 0;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(&h, d.status, sizeof(int), cudaMemcpyDeviceToHost, d.stream));
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    if (h != 0) {
+        MAGB200_CUDA_TRY(cudaMemsetAsync(d.status, 0, sizeof(int), d.stream));
+        set_error("a device-side wait ran out (status %d): the launch was abandoned, results are invalid", h);
+        return MAGB200_ERR_TIMEOUT;
+    }
+    return MAGB200_OK;
+}
+
+// ---- views --------------------------------------------------------------------------------------
+int64_t view_numel(const magb200_view_t *v) {
+    int64_t n = 1;
+    for (int i = 0; i < v->rank; ++i) n *= v->shape[i];
+    return n;
+}
+bool view_is_contiguous(const magb200_view_t *v) {
+    int64_t expect = 1;
+    for (int i = v->rank - 1; i >= 0; --i) {
+        if (v->shape[i] != 1 && v->strides[i] != expect) return false;
+        expect *= v->shape[i];
+    }
+    return true;
+}
+CollapsedDims collapse_dims(int rank, const int64_t *shape, const int64_t *strides) {
+    CollapsedDims c;
+    c.rank = 0;
+    for (int i = 0; i < rank; ++i) {
+        if (shape[i] == 1) continue;
+        if (c.rank > 0 && c.strides[c.rank - 1] == strides[i] * shape[i]) {
+            c.shape[c.rank - 1] *= shape[i];
+            c.strides[c.rank - 1] = strides[i];
+        } else {
+            c.shape[c.rank] = shape[i];
+            c.strides[c.rank] = strides[i];
+            ++c.rank;
+        }
+    }
+    return c;
+}
+static int check_view(const magb200_view_t *v, const char *what) {
+    if (!v || !v->base) { set_error("%s: null view or base pointer", what); return MAGB200_ERR_INVALID_ARG; }
+    if (!dtype_ok(v->dtype)) { set_error("%s: dtype %d is outside {float32, float16, bfloat16}", what, v->dtype); return MAGB200_ERR_INVALID_ARG; }
+    if (v->rank < 0 || v->rank > kMaxDims) { set_error("%s: rank %d out of range", what, v->rank); return MAGB200_ERR_INVALID_ARG; }
+    for (int i = 0; i < v->rank; ++i)
+        if (v->shape[i] < 1 || v->strides[i] < 0) { set_error("%s: dim %d has extent %lld stride %lld", what, i, (long long)v->shape[i], (long long)v->strides[i]); return MAGB200_ERR_INVALID_ARG; }
+    if (v->offset < 0) { set_error("%s: negative storage offset", what); return MAGB200_ERR_INVALID_ARG; }
+    return MAGB200_OK;
+}
+static inline char *view_data(const magb200_view_t *v) { return (char *)v->base + v->offset * (int64_t)dtype_size(v->dtype); }
+
+// ---- matmul front-end ---------------------------------------------------------------------------
+static int result_shape(const magb200_view_t *x, const magb200_view_t *y, int32_t *out_rank, int64_t *out_shape) {
+    const int xr = x->rank, yr = y->rank;
+    const int64_t kx = x->shape[xr - 1];
+    const int64_t ky = (yr == 1 || (yr == 2 && xr == 1)) ? y->shape[0] : y->shape[yr - 2];
+    if (kx != ky) {
+        set_error("Cannot perform matmul: last dimension of first tensor (%lld) does not match second tensor (%lld)", (long long)kx, (long long)ky);
+        return MAGB200_ERR_SHAPE;
+    }
+    const int xbd = xr > 2 ? xr - 2 : 0, ybd = yr > 2 ? yr - 2 : 0, rbd = xbd > ybd ? xbd : ybd;
+    for (int i = 0; i < rbd; ++i) {
+        int64_t xd = i < rbd - xbd ? 1 : x->shape[i - (rbd - xbd)];
+        int64_t yd = i < rbd - ybd ? 1 : y->shape[i - (rbd - ybd)];
+        if (xd != yd && xd != 1 && yd != 1) {
+            set_error("Cannot perform matmul: batch dimensions at index %d do not match (%lld != %lld)", i, (long long)xd, (long long)yd);
+            return MAGB200_ERR_SHAPE;
+        }
+    }
+    if (xr == 1 && yr == 1) { *out_rank = 0; out_shape[0] = 1; return MAGB200_OK; }  /* (K)x(K) -> scalar, mag_empty_scalar */
+    if (xr == 1 && yr == 2) { *out_rank = 1; out_shape[0] = y->shape[1]; return MAGB200_OK; }
+    if (xr == 2 && yr == 1) { *out_rank = 1; out_shape[0] = x->shape[0]; return MAGB200_OK; }
+    for (int i = 0; i < rbd; ++i) {
+        int64_t xd = i < rbd - xbd ? 1 : x->shape[i - (rbd - xbd)];
+        int64_t yd = i < rbd - ybd ? 1 : y->shape[i - (rbd - ybd)];
+        out_shape[i] = xd > yd ? xd : yd;
+    }
+    out_shape[rbd] = xr == 1 ? 1 : x->shape[xr - 2];
+    out_shape[rbd + 1] = yr == 1 ? 1 : y->shape[yr - 1];
+    *out_rank = rbd + 2;
+    return MAGB200_OK;
+}
+
+struct FullProblem {
+    GemmProblem g;                  // innermost (up to three) batch dims
+    int n_outer;                    // further outer batch dims, looped on the host
+    int64_t oshape[kMaxDims], osA[kMaxDims], osB[kMaxDims];
+};
+
+static int build_problem(const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r, FullProblem &fp) {
+    int rc;
+    if ((rc = check_view(x, "matmul x")) || (rc = check_view(y, "matmul y")) || (rc = check_view(r, "matmul result"))) return rc;
+    if (x->rank < 1 || y->rank < 1) { set_error("matmul: both tensors must have rank at least 1"); return MAGB200_ERR_INVALID_ARG; }
+    if (x->dtype != y->dtype || x->dtype != r->dtype) {
+        set_error("matmul: operands and result must share one dtype (got %d, %d -> %d)", x->dtype, y->dtype, r->dtype);
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    int32_t rr = 0;
+    int64_t rs[kMaxDims + 2];
+    if ((rc = result_shape(x, y, &rr, rs))) return rc;
+    // the result must be the contiguous tensor the operator stub allocates; a leading size-1 difference
+    // in rank is not accepted: shapes must match exactly
+    bool same = (rr == r->rank);
+    for (int i = 0; same && i < rr; ++i) same = (rs[i] == r->shape[i]);
+    if (!same) { set_error("matmul: result view does not have the inferred shape"); return MAGB200_ERR_SHAPE; }
+    if (!view_is_contiguous(r)) { set_error("matmul: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
+
+    GemmProblem &g = fp.g;
+    memset(&fp, 0, sizeof(fp));
+    const int xr = x->rank, yr = y->rank;
+    g.dtype = x->dtype;
+    g.M = xr == 1 ? 1 : x->shape[xr - 2];
+    g.K = x->shape[xr - 1];
+    g.N = yr == 1 ? 1 : y->shape[yr - 1];
+    g.A = view_data(x); g.B = view_data(y); g.C = view_data(r);
+    g.sAm = xr == 1 ? 0 : x->strides[xr - 2];
+    g.sAk = x->strides[xr - 1];
+    if (yr == 1) { g.sBk = y->strides[0]; g.sBn = 0; }
+    else { g.sBk = y->strides[yr - 2]; g.sBn = y->strides[yr - 1]; }
+
+    // batch dims of the result with per-operand strides (0 where the operand is broadcast)
+    const int xbd = xr > 2 ? xr - 2 : 0, ybd = yr > 2 ? yr - 2 : 0, rbd = xbd > ybd ? xbd : ybd;
+    int64_t ext[kMaxDims], sa[kMaxDims], sb[kMaxDims];
+    int nb = 0;
+    for (int i = 0; i < rbd; ++i) {
+        const int xi = i - (rbd - xbd), yi = i - (rbd - ybd);
+        const int64_t xd = xi < 0 ? 1 : x->shape[xi], yd = yi < 0 ? 1 : y->shape[yi];
+        const int64_t e = xd > yd ? xd : yd;
+        if (e == 1) continue;
+        ext[nb] = e;
+        sa[nb] = xd == 1 ? 0 : x->strides[xi];
+        sb[nb] = yd == 1 ? 0 : y->strides[yi];
+        ++nb;
+    }
+    // fold the innermost batch dim into M while y is broadcast there and x's rows continue seamlessly:
+    // nn.Linear on [B,T,K] and GQA query groups become one taller GEMM instead of many small ones
+    while (nb > 0 && sb[nb - 1] == 0 && (g.M == 1 || sa[nb - 1] == g.M * g.sAm)) {
+        if (g.M == 1) g.sAm = sa[nb - 1];
+        g.M *= ext[nb - 1];
+        --nb;
+    }
+    // merge adjacent batch dims that both operands walk with one stride
+    int m = 0;
+    for (int i = 0; i < nb; ++i) {
+        if (m > 0 && sa[m - 1] == sa[i] * ext[i] && sb[m - 1] == sb[i] * ext[i]) {
+            ext[m - 1] *= ext[i]; sa[m - 1] = sa[i]; sb[m - 1] = sb[i];
+        } else {
+            ext[m] = ext[i]; sa[m] = sa[i]; sb[m] = sb[i]; ++m;
+        }
+    }
+    nb = m;
+    const int inner = nb < kMaxBatchDims ? nb : kMaxBatchDims;
+    fp.n_outer = nb - inner;
+    for (int i = 0; i < fp.n_outer; ++i) { fp.oshape[i] = ext[i]; fp.osA[i] = sa[i]; fp.osB[i] = sb[i]; }
+    g.nbatch = inner;
+    g.batch_total = 1;
+    for (int i = 0; i < kMaxBatchDims; ++i) { g.bshape[i] = 1; g.bsA[i] = 0; g.bsB[i] = 0; }
+    for (int i = 0; i < inner; ++i) {
+        g.bshape[i] = ext[fp.n_outer + i]; g.bsA[i] = sa[fp.n_outer + i]; g.bsB[i] = sb[fp.n_outer + i];
+        g.batch_total *= g.bshape[i];
+    }
+    return MAGB200_OK;
+}
+
+static int route(const GemmProblem &g, int forced, int *kernel) {
+    const bool sk = g.M <= 8 && skinny_supported(g);
+    const bool tc = tcgen05_supported(g);
+    int k = sk ? MAGB200_KERNEL_SKINNY : (tc ? MAGB200_KERNEL_TCGEN05 : MAGB200_KERNEL_SIMT);
+    if (forced) {
+        if (forced == MAGB200_KERNEL_SKINNY_SPLITK) forced = MAGB200_KERNEL_SKINNY;
+        if ((forced == MAGB200_KERNEL_SKINNY && !sk) || (forced == MAGB200_KERNEL_TCGEN05 && !tc) ||
+            (forced != MAGB200_KERNEL_SKINNY && forced != MAGB200_KERNEL_TCGEN05 && forced != MAGB200_KERNEL_SIMT)) {
+            set_error("matmul: forced kernel %d cannot run this problem (M=%lld N=%lld K=%lld)", forced, (long long)g.M, (long long)g.N, (long long)g.K);
+            return MAGB200_ERR_INVALID_ARG;
+        }
+        k = forced;
+    }
+    *kernel = k;
+    return MAGB200_OK;
+}
+
+static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel) {
+    switch (kernel) {
+        case MAGB200_KERNEL_SKINNY: {
+            int rc = ensure_scratch(d, skinny_scratch_bytes(g));
+            if (rc) return rc;
+            int split = 0;
+            rc = launch_skinny(g, d.stream, d.scratch, d.scratch_bytes, &split);
+            g_last_kernel = split ? MAGB200_KERNEL_SKINNY_SPLITK : MAGB200_KERNEL_SKINNY;
+            return rc;
+        }
+        case MAGB200_KERNEL_TCGEN05:
+            g_last_kernel = MAGB200_KERNEL_TCGEN05;
+            return launch_gemm_tcgen05(g, d.stream, device, d.status);
+        default:
+            g_last_kernel = MAGB200_KERNEL_SIMT;
+            return launch_gemm_simt(g, d.stream);
+    }
+}
+
+static int matmul_device(DeviceState &d, int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r) {
+    FullProblem fp;
+    int rc = build_problem(x, y, r, fp);
+    if (rc) return rc;
+    int kernel = 0;
+    if ((rc = route(fp.g, g_force.load(), &kernel))) return rc;
+    if (fp.n_outer == 0) return run_one(d, device, fp.g, kernel);
+    // more than three independent batch dims survive merging: walk the outer ones on the host
+    int64_t outer_total = 1;
+    for (int i = 0; i < fp.n_outer; ++i) outer_total *= fp.oshape[i];
+    const int64_t es = (int64_t)dtype_size(fp.g.dtype);
+    const int64_t slice = fp.g.batch_total * fp.g.M * fp.g.N;
+    for (int64_t o = 0; o < outer_total; ++o) {
+        int64_t rem = o, offA = 0, offB = 0;
+        for (int i = fp.n_outer - 1; i >= 0; --i) {
+            int64_t q = rem / fp.oshape[i], idx = rem - q * fp.oshape[i];
+            offA += idx * fp.osA[i]; offB += idx * fp.osB[i];
+            rem = q;
+        }
+        GemmProblem g = fp.g;
+        g.A = (const char *)fp.g.A + offA * es;
+        g.B = (const char *)fp.g.B + offB * es;
+        g.C = (char *)fp.g.C + o * slice * es;
+        int k2 = kernel;
+        if ((rc = route(g, g_force.load(), &k2)) || (rc = run_one(d, device, g, k2))) return rc;
+    }
+    return MAGB200_OK;
+}
+
+static int cast_device(DeviceState &d, const magb200_view_t *src, const magb200_view_t *dst, bool same_dtype_required) {
+    int rc;
+    if ((rc = check_view(src, "cast source")) || (rc = check_view(dst, "cast result"))) return rc;
+    if (same_dtype_required && src->dtype != dst->dtype) { set_error("clone: dtypes differ"); return MAGB200_ERR_INVALID_ARG; }
+    const int64_t n = view_numel(src);
+    if (n != view_numel(dst)) { set_error("cast: element counts differ (%lld vs %lld)", (long long)n, (long long)view_numel(dst)); return MAGB200_ERR_SHAPE; }
+    if (!view_is_contiguous(dst)) { set_error("cast: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
+    CollapsedDims cd = collapse_dims(src->rank, src->shape, src->strides);
+    return launch_cast(src->dtype, dst->dtype, view_data(src), view_data(dst), n, cd, view_is_contiguous(src), d.stream);
+}
+
+static int ensure_staging(DeviceState &d, int slot, size_t bytes) {
+    if (bytes <= d.staging_bytes[slot]) return MAGB200_OK;
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    if (d.staging[slot]) MAGB200_CUDA_TRY(cudaFree(d.staging[slot]));
+    d.staging[slot] = nullptr; d.staging_bytes[slot] = 0;
+    MAGB200_CUDA_TRY(cudaMalloc(&d.staging[slot], bytes));
+    d.staging_bytes[slot] = bytes;
+    return MAGB200_OK;
+}
+
+}  // namespace magb200
+
+using namespace magb200;
+
+extern "C" {
+
+const char *magb200_last_error(void) { return g_err; }
+
+int magb200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    int ok = 0;
+    for (int i = 0; i < n && i < kMaxDevices; ++i) {
+        cudaDeviceProp p;
+        if (cudaGetDeviceProperties(&p, i) == cudaSuccess && p.major == 10) ++ok; else break;
+    }
+    return ok;
+}
+
+int magb200_device_name(int device, char *buf, size_t cap) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (buf && cap) snprintf(buf, cap, "%s", d->name);
+    return MAGB200_OK;
+}
+
+int magb200_device_init(int device) { DeviceState *d; return ensure_device(device, &d); }
+
+int magb200_device_shutdown(int device) {
+    int rc = check_device(device);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState &d = g_dev[device];
+    if (!d.ready) return MAGB200_OK;
+    MAGB200_CUDA_TRY(cudaSetDevice(device));
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    for (int i = 0; i < 3; ++i) if (d.staging[i]) { cudaFree(d.staging[i]); d.staging[i] = nullptr; d.staging_bytes[i] = 0; }
+    cudaFree(d.scratch); cudaFree(d.status);
+    cudaStreamDestroy(d.own_stream);
+    d = DeviceState();
+    return MAGB200_OK;
+}
+
+int magb200_synchronize(int device) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return check_status_word(*d);
+}
+
+int magb200_set_stream(int device, void *cuda_stream) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    d->stream = cuda_stream ? (cudaStream_t)cuda_stream : d->own_stream;
+    return MAGB200_OK;
+}
+void *magb200_get_stream(int device) {
+    DeviceState *d;
+    if (ensure_device(device, &d)) return nullptr;
+    return (void *)d->stream;
+}
+
+int magb200_malloc(int device, void **out, size_t bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!out) { set_error("malloc: null out pointer"); return MAGB200_ERR_INVALID_ARG; }
+    *out = nullptr;
+    MAGB200_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 1));  // cudaMalloc returns >= 256-byte aligned memory
+    return MAGB200_OK;
+}
+int magb200_free(int device, void *ptr) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (ptr) { MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream)); MAGB200_CUDA_TRY(cudaFree(ptr)); }
+    return MAGB200_OK;
+}
+int magb200_upload_async(int device, void *dst, const void *src, size_t bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d->stream));
+    return MAGB200_OK;
+}
+int magb200_download_async(int device, void *dst, const void *src, size_t bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d->stream));
+    return MAGB200_OK;
+}
+int magb200_upload(int device, void *dst, const void *src, size_t bytes) {
+    int rc = magb200_upload_async(device, dst, src, bytes);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(g_dev[device].stream));
+    return MAGB200_OK;
+}
+int magb200_download(int device, void *dst, const void *src, size_t bytes) {
+    int rc = magb200_download_async(device, dst, src, bytes);
+    if (rc) return rc;
+    return magb200_synchronize(device);
+}
+int magb200_host_alloc_pinned(void **out, size_t bytes) {
+    if (!out) { set_error("host_alloc_pinned: null out pointer"); return MAGB200_ERR_INVALID_ARG; }
+    MAGB200_CUDA_TRY(cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault));
+    return MAGB200_OK;
+}
+int magb200_host_free_pinned(void *ptr) {
+    if (ptr) MAGB200_CUDA_TRY(cudaFreeHost(ptr));
+    return MAGB200_OK;
+}
+
+int magb200_cast(int device, const magb200_view_t *src, const magb200_view_t *dst) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    return cast_device(*d, src, dst, false);
+}
+int magb200_clone(int device, const magb200_view_t *src, const magb200_view_t *dst) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    return cast_device(*d, src, dst, true);
+}
+int magb200_fill(int device, const magb200_view_t *dst, double value) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if ((rc = check_view(dst, "fill result"))) return rc;
+    if (!view_is_contiguous(dst)) { set_error("fill: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
+    return launch_fill(dst->dtype, view_data(dst), view_numel(dst), value, d->stream);
+}
+
+int magb200_matmul_result_shape(const magb200_view_t *x, const magb200_view_t *y, int32_t *out_rank, int64_t *out_shape) {
+    int rc;
+    if ((rc = check_view(x, "matmul x")) || (rc = check_view(y, "matmul y"))) return rc;
+    if (x->rank < 1 || y->rank < 1) { set_error("matmul: both tensors must have rank at least 1"); return MAGB200_ERR_INVALID_ARG; }
+    if (!out_rank || !out_shape) { set_error("matmul_result_shape: null output"); return MAGB200_ERR_INVALID_ARG; }
+    return result_shape(x, y, out_rank, out_shape);
+}
+
+int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    return matmul_device(*d, device, x, y, r);
+}
+
+int magb200_last_kernel(void) { return g_last_kernel; }
+uint64_t magb200_launch_count(void) { return g_launches.load(); }
+void magb200_launch_count_reset(void) { g_launches.store(0); }
+int magb200_force_kernel(int kernel) {
+    if (kernel < 0 || kernel > MAGB200_KERNEL_SKINNY_SPLITK) { set_error("force_kernel: unknown kernel %d", kernel); return MAGB200_ERR_INVALID_ARG; }
+    g_force.store(kernel);
+    return MAGB200_OK;
+}
+
+int magb200_matmul_host(int device, const magb200_view_t *x, size_t x_bytes, const magb200_view_t *y, size_t y_bytes, const magb200_view_t *r) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if ((rc = check_view(x, "matmul x")) || (rc = check_view(y, "matmul y")) || (rc = check_view(r, "matmul result"))) return rc;
+    const size_t r_bytes = (size_t)view_numel(r) * dtype_size(r->dtype);
+    if ((rc = ensure_staging(*d, 0, x_bytes)) || (rc = ensure_staging(*d, 1, y_bytes)) || (rc = ensure_staging(*d, 2, r_bytes))) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[0], x->base, x_bytes, cudaMemcpyHostToDevice, d->stream));
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[1], y->base, y_bytes, cudaMemcpyHostToDevice, d->stream));
+    magb200_view_t dx = *x, dy = *y, dr = *r;
+    dx.base = d->staging[0]; dy.base = d->staging[1]; dr.base = d->staging[2]; dr.offset = 0;
+    if ((rc = matmul_device(*d, device, &dx, &dy, &dr))) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(view_data(r), d->staging[2], r_bytes, cudaMemcpyDeviceToHost, d->stream));
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return check_status_word(*d);
+}
+
+int magb200_cast_host(int device, const magb200_view_t *src, size_t src_bytes, const magb200_view_t *dst) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if ((rc = check_view(src, "cast source")) || (rc = check_view(dst, "cast result"))) return rc;
+    const size_t dst_bytes = (size_t)view_numel(dst) * dtype_size(dst->dtype);
+    if ((rc = ensure_staging(*d, 0, src_bytes)) || (rc = ensure_staging(*d, 2, dst_bytes))) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[0], src->base, src_bytes, cudaMemcpyHostToDevice, d->stream));
+    magb200_view_t ds = *src, dd = *dst;
+    ds.base = d->staging[0]; dd.base = d->staging[2]; dd.offset = 0;
+    if ((rc = cast_device(*d, &ds, &dd, false))) return rc;
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(view_data(dst), d->staging[2], dst_bytes, cudaMemcpyDeviceToHost, d->stream));
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return MAGB200_OK;
+}
+
+int magb200_event_create(void **out) {
+    if (!out) { set_error("event_create: null out pointer"); return MAGB200_ERR_INVALID_ARG; }
+    cudaEvent_t e;
+    MAGB200_CUDA_TRY(cudaEventCreate(&e));
+    *out = (void *)e;
+    return MAGB200_OK;
+}
+int magb200_event_destroy(void *event) {
+    if (event) MAGB200_CUDA_TRY(cudaEventDestroy((cudaEvent_t)event));
+    return MAGB200_OK;
+}
+int magb200_event_record(int device, void *event) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    MAGB200_CUDA_TRY(cudaEventRecord((cudaEvent_t)event, d->stream));
+    return MAGB200_OK;
+}
+int magb200_event_elapsed_ms(void *start, void *stop, float *out_ms) {
+    MAGB200_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)stop));
+    MAGB200_CUDA_TRY(cudaEventElapsedTime(out_ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return MAGB200_OK;
+}
+
+}  // extern "C"

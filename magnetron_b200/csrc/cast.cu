@@ -1,0 +1,169 @@
+// Streaming dtype conversion kernels for {f32, f16, bf16} (MAG_OP_CAST, MAG_OP_CLONE, MAG_OP_FILL).
+//
+// HBM-bound: a contiguous cast moves sizeof(src)+sizeof(dst) bytes per element and does a handful of
+// integer ops. Each thread converts 8 elements per step with 128-bit loads and stores that bypass L1
+// (ld.global.cs / st.global.cs: streaming, evict-first), the grid is a multiple of the SM count, and
+// the conversions are the integer formulas of common.cuh so every NaN pattern matches the reference.
+#include "common.cuh"
+
+namespace magb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVec = 8;  // elements per thread per step
+
+template <int S, int D> __device__ __forceinline__ uint32_t convert_bits(uint32_t v);
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F32, MAGB200_F32>(uint32_t v) { return v; }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F16, MAGB200_F16>(uint32_t v) { return v; }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_BF16, MAGB200_BF16>(uint32_t v) { return v; }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F32, MAGB200_BF16>(uint32_t v) { return f32_bits_to_bf16_bits(v); }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F32, MAGB200_F16>(uint32_t v) { return f32_bits_to_f16_bits(v); }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_BF16, MAGB200_F32>(uint32_t v) { return bf16_bits_to_f32_bits(v); }
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F16, MAGB200_F32>(uint32_t v) { return f16_bits_to_f32_bits(v); }
+// 16-bit <-> 16-bit pairs go through fp32 exactly like the reference's cast table.
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_F16, MAGB200_BF16>(uint32_t v) {
+    return f32_bits_to_bf16_bits(f16_bits_to_f32_bits(v));
+}
+template <> __device__ __forceinline__ uint32_t convert_bits<MAGB200_BF16, MAGB200_F16>(uint32_t v) {
+    return f32_bits_to_f16_bits(bf16_bits_to_f32_bits(v));
+}
+
+template <int DT> struct Bits { using type = uint16_t; };
+template <> struct Bits<MAGB200_F32> { using type = uint32_t; };
+
+// Loads 8 source elements as raw bit patterns into v[8].
+template <int S> __device__ __forceinline__ void load8(const void *src, int64_t i, uint32_t (&v)[kVec]) {
+    if constexpr (S == MAGB200_F32) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint32_t *>(src) + i);
+        uint4 a = __ldcs(p), b = __ldcs(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        uint4 a = __ldcs(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(src) + i));
+        v[0] = a.x & 0xFFFFu; v[1] = a.x >> 16; v[2] = a.y & 0xFFFFu; v[3] = a.y >> 16;
+        v[4] = a.z & 0xFFFFu; v[5] = a.z >> 16; v[6] = a.w & 0xFFFFu; v[7] = a.w >> 16;
+    }
+}
+template <int D> __device__ __forceinline__ void store8(void *dst, int64_t i, const uint32_t (&v)[kVec]) {
+    if constexpr (D == MAGB200_F32) {
+        uint4 *p = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(dst) + i);
+        __stcs(p, make_uint4(v[0], v[1], v[2], v[3]));
+        __stcs(p + 1, make_uint4(v[4], v[5], v[6], v[7]));
+    } else {
+        uint4 o = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+        __stcs(reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(dst) + i), o);
+    }
+}
+
+// Contiguous source and destination, both 16-byte aligned. n8 = number of full 8-element groups.
+template <int S, int D>
+__global__ void __launch_bounds__(kThreads) cast_contig_kernel(const void *__restrict__ src, void *__restrict__ dst, int64_t n) {
+    const int64_t n8 = n / kVec;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t g = (int64_t)blockIdx.x * kThreads + threadIdx.x; g < n8; g += stride) {
+        uint32_t v[kVec];
+        load8<S>(src, g * kVec, v);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) v[j] = convert_bits<S, D>(v[j]);
+        store8<D>(dst, g * kVec, v);
+    }
+    // ragged tail (< 8 elements): first threads of block 0
+    if (blockIdx.x == 0) {
+        int64_t i = n8 * kVec + threadIdx.x;
+        if (i < n) {
+            uint32_t v = reinterpret_cast<const typename Bits<S>::type *>(src)[i];
+            reinterpret_cast<typename Bits<D>::type *>(dst)[i] = (typename Bits<D>::type)convert_bits<S, D>(v);
+        }
+    }
+}
+
+// Arbitrary strided source (collapsed dims), contiguous destination. One element per thread-step;
+// consecutive threads take consecutive destination elements, so stores stay coalesced and loads are
+// coalesced whenever the innermost collapsed stride is 1.
+template <int S, int D>
+__global__ void __launch_bounds__(kThreads) cast_strided_kernel(const void *__restrict__ src, void *__restrict__ dst,
+                                                                int64_t n, CollapsedDims dims) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        int64_t rem = i, off = 0;
+#pragma unroll 1
+        for (int d = dims.rank - 1; d >= 0; --d) {
+            int64_t q = rem / dims.shape[d];
+            off += (rem - q * dims.shape[d]) * dims.strides[d];
+            rem = q;
+        }
+        uint32_t v = reinterpret_cast<const typename Bits<S>::type *>(src)[off];
+        reinterpret_cast<typename Bits<D>::type *>(dst)[i] = (typename Bits<D>::type)convert_bits<S, D>(v);
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads) fill_kernel(void *__restrict__ dst, int64_t n, uint32_t bits) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+        reinterpret_cast<typename Bits<DT>::type *>(dst)[i] = (typename Bits<DT>::type)bits;
+}
+
+int grid_for(int64_t work_items) {
+    int64_t blocks = (work_items + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)kNumSMsB200 * 16;  // 16 resident 256-thread blocks cover every SM several times
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+template <int S, int D>
+int launch_pair(const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t stream) {
+    const bool aligned = (((uintptr_t)src | (uintptr_t)dst) & 15u) == 0;
+    if (contig && aligned) {
+        cast_contig_kernel<S, D><<<grid_for((n + kVec - 1) / kVec), kThreads, 0, stream>>>(src, dst, n);
+    } else {
+        CollapsedDims d = dims;
+        if (contig) { d.rank = 1; d.shape[0] = n; d.strides[0] = 1; }
+        cast_strided_kernel<S, D><<<grid_for(n), kThreads, 0, stream>>>(src, dst, n, d);
+    }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
+}  // namespace
+
+int launch_cast(int s, int d, const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t st) {
+    if (n <= 0) return MAGB200_OK;
+#define PAIR(SS, DD) if (s == SS && d == DD) return launch_pair<SS, DD>(src, dst, n, dims, contig, st);
+    PAIR(MAGB200_F32, MAGB200_F32) PAIR(MAGB200_F32, MAGB200_F16) PAIR(MAGB200_F32, MAGB200_BF16)
+    PAIR(MAGB200_F16, MAGB200_F32) PAIR(MAGB200_F16, MAGB200_F16) PAIR(MAGB200_F16, MAGB200_BF16)
+    PAIR(MAGB200_BF16, MAGB200_F32) PAIR(MAGB200_BF16, MAGB200_F16) PAIR(MAGB200_BF16, MAGB200_BF16)
+#undef PAIR
+    set_error("cast: unsupported dtype pair %d -> %d", s, d);
+    return MAGB200_ERR_INVALID_ARG;
+}
+
+int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream) {
+    if (n <= 0) return MAGB200_OK;
+    // Host-side conversion with the same formulas as the device path (bf16: integer RNE; fp16: RNE).
+    float f = (float)value;
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    uint32_t bits = u;
+    if (dt == MAGB200_BF16) {
+        bits = ((u & 0x7FFFFFFFu) > 0x7F800000u) ? 0x7FC0u : ((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+        fill_kernel<MAGB200_BF16><<<grid_for(n), kThreads, 0, stream>>>(dst, n, bits);
+    } else if (dt == MAGB200_F16) {
+        uint32_t a = u & 0x7FFFFFFFu;
+        if (a > 0x7F800000u) bits = ((u >> 16) & 0x8000u) | 0x7E00u | ((a >> 13) & 0x3FFu);
+        else bits = (uint32_t)__half_as_ushort(__float2half_rn(f));
+        fill_kernel<MAGB200_F16><<<grid_for(n), kThreads, 0, stream>>>(dst, n, bits);
+    } else if (dt == MAGB200_F32) {
+        fill_kernel<MAGB200_F32><<<grid_for(n), kThreads, 0, stream>>>(dst, n, bits);
+    } else {
+        set_error("fill: unsupported dtype %d", dt);
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
+}  // namespace magb200

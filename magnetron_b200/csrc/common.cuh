@@ -1,0 +1,121 @@
+// Shared device/host helpers for the B200 matmul + cast path.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/magnetron_b200.h"
+
+namespace magb200 {
+
+constexpr int kMaxDims = MAGB200_MAX_DIMS;
+constexpr int kNumSMsB200 = 148;
+
+// ---- error plumbing (thread-local message, never an exception across the C ABI) -----------------
+void set_error(const char *fmt, ...);
+int  cuda_fail(cudaError_t e, const char *what, const char *file, int line);
+void count_launch(int n = 1);
+
+#define MAGB200_CUDA_TRY(expr)                                                        \
+    do {                                                                              \
+        cudaError_t _e = (expr);                                                      \
+        if (_e != cudaSuccess) return ::magb200::cuda_fail(_e, #expr, __FILE__, __LINE__); \
+    } while (0)
+
+static inline size_t dtype_size(int dt) { return dt == MAGB200_F32 ? 4 : 2; }
+static inline bool dtype_ok(int dt) { return dt == MAGB200_F32 || dt == MAGB200_F16 || dt == MAGB200_BF16; }
+
+// ---- a view with its dimensions collapsed, passed to kernels by value ---------------------------
+// Adjacent dims d, d+1 are merged when stride[d] == stride[d+1]*shape[d+1]; size-1 dims vanish.
+struct CollapsedDims {
+    int     rank;               // 0..kMaxDims (0: a single element)
+    int64_t shape[kMaxDims];
+    int64_t strides[kMaxDims];
+};
+CollapsedDims collapse_dims(int rank, const int64_t *shape, const int64_t *strides);
+bool    view_is_contiguous(const magb200_view_t *v);
+int64_t view_numel(const magb200_view_t *v);
+
+// ---- bit-exact scalar conversions (device) ------------------------------------------------------
+// fp32 -> bf16: every NaN becomes 0x7FC0; otherwise round-to-nearest-even on the integer pattern
+// (magnetron/core/mag_bfloat16.h:47-58). cvt.rn.bf16.f32 is not used because it maps NaN to 0x7FFF.
+__device__ __forceinline__ uint32_t f32_bits_to_bf16_bits(uint32_t u) {
+    uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;
+    return ((u & 0x7FFFFFFFu) > 0x7F800000u) ? 0x7FC0u : r;
+}
+__device__ __forceinline__ uint32_t bf16_bits_to_f32_bits(uint32_t h) { return h << 16; }
+
+// fp32 -> fp16 with the semantics of x86 F16C `vcvtps2ph` (magnetron/cpu/mag_cpu_impl_cast.inl:12-28):
+// RNE with gradual underflow; NaN keeps sign + top 10 payload bits and gets the quiet bit.
+__device__ __forceinline__ uint32_t f32_bits_to_f16_bits(uint32_t u) {
+    uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return ((u >> 16) & 0x8000u) | 0x7E00u | ((a >> 13) & 0x3FFu);
+    return (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(u)));
+}
+// fp16 -> fp32 with the semantics of `vcvtph2ps` (magnetron/cpu/mag_cpu_impl_cast.inl:30-46):
+// exact; a signalling NaN is quieted, payload shifted up.
+__device__ __forceinline__ uint32_t f16_bits_to_f32_bits(uint32_t h) {
+    h &= 0xFFFFu;
+    if ((h & 0x7FFFu) > 0x7C00u) return ((h & 0x8000u) << 16) | 0x7FC00000u | ((h & 0x3FFu) << 13);
+    return __float_as_uint(__half2float(__ushort_as_half((unsigned short)h)));
+}
+
+template <int DT> __device__ __forceinline__ float load_as_f32(const void *p, int64_t i);
+template <> __device__ __forceinline__ float load_as_f32<MAGB200_F32>(const void *p, int64_t i) { return ((const float *)p)[i]; }
+template <> __device__ __forceinline__ float load_as_f32<MAGB200_F16>(const void *p, int64_t i) {
+    return __uint_as_float(f16_bits_to_f32_bits(((const uint16_t *)p)[i]));
+}
+template <> __device__ __forceinline__ float load_as_f32<MAGB200_BF16>(const void *p, int64_t i) {
+    return __uint_as_float(((uint32_t)((const uint16_t *)p)[i]) << 16);
+}
+template <int DT> __device__ __forceinline__ void store_from_f32(void *p, int64_t i, float v);
+template <> __device__ __forceinline__ void store_from_f32<MAGB200_F32>(void *p, int64_t i, float v) { ((float *)p)[i] = v; }
+template <> __device__ __forceinline__ void store_from_f32<MAGB200_F16>(void *p, int64_t i, float v) {
+    ((uint16_t *)p)[i] = (uint16_t)f32_bits_to_f16_bits(__float_as_uint(v));
+}
+template <> __device__ __forceinline__ void store_from_f32<MAGB200_BF16>(void *p, int64_t i, float v) {
+    ((uint16_t *)p)[i] = (uint16_t)f32_bits_to_bf16_bits(__float_as_uint(v));
+}
+
+// two fp32 accumulators -> one packed 32-bit word of two 16-bit results (element 0 in the low half)
+template <int DT> __device__ __forceinline__ uint32_t pack2_from_f32(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2_from_f32<MAGB200_BF16>(float lo, float hi) {
+    return f32_bits_to_bf16_bits(__float_as_uint(lo)) | (f32_bits_to_bf16_bits(__float_as_uint(hi)) << 16);
+}
+template <> __device__ __forceinline__ uint32_t pack2_from_f32<MAGB200_F16>(float lo, float hi) {
+    return f32_bits_to_f16_bits(__float_as_uint(lo)) | (f32_bits_to_f16_bits(__float_as_uint(hi)) << 16);
+}
+
+// ---- canonical description of one matmul, produced by the front-end in cabi.cu -----------------
+constexpr int kMaxBatchDims = 3;
+struct GemmProblem {
+    int     dtype;                 // operand and result dtype
+    int64_t M, N, K;
+    const void *A;                 // x data (base + offset applied)
+    const void *B;                 // y data
+    void       *C;                 // result, row-major [batch..., M, N], ldc = N
+    int64_t sAm, sAk;              // element strides of x's last two dims
+    int64_t sBk, sBn;              // element strides of y's last two dims
+    int     nbatch;                // collapsed batch dims, 0..kMaxBatchDims
+    int64_t bshape[kMaxBatchDims]; // result batch extents (outermost first)
+    int64_t bsA[kMaxBatchDims];    // x batch strides in elements (0 = broadcast)
+    int64_t bsB[kMaxBatchDims];    // y batch strides
+    int64_t batch_total;           // product of bshape
+};
+
+// kernel launchers (each returns a magb200_status_t); `stream` is the device's launch stream
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
+bool skinny_supported(const GemmProblem &p);
+int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk);
+bool tcgen05_supported(const GemmProblem &p);
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int device, int *status_word_dev);
+
+int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
+                const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);
+int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream);
+
+}  // namespace magb200

@@ -1,0 +1,499 @@
+// Prefill-shaped bf16/fp16 matmul on the 5th-generation tensor cores (sm_100a).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN. Three warp roles:
+//   warp 0     : TMA producer   -- cp.async.bulk.tensor loads of A (128 x 64) and B (BN x 64) tiles into
+//                                  a ring of shared-memory stages (128-byte swizzle), completion on mbarriers
+//   warp 1     : MMA issuer     -- one thread issues tcgen05.mma.kind::f16 (M=128, N=BN, K=16) straight from
+//                                  shared-memory descriptors, fp32 accumulators live in TMEM; tcgen05.commit
+//                                  releases each stage and finally signals the epilogue
+//   warps 2..5 : epilogue       -- tcgen05.ld the accumulator (each warp owns its 32 TMEM lanes), round once
+//                                  to bf16/fp16 and store to C
+// TMEM holds two accumulators (2 x BN columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts: either operand may be K-major (inner dim K: the `W.T` view of an nn.Linear weight, or a
+// plain row-major activation) or MN-major (inner dim M / N: a contiguous [K,N] weight, V in P.V, a
+// transposed activation). The major-ness goes into the instruction descriptor and the shared-memory
+// descriptors, so no operand is ever transposed or packed in memory. Batch and broadcast dims become extra
+// TMA coordinates (coordinate 0 on a broadcast dim).
+//
+// Every wait on an mbarrier is bounded: after about a second without progress the kernel raises a status
+// word, stops issuing work, drains and frees its TMEM, so a lost signal cannot wedge the device.
+#include "common.cuh"
+
+#include <cuda.h>  // CUtensorMap and enums only; the driver entry point is resolved at run time
+
+namespace magb200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 x 16-bit = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarp0 = 2;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr int kStatusTimeout = 1;
+
+struct TcArgs {
+    void *C;
+    int64_t M, N, K;
+    int dtype;
+    int a_mn, b_mn;                     // 1: operand is MN-major
+    int nbatch;
+    int64_t bshape[kMaxBatchDims];
+    int a_has[kMaxBatchDims], b_has[kMaxBatchDims];  // 0: operand is broadcast along this batch dim
+    int64_t tiles_m, tiles_n, total_tiles;
+    int num_kb;
+    int *status;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait. Returns false (and raises the CTA's abort flag) when the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (start address, LBO, SBO in 16-byte units;
+// bits 46-47 = descriptor version 1, bits 61-63 = 2 for SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <int BN> struct Cfg {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128 / 256 / 512 columns
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, int DT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
+    using C = Cfg<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;             // 1024-byte alignment for the 128B swizzle
+    unsigned char *tiles_ptr = smem_raw + (tiles - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles_ptr + (size_t)C::kStages * C::kStageBytes);
+    // barrier slots: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8u * C::kStages;
+    const uint32_t tfull0 = empty0 + 8u * C::kStages;
+    const uint32_t tempty0 = tfull0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 2 * C::kStages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * C::kStages + 5);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull0 + 8u * i, 1); mbar_init(tempty0 + 8u * i, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {  // TMEM allocation is a warp-wide operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t tiles_per_batch = args.tiles_m * args.tiles_n;
+
+    if (warp == 0) {
+        // ===================== TMA producer (one thread) =====================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x) {
+                const int64_t batch = tile / tiles_per_batch;
+                const int64_t trem = tile - batch * tiles_per_batch;
+                const int64_t tm = trem / args.tiles_n, tn = trem - tm * args.tiles_n;
+                const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+                int bc[kMaxBatchDims] = {0, 0, 0};
+                {
+                    int64_t rem = batch;
+                    for (int d = args.nbatch - 1; d >= 0; --d) {
+                        int64_t q = rem / args.bshape[d];
+                        bc[d] = (int)(rem - q * args.bshape[d]);
+                        rem = q;
+                    }
+                }
+                // TMA coordinates are fastest-dim first: {inner, outer, b2, b1, b0}
+                const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
+                const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
+                for (int kb = 0; kb < args.num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = full0 + 8u * stage;
+                    const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes;
+                    mbar_arrive_expect_tx(full, (uint32_t)C::kStageBytes);
+                    const int k0 = kb * BK;
+                    if (!args.a_mn) {
+                        tma_load_5d(sa, &tmA, full, k0, m0, a2, a1, a0);               // box {64 k, 128 m}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)                                 // boxes {64 m, 64 k}
+                            tma_load_5d(sa + c * 8192, &tmA, full, m0 + c * 64, k0, a2, a1, a0);
+                    }
+                    if (!args.b_mn) {
+                        tma_load_5d(sb, &tmB, full, k0, n0, b2, b1, b0);               // box {64 k, BN n}
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)                                 // boxes {64 n, 64 k}
+                            tma_load_5d(sb + c * 8192, &tmB, full, n0 + c * 64, k0, b2, b1, b0);
+                    }
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer (one thread) =====================
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, A/B format, major-ness, N>>3 at bit 17, M>>4 at bit 24
+            const uint32_t fmt = (DT == MAGB200_BF16) ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)args.a_mn << 15) |
+                                   ((uint32_t)args.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major tile: rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart (SBO), K step = 32 bytes.
+            // MN-major tile: chunks of 64 (MN) x 64 (K): 8-row K atoms 1024 bytes apart (SBO), MN chunks 8192
+            // bytes apart (LBO), K step of 16 rows = 2048 bytes.
+            const uint32_t a_lbo = args.a_mn ? 8192u : 16u, a_step = args.a_mn ? 2048u : 32u;
+            const uint32_t b_lbo = args.b_mn ? 8192u : 16u, b_step = args.b_mn ? 2048u : 32u;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t titer = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
+                const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < args.num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = make_smem_desc(sa + k * a_step, a_lbo, 1024u);
+                        const uint64_t bd = make_smem_desc(sb + k * b_step, b_lbo, 1024u);
+                        tcgen05_mma_f16(tmem_d, ad, bd, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty0 + 8u * stage);   // stage is free once these MMAs have read it
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tcgen05_commit(tfull0 + 8u * acc);  // accumulator complete
+            }
+        }
+    } else {
+        // ===================== epilogue (4 warps, 32 TMEM lanes each) =====================
+        const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        uint32_t titer = 0;
+        bool ok = true;
+        const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
+        for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
+            const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
+            const int64_t batch = tile / tiles_per_batch;
+            const int64_t trem = tile - batch * tiles_per_batch;
+            const int64_t tm = trem / args.tiles_n, tn = trem - tm * args.tiles_n;
+            const int64_t row = tm * BM + quarter * 32 + lane;
+            const int64_t n0 = tn * BN;
+            // every lane waits (each needs the acquire), then the warp agrees on one outcome so that the
+            // warp-wide tcgen05.ld below is never reached by a partial warp
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint16_t *crow = reinterpret_cast<uint16_t *>(args.C) + (batch * args.M + row) * args.N + n0;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c, r);
+                tmem_ld_wait();
+                if (row < args.M && n0 + c < args.N) {
+                    if (vec_ok && n0 + c + 32 <= args.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+        }
+    }
+
+    // ---- teardown: everyone meets here (all waits above are bounded), then the allocating warp frees TMEM
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, kStatusTimeout);
+        // let copies and MMAs that were already issued land before the shared memory and TMEM go away
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// One operand as TMA sees it: inner dim (unit stride), outer dim (pitch), up to three batch dims.
+struct OperandDesc {
+    const void *base;
+    int64_t inner_extent, outer_extent, outer_pitch;  // elements
+    int64_t bext[kMaxBatchDims], bstride[kMaxBatchDims];
+    int has[kMaxBatchDims];
+    uint32_t box_inner, box_outer;
+};
+
+bool operand_ok(const OperandDesc &o) {
+    if ((uintptr_t)o.base & 15u) return false;
+    if (o.outer_extent > 1 && (o.outer_pitch <= 0 || (o.outer_pitch * 2) % 16)) return false;
+    if (o.inner_extent >= (1ll << 32) || o.outer_extent >= (1ll << 32)) return false;
+    if (o.outer_pitch * 2 >= (1ll << 40)) return false;
+    for (int d = 0; d < kMaxBatchDims; ++d)
+        if (o.has[d] && (o.bstride[d] <= 0 || (o.bstride[d] * 2) % 16 || o.bstride[d] * 2 >= (1ll << 40) || o.bext[d] >= (1ll << 32)))
+            return false;
+    return true;
+}
+
+int encode(const OperandDesc &o, int dtype, CUtensorMap *out) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return MAGB200_ERR_CUDA; }
+    // fastest dim first: {inner, outer, b2, b1, b0}
+    cuuint64_t dims[5] = {(cuuint64_t)o.inner_extent, (cuuint64_t)o.outer_extent, 1, 1, 1};
+    cuuint64_t strides[4];
+    // A dim of extent 1 still needs a legal stride (multiple of 16 bytes); use the packed size below it.
+    uint64_t packed = (uint64_t)((o.inner_extent * 2 + 15) / 16 * 16);
+    strides[0] = o.outer_extent > 1 ? (cuuint64_t)o.outer_pitch * 2 : packed;
+    uint64_t prev = strides[0] * (uint64_t)o.outer_extent;
+    for (int i = 0; i < kMaxBatchDims; ++i) {
+        const int d = kMaxBatchDims - 1 - i;  // b2 is the fastest batch dim
+        if (o.has[d]) { dims[2 + i] = (cuuint64_t)o.bext[d]; strides[1 + i] = (cuuint64_t)o.bstride[d] * 2; }
+        else { dims[2 + i] = 1; strides[1 + i] = prev; }
+        if (strides[1 + i] >= (1ull << 40)) strides[1 + i] = 16;  // extent-1 dim: the value is never used
+        prev = strides[1 + i] * dims[2 + i];
+    }
+    cuuint32_t box[5] = {o.box_inner, o.box_outer, 1, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(out, dtype == MAGB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                    const_cast<void *>(o.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with %d (dims %llu %llu %llu %llu %llu, strides %llu %llu %llu %llu, box %u %u)", (int)r,
+                  (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2], (unsigned long long)dims[3],
+                  (unsigned long long)dims[4], (unsigned long long)strides[0], (unsigned long long)strides[1],
+                  (unsigned long long)strides[2], (unsigned long long)strides[3], box[0], box[1]);
+        return MAGB200_ERR_CUDA;
+    }
+    return MAGB200_OK;
+}
+
+// Layout of one operand for the tensor-core path, or false when TMA cannot describe it.
+bool describe(const GemmProblem &p, bool is_a, int BN, OperandDesc &o, int &mn_major) {
+    const int64_t s_mn = is_a ? p.sAm : p.sBn, s_k = is_a ? p.sAk : p.sBk;
+    const int64_t e_mn = is_a ? p.M : p.N;
+    o.base = is_a ? p.A : p.B;
+    if (s_k == 1 || p.K == 1) {            // K-major (with K == 1 the K stride is never stepped)
+        mn_major = 0;
+        o.inner_extent = p.K; o.outer_extent = e_mn; o.outer_pitch = s_mn;
+        o.box_inner = BK; o.box_outer = is_a ? BM : BN;
+    } else if (s_mn == 1 || e_mn == 1) {   // MN-major
+        mn_major = 1;
+        o.inner_extent = e_mn; o.outer_extent = p.K; o.outer_pitch = s_k;
+        o.box_inner = 64; o.box_outer = BK;
+    } else {
+        return false;
+    }
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        const int64_t st = d < p.nbatch ? (is_a ? p.bsA[d] : p.bsB[d]) : 0;
+        const int64_t ex = d < p.nbatch ? p.bshape[d] : 1;
+        o.has[d] = (ex > 1 && st != 0) ? 1 : 0;
+        o.bext[d] = o.has[d] ? ex : 1;
+        o.bstride[d] = st;
+    }
+    return operand_ok(o);
+}
+
+int pick_bn(const GemmProblem &p) {
+    // Largest tile that still gives every SM work; small outputs take narrower tiles.
+    const int64_t tm = (p.M + BM - 1) / BM;
+    for (int bn : {256, 128}) {
+        if (p.N >= bn && tm * ((p.N + bn - 1) / bn) * p.batch_total >= kNumSMsB200) return bn;
+    }
+    if (p.N > 128) return 128;  // few tiles either way: prefer fewer TMEM columns / more stages
+    return p.N > 64 ? 128 : 64;
+}
+
+template <int BN, int DT>
+int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st) {
+    using C = Cfg<BN>;
+    auto kernel = gemm_tcgen05_kernel<BN, DT>;
+    static bool attr_set = false;  // per template instantiation
+    if (!attr_set) {
+        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+        attr_set = true;
+    }
+    args.tiles_m = (p.M + BM - 1) / BM;
+    args.tiles_n = (p.N + BN - 1) / BN;
+    args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    const unsigned grid = (unsigned)(args.total_tiles < kNumSMsB200 ? args.total_tiles : kNumSMsB200);
+    kernel<<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, args);
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
+}  // namespace
+
+bool tcgen05_supported(const GemmProblem &p) {
+    if (p.dtype != MAGB200_BF16 && p.dtype != MAGB200_F16) return false;
+    if (p.M < 1 || p.N < 1 || p.K < 1) return false;
+    if (p.M >= (1ll << 31) || p.N >= (1ll << 31) || p.K >= (1ll << 31)) return false;
+    OperandDesc a, b;
+    int amn, bmn;
+    return describe(p, true, 128, a, amn) && describe(p, false, 128, b, bmn);
+}
+
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int device, int *status_word_dev) {
+    (void)device;
+    const int bn = pick_bn(p);
+    OperandDesc a, b;
+    int amn = 0, bmn = 0;
+    if (!describe(p, true, bn, a, amn) || !describe(p, false, bn, b, bmn)) {
+        set_error("tcgen05 matmul: operand layout cannot be described by a TMA tensor map");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = encode(a, p.dtype, &ta)) || (rc = encode(b, p.dtype, &tb))) return rc;
+    TcArgs args;
+    memset(&args, 0, sizeof(args));
+    args.C = p.C; args.M = p.M; args.N = p.N; args.K = p.K; args.dtype = p.dtype;
+    args.a_mn = amn; args.b_mn = bmn; args.nbatch = p.nbatch;
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        args.bshape[d] = d < p.nbatch ? p.bshape[d] : 1;
+        args.a_has[d] = a.has[d]; args.b_has[d] = b.has[d];
+    }
+    args.num_kb = (int)((p.K + BK - 1) / BK);
+    args.status = status_word_dev;
+#define LAUNCH(BNV)                                                                                   \
+    return p.dtype == MAGB200_BF16 ? launch_cfg<BNV, MAGB200_BF16>(p, ta, tb, args, st)                \
+                                   : launch_cfg<BNV, MAGB200_F16>(p, ta, tb, args, st)
+    if (bn == 256) { LAUNCH(256); }
+    if (bn == 128) { LAUNCH(128); }
+    LAUNCH(64);
+#undef LAUNCH
+}
+
+}  // namespace magb200

@@ -1,0 +1,444 @@
+// Decode-shaped products (M <= 8): weight-streaming kernels bound by HBM bandwidth.
+//
+// C[M,N] = A[M,K] . B[K,N] with a handful of activation rows and a large weight matrix B. Every
+// weight element is read from HBM exactly once with 128-bit loads that bypass L1; the activations
+// are staged once per CTA in shared memory; accumulation is fp32 over the whole K with one rounding.
+//
+//  * skinny_km: B is K-major (the `W.T` view of a row-major [N,K] nn.Linear weight: sBk == 1).
+//    One warp owns R consecutive weight rows; its 32 lanes stride along K in 16-byte vectors and the
+//    R*M partial sums are combined with warp shuffles.
+//  * skinny_nm: B is N-major (contiguous [K,N], the layout the reference's own GEMV path needs,
+//    magnetron/cpu/mag_cpu_impl_ops_matmul.inl:2940). One thread owns 16 bytes of consecutive
+//    columns, the 8 warps of a CTA split the CTA's K range, partial sums meet in shared memory.
+//
+// When K is too long for the activation tile to fit in shared memory, or N is too small to occupy
+// 148 SMs, K is split across CTAs (grid.y): each split writes fp32 partials to a scratch buffer
+// [split][batch][M][N] and a second tiny kernel sums the splits in a fixed order and rounds once,
+// so results do not depend on scheduling.
+#include "common.cuh"
+
+namespace magb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <int DT> struct Elem { static constexpr int size = 2; static constexpr int vec = 8; using bits = uint16_t; };
+template <> struct Elem<MAGB200_F32> { static constexpr int size = 4; static constexpr int vec = 4; using bits = uint32_t; };
+
+struct SkinnyArgs {
+    const void *A, *B;
+    void *C;            // result [batch][M][N] in the operand dtype (used when nsplit == 1)
+    float *partial;     // fp32 scratch [nsplit][batch][M][N] (used when nsplit > 1)
+    int64_t N, K;
+    int64_t sAm, sAk;   // activation strides (elements)
+    int64_t ldb;        // pitch of B's slow dim (elements): sBn for K-major, sBk for N-major
+    int64_t kch;        // K elements per split (multiple of the vector width)
+    int nsplit;
+    int nbatch;
+    int64_t bshape[kMaxBatchDims], bsA[kMaxBatchDims], bsB[kMaxBatchDims];
+    int64_t batch_total;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// 16 bytes of storage -> fp32 lanes
+template <int DT> __device__ __forceinline__ void unpack(const uint4 &v, float (&f)[Elem<DT>::vec]) {
+    if constexpr (DT == MAGB200_F32) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else if constexpr (DT == MAGB200_BF16) {
+        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+        f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+        f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xFFFF0000u);
+        f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xFFFF0000u);
+    } else {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+}
+
+__device__ __forceinline__ void batch_offsets(const SkinnyArgs &a, int64_t batch, int64_t &offA, int64_t &offB) {
+    offA = 0; offB = 0;
+    int64_t rem = batch;
+    for (int d = a.nbatch - 1; d >= 0; --d) {
+        int64_t q = rem / a.bshape[d];
+        int64_t idx = rem - q * a.bshape[d];
+        offA += idx * a.bsA[d];
+        offB += idx * a.bsB[d];
+        rem = q;
+    }
+}
+
+template <int DT> __device__ __forceinline__ void store_result(const SkinnyArgs &a, int64_t batch, int split, int m, int M,
+                                                               int64_t n, float v) {
+    if (a.nsplit == 1) store_from_f32<DT>(a.C, (batch * M + m) * a.N + n, v);
+    else a.partial[(((int64_t)split * a.batch_total + batch) * M + m) * a.N + n] = v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// K-major weights: grid = (row blocks, nsplit, batch)
+// ------------------------------------------------------------------------------------------------
+template <int DT, int M, int R>
+__global__ void __launch_bounds__(kThreads) skinny_km_kernel(const SkinnyArgs a) {
+    using E = Elem<DT>;
+    constexpr int V = E::vec;
+    extern __shared__ __align__(16) unsigned char smem[];
+    typename E::bits *xs = reinterpret_cast<typename E::bits *>(smem);  // [M][kch]
+
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int64_t kc = min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+
+    // stage the activation chunk (raw bits, any strides)
+    {
+        const typename E::bits *A = reinterpret_cast<const typename E::bits *>(a.A) + offA;
+        for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
+            int64_t m = idx / kc, k = idx - m * kc;
+            xs[m * a.kch + k] = A[m * a.sAm + (k0 + k) * a.sAk];
+        }
+    }
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t kvecs = kc / V;
+    const int64_t kchv = a.kch / V;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(xs);
+    const typename E::bits *Bbase = reinterpret_cast<const typename E::bits *>(a.B) + offB + k0;
+
+    for (int64_t row0 = ((int64_t)blockIdx.x * kWarps + warp) * R; row0 < a.N; row0 += (int64_t)gridDim.x * kWarps * R) {
+        float acc[R][M];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+        const uint4 *wrow[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            int64_t row = min(row0 + r, a.N - 1);  // clamp: tail rows are computed twice, stored once
+            wrow[r] = reinterpret_cast<const uint4 *>(Bbase + row * a.ldb);
+        }
+#pragma unroll 2
+        for (int64_t kv = lane; kv < kvecs; kv += 32) {
+            uint4 w[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) w[r] = ldg_stream(wrow[r] + kv);
+            float wf[R][V];
+#pragma unroll
+            for (int r = 0; r < R; ++r) unpack<DT>(w[r], wf[r]);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float xf[V];
+                unpack<DT>(xv[m * kchv + kv], xf);
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int j = 0; j < V; ++j) acc[r][m] = fmaf(wf[r][j], xf[j], acc[r][m]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float v = acc[r][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                acc[r][m] = v;
+            }
+        // lane (r*M + m) stores one value, so the R*M results leave the warp in one pass
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (lane == ((r * M + m) & 31) && row0 + r < a.N) store_result<DT>(a, batch, split, m, M, row0 + r, acc[r][m]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// N-major weights: grid = (column blocks, nsplit, batch); a CTA covers 32*V columns
+// ------------------------------------------------------------------------------------------------
+template <int DT, int M>
+__global__ void __launch_bounds__(kThreads) skinny_nm_kernel(const SkinnyArgs a) {
+    using E = Elem<DT>;
+    constexpr int V = E::vec;
+    constexpr int CB = 32 * V;
+    extern __shared__ __align__(16) unsigned char smem[];
+    float *xs = reinterpret_cast<float *>(smem);   // [M][kch] activations as fp32
+    float *red = xs + (int64_t)M * a.kch;          // [M][CB] cross-warp sums
+
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int64_t kc = min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+
+    for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
+        int64_t m = idx / kc, k = idx - m * kc;
+        xs[m * a.kch + k] = load_as_f32<DT>(a.A, offA + m * a.sAm + (k0 + k) * a.sAk);
+    }
+    for (int idx = threadIdx.x; idx < M * CB; idx += kThreads) red[idx] = 0.f;
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t col = (int64_t)blockIdx.x * CB + (int64_t)lane * V;
+    float acc[M][V];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[m][j] = 0.f;
+
+    if (col < a.N) {  // N is a multiple of V, so a thread's V columns are all in range or all out
+        // contiguous K slice per warp
+        const int64_t per = (kc + kWarps - 1) / kWarps;
+        const int64_t kb = warp * per, ke = min(kc, kb + per);
+        const typename E::bits *Bp = reinterpret_cast<const typename E::bits *>(a.B) + offB + k0 * a.ldb + col;
+        int64_t k = kb;
+        for (; k + 4 <= ke; k += 4) {
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = ldg_stream(reinterpret_cast<const uint4 *>(Bp + (k + u) * a.ldb));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float wf[V];
+                unpack<DT>(w[u], wf);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    float x = xs[m * a.kch + k + u];
+#pragma unroll
+                    for (int j = 0; j < V; ++j) acc[m][j] = fmaf(x, wf[j], acc[m][j]);
+                }
+            }
+        }
+        for (; k < ke; ++k) {
+            float wf[V];
+            unpack<DT>(ldg_stream(reinterpret_cast<const uint4 *>(Bp + k * a.ldb)), wf);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float x = xs[m * a.kch + k];
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[m][j] = fmaf(x, wf[j], acc[m][j]);
+            }
+        }
+    }
+    // Cross-warp sum in a fixed order (warp 0 first ... warp 7 last) so the result is reproducible.
+    for (int w = 0; w < kWarps; ++w) {
+        if (warp == w) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int j = 0; j < V; ++j) red[m * CB + lane * V + j] += acc[m][j];
+        }
+        __syncthreads();
+    }
+    for (int idx = threadIdx.x; idx < M * CB; idx += kThreads) {
+        int m = idx / CB, c = idx - m * CB;
+        int64_t n = (int64_t)blockIdx.x * CB + c;
+        if (n < a.N) store_result<DT>(a, batch, split, m, M, n, red[idx]);
+    }
+}
+
+// partial[nsplit][total] -> C[total], splits summed in index order, one rounding
+template <int DT>
+__global__ void __launch_bounds__(kThreads) skinny_finalize_kernel(const float *__restrict__ partial, void *__restrict__ C,
+                                                                   int64_t total, int nsplit) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
+        float s = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) s += partial[(int64_t)sp * total + i];
+        store_from_f32<DT>(C, i, s);
+    }
+}
+
+constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
+
+struct Plan {
+    bool km;       // K-major weights
+    int R;         // rows per warp (km)
+    int64_t kch;
+    int nsplit;
+    size_t smem;
+    unsigned gridx;
+};
+
+template <int DT>
+bool make_plan(const GemmProblem &p, Plan &pl) {
+    using E = Elem<DT>;
+    const int V = E::vec;
+    const int M = (int)p.M;
+    const bool km = (p.sBk == 1 && p.K > 1) || (p.sBk == 1 && p.N == 1);
+    const bool nm = (p.sBn == 1);
+    if (!km && !nm) return false;
+    if (((uintptr_t)p.B) & 15u) return false;
+    if (p.batch_total > 65535) return false;
+    for (int d = 0; d < p.nbatch; ++d)
+        if (p.bsB[d] % V) return false;  // every batch slice of B must stay 16-byte aligned
+    pl.km = km;
+    if (km) {
+        if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
+        const int64_t warps_wanted = (int64_t)kNumSMsB200 * 2 * kWarps;
+        pl.R = (p.N >= 4 * warps_wanted) ? 4 : (p.N >= 2 * warps_wanted ? 2 : 1);
+        if (M > 4 && pl.R > 2) pl.R = 2;  // keep R*M accumulators + unpacked operands in registers
+        int64_t kch_max = (int64_t)(kSmemBudget / ((size_t)M * E::size));
+        kch_max -= kch_max % (V * 32);
+        int64_t kch = p.K;
+        int nsplit = 1;
+        if (kch > kch_max) { nsplit = (int)((p.K + kch_max - 1) / kch_max); }
+        // too few row groups to occupy the GPU and a long K: split K as well
+        const int64_t groups = (p.N + pl.R - 1) / pl.R * p.batch_total;
+        if (groups < warps_wanted / 2 && p.K >= 4096) {
+            int want = (int)((warps_wanted / 2 + groups - 1) / groups);
+            int cap = (int)(p.K / 1024);
+            if (want > cap) want = cap;
+            if (want > nsplit) nsplit = want;
+        }
+        if (nsplit > 1) {
+            kch = (p.K + nsplit - 1) / nsplit;
+            kch = (kch + V * 32 - 1) / (V * 32) * (V * 32);
+            nsplit = (int)((p.K + kch - 1) / kch);
+        }
+        pl.kch = kch; pl.nsplit = nsplit;
+        pl.smem = (size_t)M * kch * E::size;
+        int64_t blocks = (p.N + (int64_t)kWarps * pl.R - 1) / ((int64_t)kWarps * pl.R);
+        int64_t cap = ((int64_t)kNumSMsB200 * 2 * 4) / ((int64_t)nsplit * p.batch_total) ;
+        if (cap < 1) cap = 1;
+        pl.gridx = (unsigned)(blocks < cap ? blocks : cap);
+    } else {
+        if (p.N % V || p.sBk % V) return false;
+        const int CB = 32 * V;
+        int64_t kch_max = (int64_t)((kSmemBudget - (size_t)M * CB * 4) / ((size_t)M * 4));
+        kch_max -= kch_max % 32;
+        int64_t kch = p.K;
+        int nsplit = 1;
+        if (kch > kch_max) nsplit = (int)((p.K + kch_max - 1) / kch_max);
+        const int64_t blocks = (p.N + CB - 1) / CB;
+        if (blocks * p.batch_total < kNumSMsB200 && p.K >= 2048) {
+            int want = (int)((kNumSMsB200 * 2 + blocks * p.batch_total - 1) / (blocks * p.batch_total));
+            int cap = (int)(p.K / 512);
+            if (want > cap) want = cap;
+            if (want > nsplit) nsplit = want;
+        }
+        if (nsplit > 1) {
+            kch = (p.K + nsplit - 1) / nsplit;
+            kch = (kch + 31) / 32 * 32;
+            nsplit = (int)((p.K + kch - 1) / kch);
+        }
+        pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
+        pl.smem = (size_t)M * kch * 4 + (size_t)M * CB * 4;
+        pl.gridx = (unsigned)blocks;
+    }
+    return pl.nsplit <= 65535;
+}
+
+template <typename K>
+int set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return MAGB200_OK;
+}
+
+template <int DT, int M>
+int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStream_t st) {
+    dim3 grid(pl.gridx, pl.nsplit, (unsigned)p.batch_total);
+    int rc = MAGB200_OK;
+    if (pl.km) {
+        if (pl.R == 4) {
+            if constexpr (M <= 4) {
+                if ((rc = set_smem(skinny_km_kernel<DT, M, 4>, pl.smem))) return rc;
+                skinny_km_kernel<DT, M, 4><<<grid, kThreads, pl.smem, st>>>(a);
+            }
+        } else if (pl.R == 2) {
+            if ((rc = set_smem(skinny_km_kernel<DT, M, 2>, pl.smem))) return rc;
+            skinny_km_kernel<DT, M, 2><<<grid, kThreads, pl.smem, st>>>(a);
+        } else {
+            if ((rc = set_smem(skinny_km_kernel<DT, M, 1>, pl.smem))) return rc;
+            skinny_km_kernel<DT, M, 1><<<grid, kThreads, pl.smem, st>>>(a);
+        }
+    } else {
+        if ((rc = set_smem(skinny_nm_kernel<DT, M>, pl.smem))) return rc;
+        skinny_nm_kernel<DT, M><<<grid, kThreads, pl.smem, st>>>(a);
+    }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
+template <int DT>
+int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk) {
+    Plan pl;
+    if (!make_plan<DT>(p, pl)) { set_error("skinny: layout not supported"); return MAGB200_ERR_INVALID_ARG; }
+    const int64_t total = p.batch_total * p.M * p.N;
+    if (pl.nsplit > 1 && (size_t)pl.nsplit * total * sizeof(float) > scratch_bytes) {
+        set_error("skinny: split-K scratch of %zu bytes exceeds the %zu available", (size_t)pl.nsplit * total * 4, scratch_bytes);
+        return MAGB200_ERR_TOO_LARGE;
+    }
+    SkinnyArgs a;
+    a.A = p.A; a.B = p.B; a.C = p.C; a.partial = scratch;
+    a.N = p.N; a.K = p.K; a.sAm = p.sAm; a.sAk = p.sAk;
+    a.ldb = pl.km ? p.sBn : p.sBk;
+    a.kch = pl.kch; a.nsplit = pl.nsplit; a.nbatch = p.nbatch; a.batch_total = p.batch_total;
+    for (int d = 0; d < kMaxBatchDims; ++d) { a.bshape[d] = p.bshape[d]; a.bsA[d] = p.bsA[d]; a.bsB[d] = p.bsB[d]; }
+    int rc;
+    switch (p.M) {
+#define CASE(MM) case MM: rc = launch_m<DT, MM>(p, pl, a, st); break;
+        CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
+#undef CASE
+        default: set_error("skinny: M=%lld out of range", (long long)p.M); return MAGB200_ERR_INVALID_ARG;
+    }
+    if (rc) return rc;
+    if (pl.nsplit > 1) {
+        int64_t blocks = (total + kThreads - 1) / kThreads;
+        if (blocks > kNumSMsB200 * 8) blocks = kNumSMsB200 * 8;
+        skinny_finalize_kernel<DT><<<(unsigned)blocks, kThreads, 0, st>>>(scratch, p.C, total, pl.nsplit);
+        count_launch();
+        MAGB200_CUDA_TRY(cudaGetLastError());
+    }
+    if (used_splitk) *used_splitk = pl.nsplit > 1;
+    return MAGB200_OK;
+}
+
+}  // namespace
+
+bool skinny_supported(const GemmProblem &p) {
+    if (p.M < 1 || p.M > 8) return false;
+    Plan pl;
+    switch (p.dtype) {
+        case MAGB200_F32:  return make_plan<MAGB200_F32>(p, pl);
+        case MAGB200_F16:  return make_plan<MAGB200_F16>(p, pl);
+        case MAGB200_BF16: return make_plan<MAGB200_BF16>(p, pl);
+    }
+    return false;
+}
+
+// Scratch needed by launch_skinny for this problem (0 when K is not split).
+size_t skinny_scratch_bytes(const GemmProblem &p) {
+    Plan pl;
+    bool ok = false;
+    switch (p.dtype) {
+        case MAGB200_F32:  ok = make_plan<MAGB200_F32>(p, pl); break;
+        case MAGB200_F16:  ok = make_plan<MAGB200_F16>(p, pl); break;
+        case MAGB200_BF16: ok = make_plan<MAGB200_BF16>(p, pl); break;
+    }
+    if (!ok || pl.nsplit <= 1) return 0;
+    return (size_t)pl.nsplit * p.batch_total * p.M * p.N * sizeof(float);
+}
+
+int launch_skinny(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk) {
+    switch (p.dtype) {
+        case MAGB200_F32:  return launch_dt<MAGB200_F32>(p, st, scratch, scratch_bytes, used_splitk);
+        case MAGB200_F16:  return launch_dt<MAGB200_F16>(p, st, scratch, scratch_bytes, used_splitk);
+        case MAGB200_BF16: return launch_dt<MAGB200_BF16>(p, st, scratch, scratch_bytes, used_splitk);
+    }
+    set_error("skinny: unsupported dtype %d", p.dtype);
+    return MAGB200_ERR_INVALID_ARG;
+}
+
+}  // namespace magb200

@@ -139,7 +139,7 @@ class MatmulShapeError(ValueError):
 
 def matmul_result_shape(xs, ys) -> tuple:
     """Result shape rules of `mag_matmul` (magnetron/core/mag_op_stubs.c:1249-1310):
-    (K)x(K)->() [stored as one element], (K)x(K,N)->(N), (M,K)x(K)->(M), otherwise batched with
+    (K)x(K)->() (a rank-0 scalar), (K)x(K,N)->(N), (M,K)x(K)->(M), otherwise batched with
     batch dims broadcast iff equal or 1."""
     xs, ys = tuple(xs), tuple(ys)
     if len(xs) < 1 or len(ys) < 1:
@@ -157,7 +157,7 @@ def matmul_result_shape(xs, ys) -> tuple:
         if a != b and a != 1 and b != 1:
             raise MatmulShapeError(f"batch dims {a} vs {b}")
     if len(xs) == 1 and len(ys) == 1:
-        return (1,)
+        return ()
     if len(xs) == 1 and len(ys) == 2:
         return (ys[1],)
     if len(xs) == 2 and len(ys) == 1:

@@ -87,6 +87,19 @@ class Tensor:
     def data_ptr(self) -> int:
         return self.api.lib.mag_tensor_data_ptr(self.ptr)
 
+    # view recipes (same method names as magnetron_b200.Tensor so one case list drives both)
+    def transpose(self, d0, d1):
+        return self.api.transpose(self, d0, d1)
+
+    def permute(self, dims):
+        return self.api.permute(self, dims)
+
+    def view(self, shape):
+        return self.api.view(self, shape)
+
+    def slice(self, dim, start, length, step=1):
+        return self.api.view_slice(self, dim, start, length, step)
+
 
 class MagApi:
     """One magnetron context on one device string ("cpu", "cuda:0", ...)."""
@@ -116,6 +129,7 @@ class MagApi:
             "mag_reshape": (C.c_int, [VP, C.POINTER(P), P, I64P, I64]),
             "mag_transpose": (C.c_int, [VP, C.POINTER(P), P, I64, I64]),
             "mag_permute": (C.c_int, [VP, C.POINTER(P), P, I64P, I64]),
+            "mag_view_slice": (C.c_int, [VP, C.POINTER(P), P, I64, I64, I64, I64]),
             "mag_matmul": (C.c_int, [VP, C.POINTER(P), P, P]),
             "mag_tensor_rank": (I64, [P]),
             "mag_tensor_shape_ptr": (I64P, [P]),
@@ -192,6 +206,9 @@ class MagApi:
 
     def permute(self, x: Tensor, dims) -> Tensor:
         return self._call(self.lib.mag_permute, x.ptr, self._dims(dims), len(dims))
+
+    def view_slice(self, x: Tensor, dim: int, start: int, length: int, step: int = 1) -> Tensor:
+        return self._call(self.lib.mag_view_slice, x.ptr, dim, start, length, step)
 
     def contiguous(self, x: Tensor) -> Tensor:
         return self._call(self.lib.mag_contiguous, x.ptr)
