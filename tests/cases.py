@@ -26,6 +26,8 @@ MATMUL_CASES = [
     ("linear_wT_tail", (19, 72), [], (37, 72), [("T", 0, 1)]),
     ("x_T", (40, 17), [("T", 0, 1)], (40, 9), []),                        # x transposed
     ("both_T", (40, 17), [("T", 0, 1)], (9, 40), [("T", 0, 1)]),
+    ("x_T_al", (64, 24), [("T", 0, 1)], (64, 16), []),                    # transposed x with a 16-byte-multiple pitch
+    ("both_T_al", (64, 136), [("T", 0, 1)], (16, 64), [("T", 0, 1)]),
     ("mat_vec", (12, 32), [], (32,), []),
     ("vec_mat", (32,), [], (32, 12), []),
     ("vec_vec", (48,), [], (48,), []),
@@ -41,7 +43,7 @@ MATMUL_CASES = [
     ("batch_y_T", (2, 3, 8, 16), [], (2, 3, 24, 16), [("T", 2, 3)]),       # q @ k.transpose(2,3)
     ("gqa_scores", (1, 2, 2, 16, 8), [], (1, 2, 16, 8), [("T", 2, 3), ("view", (1, 2, 1, 8, 16))]),
     ("gqa_pv", (1, 2, 2, 16, 16), [], (1, 2, 16, 8), [("view", (1, 2, 1, 16, 8))]),
-    ("slice_k", (10, 64), [("slice", 1, 16, 32, 1)], (64, 12), [("slice", 0, 16, 32, 1)]),   # row-sharded K slice
+    ("slice_k", (10, 64), [("slice", 1, 16, 32, 1)], (64, 16), [("slice", 0, 16, 32, 1)]),   # row-sharded K slice
     ("slice_n", (10, 32), [], (32, 48), [("slice", 1, 8, 24, 1)]),                           # column shard
     ("stride2", (6, 32), [("slice", 1, 0, 16, 2)], (16, 10), []),                            # inner stride 2
     ("permute_x", (4, 3, 16), [("permute", (1, 0, 2))], (16, 40), []),

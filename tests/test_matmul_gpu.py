@@ -1,0 +1,231 @@
+"""GPU parity tests of MAG_OP_MATMUL through the C ABI.
+
+Every case is checked three ways: (1) the accuracy gate against the reference CPU backend's golden
+result (error vs fp64 not above 2x the reference's), (2) this library's own bar -- one rounding of an
+fp32-accumulated sum, |err| <= (u + K 2^-24) sum_k|a||b| -- and (3) elementwise closeness to the
+reference result in the reference tests' tolerances wherever the reference itself is right."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import magnetron_b200 as mb
+from oracle import mag_oracle as O
+from oracle import ref_driver as R
+from tests import cases
+from tests.common import case_operands, case_truth, gate, golden, reference_defect_mask, unit_roundoff
+
+pytestmark = pytest.mark.gpu
+CASE_NAMES = [c[0] for c in cases.MATMUL_CASES]
+
+
+def run_case(dev, name, dt, kernel=None):
+    xb, yb = case_operands(name, dt)
+    _, _, xops, _, yops = cases.case_by_name(name)
+    tx, ty = mb.Tensor.from_bits(dev, dt, xb), mb.Tensor.from_bits(dev, dt, yb)
+    vx, vy = cases.apply_ops(tx, xops), cases.apply_ops(ty, yops)
+    mb.force_kernel(kernel)
+    try:
+        r = vx @ vy
+        used = mb.last_kernel()
+        mb.synchronize(dev)
+    finally:
+        mb.force_kernel(None)
+    got = r.to_bits()
+    for t in (r, tx, ty):
+        t.release()
+    return xb, yb, got, used, vx.shape[-1]
+
+
+def check_case(name, dname, dt, xb, yb, got, K):
+    truth, scale = case_truth(name, dt, xb, yb)
+    ref = golden("matmul_golden.npz")[f"{name}.{dname}.r"]
+    assert got.shape == truth.shape == tuple(golden("matmul_golden.npz")[f"{name}.{dname}.rshape"])
+    mg, _ = gate(dt, got, ref, truth, scale, K)
+    assert mg["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, mg        # single rounding of an fp32 sum
+    ok = ~reference_defect_mask(name, dt, truth.shape)
+    a, r = O.bits_to_f64(dt, got), O.bits_to_f64(dt, ref)
+    atol, rtol = ((1e-5, 1e-5) if dt == O.FLOAT32 else (1e-2, 1e-2))
+    assert np.all((np.abs(a - r) <= atol * max(1.0, np.abs(truth).max()) + rtol * np.abs(r))[ok])
+
+
+@pytest.mark.parametrize("name", CASE_NAMES)
+@pytest.mark.parametrize("dname", list(cases.DTYPES))
+def test_case_auto_route(gpu, name, dname):
+    dt = cases.DTYPES[dname]
+    xb, yb, got, used, K = run_case(gpu, name, dt)
+    assert used in ("tcgen05", "skinny", "skinny_splitk", "simt")
+    check_case(name, dname, dt, xb, yb, got, K)
+
+
+@pytest.mark.parametrize("name", CASE_NAMES)
+@pytest.mark.parametrize("dname", list(cases.DTYPES))
+def test_case_simt_kernel(gpu, name, dname):
+    dt = cases.DTYPES[dname]
+    xb, yb, got, used, K = run_case(gpu, name, dt, "simt")
+    assert used == "simt"
+    check_case(name, dname, dt, xb, yb, got, K)
+
+
+TC_CASES = ["sq64", "rect_big", "linear_wT", "linear_wT_tail", "x_T_al", "both_T_al", "batch_y_T", "gqa_scores", "gqa_pv",
+            "slice_k", "slice_n", "big_k", "tile_edge", "batch_same", "batch_bcast_y", "batch_mixed", "permute_x"]
+
+
+@pytest.mark.parametrize("name", TC_CASES)
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_case_tcgen05_kernel(gpu, name, dname):
+    """Small and ragged shapes forced through the tensor-core kernel: tails in M, N and K, both operand
+    major-nesses, batch and broadcast coordinates."""
+    dt = cases.DTYPES[dname]
+    xb, yb, got, used, K = run_case(gpu, name, dt, "tcgen05")
+    assert used == "tcgen05"
+    check_case(name, dname, dt, xb, yb, got, K)
+
+
+SKINNY_CASES = ["gemv_wT", "gemv_kn", "skinny4_wT", "skinny8_kn", "big_k"]
+
+
+@pytest.mark.parametrize("name", SKINNY_CASES)
+@pytest.mark.parametrize("dname", list(cases.DTYPES))
+def test_case_skinny_kernel(gpu, name, dname):
+    dt = cases.DTYPES[dname]
+    xb, yb, got, used, K = run_case(gpu, name, dt, "skinny")
+    assert used in ("skinny", "skinny_splitk")
+    check_case(name, dname, dt, xb, yb, got, K)
+
+
+def bits(dt, rng, shape, scale):
+    return O.f32_to_bits(dt, cases.gen_storage(rng, shape, scale))
+
+
+def sampled_check(dt, xb, wb_nk, got, rows, K):
+    """fp64 truth on a sample of output rows of x @ W.T (full-size shapes)."""
+    x = O.bits_to_f64(dt, xb[rows]); w = O.bits_to_f64(dt, wb_nk)
+    truth = x @ w.T
+    scale = np.abs(x) @ np.abs(w).T
+    m = O.error_metrics(dt, got[rows], truth, scale)
+    assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, m
+    return m
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f32"])
+def test_single_op_workload_512x2048x2048(gpu, dname):
+    """C[512,2048] = A[512,2048] @ W[2048,2048]^T with W a transposed strided view, seed 0; checked
+    against fp64 and, when the reference library is on this machine, against its error in the same run."""
+    dt = cases.DTYPES[dname]
+    rng = np.random.default_rng(0)
+    xb, wb = bits(dt, rng, (512, 2048), 1.0), bits(dt, rng, (2048, 2048), 0.02)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    r = tx @ tw.T
+    assert mb.last_kernel() == ("tcgen05" if dt == O.BFLOAT16 else "simt")
+    got = r.to_bits()
+    truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
+    scale = np.abs(O.bits_to_f64(dt, xb)) @ np.abs(O.bits_to_f64(dt, wb)).T
+    mg = O.error_metrics(dt, got, truth, scale)
+    assert mg["e"] <= unit_roundoff(dt) + 2048 * 2.0 ** -24, mg
+    if R.available():
+        api = R.MagApi("cpu", log_level=1)
+        try:
+            ra, rw = api.from_bits(dt, xb), api.from_bits(dt, wb)
+            rwt = api.transpose(rw, 0, 1)
+            rr = api.matmul(ra, rwt)
+            mr = O.error_metrics(dt, api.to_bits(rr), truth, scale)
+            for h in (rr, rwt, ra, rw):
+                h.release()
+        finally:
+            api.close(True)
+        assert mg["e"] <= 2.0 * mr["e"], (mg, mr)
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (4096, 1024, 4096), (1000, 12288, 4096), (4096, 4096, 12288)])
+def test_prefill_shapes_sampled(gpu, M, N, K):
+    """Qwen3-8B-shaped prefill GEMMs (seed 3) at full size; fp64 truth on 48 sampled rows, plus the
+    size-independent checks: identical result when rerun, and zero rows of A give zero rows of C."""
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(3)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.02)
+    xb[5] = 0; xb[M - 1] = 0
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    r = tx @ tw.T
+    assert mb.last_kernel() == "tcgen05"
+    got = r.to_bits()
+    rows = np.unique(np.concatenate([[0, 5, 127, 128, M - 1], rng.integers(0, M, 43)]))
+    sampled_check(dt, xb, wb, got, rows, K)
+    assert not got[5].any() and not got[M - 1].any()
+    again = (tx @ tw.T).to_bits()
+    assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N,K", [(2048, 1024), (1024, 1024), (3072, 1024), (1024, 3072), (151936, 1024), (5120, 25600)])
+def test_decode_shapes(gpu, M, N, K):
+    """Qwen3-0.6B decode projections and lm_head (and the long-K down projection of the 32B model),
+    batch sweep M in {1,2,4,8}, weights through the `W.T` view; fp64 truth on sampled output columns."""
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(2)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.02)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    r = tx @ tw.T
+    assert mb.last_kernel() in ("skinny", "skinny_splitk")
+    got = r.to_bits()
+    cols = np.unique(np.concatenate([[0, 1, N - 1], rng.integers(0, N, 500)]))
+    x = O.bits_to_f64(dt, xb); w = O.bits_to_f64(dt, wb[cols])
+    truth = x @ w.T
+    m = O.error_metrics(dt, got[:, cols], truth, np.abs(x) @ np.abs(w).T)
+    assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, m
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_attention_broadcast_shapes(gpu, dname):
+    """Scores Q @ K^T and outputs P @ V with K/V broadcast over 4 query heads per KV head through views
+    (reduced batch and sequence so the fp64 truth stays cheap)."""
+    dt = cases.DTYPES[dname]
+    B, KV, G, T, D = 2, 2, 4, 256, 128
+    rng = np.random.default_rng(4)
+    q, k, v = bits(dt, rng, (B, KV, G, T, D), 1.0), bits(dt, rng, (B, KV, T, D), 1.0), bits(dt, rng, (B, KV, T, D), 1.0)
+    tq, tk, tv = (mb.Tensor.from_bits(gpu, dt, a) for a in (q, k, v))
+    kt = tk.transpose(2, 3).view((B, KV, 1, D, T))
+    s = tq @ kt
+    assert mb.last_kernel() == "tcgen05" and s.shape == (B, KV, G, T, T)
+    qf, kf, vf = (O.bits_to_f64(dt, a) for a in (q, k, v))
+    truth = np.einsum("bhgtd,bhsd->bhgts", qf, kf)
+    scale = np.einsum("bhgtd,bhsd->bhgts", np.abs(qf), np.abs(kf))
+    m = O.error_metrics(dt, s.to_bits(), truth, scale)
+    assert m["e"] <= unit_roundoff(dt) + D * 2.0 ** -24, m
+    # P = softmax(scaled logits) rounded to the storage dtype, then P @ V
+    logits = truth / np.sqrt(D)
+    p = np.exp(logits - logits.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+    pb = O.f32_to_bits(dt, p.astype(np.float32))
+    tp = mb.Tensor.from_bits(gpu, dt, pb)
+    o = tp @ tv.view((B, KV, 1, T, D))
+    assert mb.last_kernel() == "tcgen05" and o.shape == (B, KV, G, T, D)
+    pf = O.bits_to_f64(dt, pb)
+    truth2 = np.einsum("bhgts,bhsd->bhgtd", pf, vf)
+    m2 = O.error_metrics(dt, o.to_bits(), truth2, np.einsum("bhgts,bhsd->bhgtd", np.abs(pf), np.abs(vf)))
+    assert m2["e"] <= unit_roundoff(dt) + T * 2.0 ** -24, m2
+
+
+def test_host_buffer_matmul(gpu):
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(8)
+    xb, wb = bits(dt, rng, (64, 256), 1.0), bits(dt, rng, (96, 256), 0.1)
+    out = np.empty((64, 96), np.uint16)
+    xv = mb.make_view(xb.ctypes.data, dt, (64, 256))
+    wv = mb.make_view(wb.ctypes.data, dt, (256, 96), (1, 256))   # W.T view of the host buffer
+    rv = mb.make_view(out.ctypes.data, dt, (64, 96))
+    mb.check(mb.lib().magb200_matmul_host(gpu, C.byref(xv), xb.nbytes, C.byref(wv), wb.nbytes, C.byref(rv)))
+    truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
+    m = O.error_metrics(dt, out, truth, np.abs(O.bits_to_f64(dt, xb)) @ np.abs(O.bits_to_f64(dt, wb)).T)
+    assert m["e"] <= unit_roundoff(dt) + 256 * 2.0 ** -24
+
+
+def test_errors(gpu):
+    a = mb.Tensor.from_bits(gpu, O.BFLOAT16, np.zeros((4, 5), np.uint16))
+    b = mb.Tensor.from_bits(gpu, O.BFLOAT16, np.zeros((6, 7), np.uint16))
+    with pytest.raises(mb.MagB200Error) as e:
+        a @ b
+    assert e.value.code == mb.ERR_SHAPE
+    c = mb.Tensor.from_bits(gpu, O.FLOAT16, np.zeros((5, 7), np.uint16))
+    out = mb.Tensor(gpu, O.BFLOAT16, (4, 7))
+    rc = mb.lib().magb200_matmul(gpu, C.byref(a.view_struct()), C.byref(c.view_struct()), C.byref(out.view_struct()))
+    assert rc == mb.ERR_INVALID_ARG      # both inputs must share one dtype (core/mag_op_stubs.c:224-247)
