@@ -9,6 +9,12 @@
 //
 // Tile: 128x128x16 per 256-thread CTA, 8x8 accumulators per thread held as 2x2 blocks of 4x4 so the
 // shared-memory reads are conflict-free 128-bit loads.
+//
+// fp32 accuracy: a single fp32 accumulator that walks the whole K loses several units in the last place
+// at K in the thousands, more than the reference's blocked CPU kernel does. For float32 the kernel
+// therefore sums each 16-wide K tile in a fresh accumulator and folds it into the running total with an
+// error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 16-term
+// tile. The 16-bit dtypes skip this: their error is set by the final rounding of the result.
 #include "common.cuh"
 
 namespace magb200 {
@@ -18,7 +24,7 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256, PAD = 4;
 
 template <int DT>
-__global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n) {
+__global__ void __launch_bounds__(THREADS, 1) gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n) {
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
 
@@ -46,11 +52,16 @@ __global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const GemmProblem p,
     const int t = threadIdx.x;
     const int tx = t & 15, ty = t >> 4;
 
-    float acc[8][8];
+    constexpr bool kCompensated = (DT == MAGB200_F32);
+    float acc[8][8];                                   // sum of the current K tile (fp32) or of all of K (16-bit)
+    float total[kCompensated ? 8 : 1][8], low[kCompensated ? 8 : 1][8];  // running total and its lost low part
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 8; ++j) {
+            acc[i][j] = 0.f;
+            if constexpr (kCompensated) { total[i][j] = 0.f; low[i][j] = 0.f; }
+        }
 
     const bool a_k_fast = (p.sAk == 1) || (p.sAm != 1);  // walk k fastest unless m is the unit-stride dim
     const bool b_n_fast = (p.sBn == 1) || (p.sBk != 1);
@@ -90,7 +101,27 @@ __global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const GemmProblem p,
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
+        if constexpr (kCompensated) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // TwoSum: s + e == total + acc exactly
+                    const float s = __fadd_rn(total[i][j], acc[i][j]);
+                    const float bp = __fsub_rn(s, total[i][j]);
+                    const float e = __fadd_rn(__fsub_rn(total[i][j], __fsub_rn(s, bp)), __fsub_rn(acc[i][j], bp));
+                    total[i][j] = s;
+                    low[i][j] = __fadd_rn(low[i][j], e);
+                    acc[i][j] = 0.f;
+                }
+        }
         __syncthreads();
+    }
+    if constexpr (kCompensated) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i][j] = __fadd_rn(total[i][j], low[i][j]);
     }
 
     // ---- epilogue: one rounding to the result dtype, row-major C with ldc = N ----

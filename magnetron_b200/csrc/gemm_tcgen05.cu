@@ -30,7 +30,6 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr int kStatusTimeout = 1;
 

@@ -4,9 +4,15 @@
 // weight element is read from HBM exactly once with 128-bit loads that bypass L1; the activations
 // are staged once per CTA in shared memory; accumulation is fp32 over the whole K with one rounding.
 //
-//  * skinny_km: B is K-major (the `W.T` view of a row-major [N,K] nn.Linear weight: sBk == 1).
-//    One warp owns R consecutive weight rows; its 32 lanes stride along K in 16-byte vectors and the
-//    R*M partial sums are combined with warp shuffles.
+//  * skinny_km_mma (bf16 / fp16): B is K-major (the `W.T` view of a row-major [N,K] nn.Linear weight:
+//    sBk == 1). A warp owns 16 consecutive weight rows and feeds them, straight from its 128-bit global
+//    loads, into mma.sync.m16n8k16 as the A operand; the (up to 8) activation rows are the 8 columns of
+//    the B operand. Because a dot product does not care in which order K is visited, the 8 consecutive K
+//    values that one 128-bit load brings are assigned to the instruction's K slots by a fixed permutation
+//    that A and B share, so no shuffle or shared-memory transpose of the weights is needed. The FP32 pipe
+//    is then idle: M = 8 costs the same as M = 1 and the kernel stays HBM bound across the batch sweep.
+//  * skinny_km (float32, and layouts the MMA variant cannot take): one warp owns R consecutive weight
+//    rows; its 32 lanes stride along K in 16-byte vectors, FFMA, warp-shuffle reduction.
 //  * skinny_nm: B is N-major (contiguous [K,N], the layout the reference's own GEMV path needs,
 //    magnetron/cpu/mag_cpu_impl_ops_matmul.inl:2940). One thread owns 16 bytes of consecutive
 //    columns, the 8 warps of a CTA split the CTA's K range, partial sums meet in shared memory.
@@ -164,6 +170,102 @@ __global__ void __launch_bounds__(kThreads) skinny_km_kernel(const SkinnyArgs a)
 }
 
 // ------------------------------------------------------------------------------------------------
+// K-major 16-bit weights on mma.sync: grid = (row-tile groups, nsplit, batch)
+// ------------------------------------------------------------------------------------------------
+template <int DT> __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                            uint32_t b0, uint32_t b1) {
+    if constexpr (DT == MAGB200_BF16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// KW warps of the CTA split the CTA's K range, RW = 8 / KW warps take different 16-row tiles.
+// Fragment bookkeeping (g = lane / 4, t = lane % 4): the thread loads K values [k, k+8) of weight rows
+// r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
+// k+4..7: slots (2t, 2t+1) <- first pair, slots (2t+8, 2t+9) <- second pair, the same in A and B.
+template <int DT, int KW>
+__global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int64_t xstride,
+                                                                 const int64_t tiles_per_pass) {
+    constexpr int RW = kWarps / KW;
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem);                      // [M][xstride]
+    float *red = reinterpret_cast<float *>(smem + (size_t)M * xstride * 2);  // [KW][RW][128] when KW > 1
+
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int64_t kc = min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+    {
+        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA;
+        for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
+            int64_t m = idx / kc, k = idx - m * kc;
+            xs[m * xstride + k] = A[m * a.sAm + (k0 + k) * a.sAk];
+        }
+    }
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rw = warp / KW, kw = warp % KW;
+    const int g = lane >> 2, t = lane & 3;
+    int64_t per = (kc + KW - 1) / KW;
+    per = (per + 31) / 32 * 32;
+    const int64_t ks = min(kc, (int64_t)kw * per), ke = min(kc, ks + per);
+    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
+    const uint16_t *xrow = xs + (int64_t)g * xstride;
+    const int64_t num_tiles = (a.N + 15) / 16;
+
+    for (int64_t pass = 0; pass * tiles_per_pass < num_tiles; ++pass) {
+        const int64_t tile = pass * tiles_per_pass + (int64_t)blockIdx.x * RW + rw;
+        const bool active = tile < num_tiles;
+        const int64_t r0 = tile * 16;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        if (active) {
+            const uint16_t *pa = Bbase + min(r0 + g, a.N - 1) * a.ldb;       // clamp: tail rows are loaded twice, stored once
+            const uint16_t *pb = Bbase + min(r0 + g + 8, a.N - 1) * a.ldb;
+#pragma unroll 4
+            for (int64_t k = ks + t * 8; k < ke; k += 32) {
+                const uint4 wa = ldg_stream(reinterpret_cast<const uint4 *>(pa + k));
+                const uint4 wb = ldg_stream(reinterpret_cast<const uint4 *>(pb + k));
+                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                if (g < M) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+                mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+                mma_16816<DT>(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+            }
+        }
+        if constexpr (KW > 1) {
+            // sum the K slices in slice order (reproducible), then the kw == 0 warp stores
+            float *mine = red + ((size_t)kw * RW + rw) * 128 + lane * 4;
+            mine[0] = c[0]; mine[1] = c[1]; mine[2] = c[2]; mine[3] = c[3];
+            __syncthreads();
+            if (kw == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float s = 0.f;
+                    for (int w = 0; w < KW; ++w) s += red[((size_t)w * RW + rw) * 128 + lane * 4 + i];
+                    c[i] = s;
+                }
+            }
+            __syncthreads();
+        }
+        if (active && kw == 0) {
+            // c[0], c[1]: weight row r0+g, tokens 2t, 2t+1;  c[2], c[3]: weight row r0+g+8
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t n = r0 + g + (i >> 1) * 8;
+                const int m = 2 * t + (i & 1);
+                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i]);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // N-major weights: grid = (column blocks, nsplit, batch); a CTA covers 32*V columns
 // ------------------------------------------------------------------------------------------------
 template <int DT, int M>
@@ -263,6 +365,9 @@ constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
 
 struct Plan {
     bool km;       // K-major weights
+    bool mma;      // K-major 16-bit weights through mma.sync
+    int KW;        // warps along K per CTA (mma)
+    int64_t xstride;
     int R;         // rows per warp (km)
     int64_t kch;
     int nsplit;
@@ -283,6 +388,42 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     for (int d = 0; d < p.nbatch; ++d)
         if (p.bsB[d] % V) return false;  // every batch slice of B must stay 16-byte aligned
     pl.km = km;
+    pl.mma = false;
+    if (km && DT != MAGB200_F32) {
+        if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
+        // activation rows live in shared memory with a pitch of 64 bytes mod 128 so that the 8 row groups
+        // of a warp hit different banks
+        int64_t kch_max = (int64_t)(kSmemBudget - 8 * 1024) / ((int64_t)M * 2) - 96;
+        kch_max -= kch_max % 256;
+        int64_t kch = p.K;
+        int nsplit = 1;
+        if (kch > kch_max) nsplit = (int)((p.K + kch_max - 1) / kch_max);
+        const int64_t tiles = (p.N + 15) / 16;
+        const int64_t warps_wanted = (int64_t)kNumSMsB200 * 16;
+        // few row tiles and a long K: split K across CTAs too (each split keeps at least 2048 K values)
+        if (tiles * kWarps * p.batch_total < warps_wanted && p.K >= 8192) {
+            int want = (int)((warps_wanted + tiles * kWarps * p.batch_total - 1) / (tiles * kWarps * p.batch_total));
+            int cap = (int)(p.K / 2048);
+            if (want > cap) want = cap;
+            if (want > nsplit) nsplit = want;
+        }
+        if (nsplit > 1) {
+            kch = (p.K + nsplit - 1) / nsplit;
+            kch = (kch + 255) / 256 * 256;
+            nsplit = (int)((p.K + kch - 1) / kch);
+        }
+        int KW = 1;
+        while (KW < kWarps && tiles * KW * nsplit * p.batch_total < warps_wanted && kch / (KW * 2) >= 128) KW *= 2;
+        pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
+        pl.xstride = (kch + 63) / 64 * 64 + 32;
+        pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0);
+        const int RW = kWarps / KW;
+        int64_t blocks = (tiles + RW - 1) / RW;
+        int64_t cap = ((int64_t)kNumSMsB200 * 8) / ((int64_t)nsplit * p.batch_total);
+        if (cap < 1) cap = 1;
+        pl.gridx = (unsigned)(blocks < cap ? blocks : cap);
+        return pl.nsplit <= 65535;
+    }
     if (km) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
         const int64_t warps_wanted = (int64_t)kNumSMsB200 * 2 * kWarps;
@@ -349,7 +490,19 @@ template <int DT, int M>
 int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStream_t st) {
     dim3 grid(pl.gridx, pl.nsplit, (unsigned)p.batch_total);
     int rc = MAGB200_OK;
-    if (pl.km) {
+    if (pl.mma) {
+        if constexpr (DT != MAGB200_F32) {
+            const int RW = kWarps / pl.KW;
+            const int64_t tiles_per_pass = (int64_t)pl.gridx * RW;
+#define LAUNCH_KW(KWV)                                                                                   \
+    case KWV:                                                                                            \
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
+        skinny_km_mma_kernel<DT, KWV><<<grid, kThreads, pl.smem, st>>>(a, M, pl.xstride, tiles_per_pass); \
+        break;
+            switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
+#undef LAUNCH_KW
+        }
+    } else if (pl.km) {
         if (pl.R == 4) {
             if constexpr (M <= 4) {
                 if ((rc = set_smem(skinny_km_kernel<DT, M, 4>, pl.smem))) return rc;
