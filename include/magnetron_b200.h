@@ -134,6 +134,18 @@ int  magb200_matmul_host(int device, const magb200_view_t *x, size_t x_storage_b
                          const magb200_view_t *r);
 int  magb200_cast_host(int device, const magb200_view_t *src, size_t src_storage_bytes, const magb200_view_t *dst);
 
+/* ---- CUDA graphs for launch-bound sequences -----------------------------------------------------
+ * A decode step is hundreds of microsecond-sized matmuls; replaying them as one graph removes the
+ * per-call host cost. Between begin and end, operator calls on `device` are recorded instead of run.
+ * Calls that allocate or synchronise (malloc/free/upload/download/synchronize, the *_host entry points,
+ * a matmul whose split-K workspace would have to grow) are not allowed while capturing: run the sequence
+ * once un-captured first. The reference has no counterpart (its CPU backend runs each operator
+ * synchronously, magnetron/cpu/mag_cpu.c:70-89). */
+int  magb200_graph_begin_capture(int device);
+int  magb200_graph_end_capture(int device, void **out_graph);
+int  magb200_graph_launch(int device, void *graph);     /* stream-ordered replay of the recorded launches */
+int  magb200_graph_destroy(void *graph);
+
 /* ---- timing on the library's stream (CUDA events recorded on the launch stream) --------------- */
 int  magb200_event_create(void **out_event);
 int  magb200_event_destroy(void *event);

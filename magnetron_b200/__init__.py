@@ -79,6 +79,10 @@ SIGNATURES = {
     "magb200_force_kernel": (C.c_int, [C.c_int]),
     "magb200_matmul_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP, C.c_size_t, _VP]),
     "magb200_cast_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP]),
+    "magb200_graph_begin_capture": (C.c_int, [C.c_int]),
+    "magb200_graph_end_capture": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "magb200_graph_launch": (C.c_int, [C.c_int, C.c_void_p]),
+    "magb200_graph_destroy": (C.c_int, [C.c_void_p]),
     "magb200_event_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "magb200_event_destroy": (C.c_int, [C.c_void_p]),
     "magb200_event_record": (C.c_int, [C.c_int, C.c_void_p]),

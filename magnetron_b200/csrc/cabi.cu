@@ -40,6 +40,7 @@ struct DeviceState {
     void *staging[3] = {nullptr, nullptr, nullptr};  // device buffers of the host-buffer entry points
     size_t staging_bytes[3] = {0, 0, 0};
     char name[256] = "";
+    bool capturing = false;          // between graph_begin_capture and graph_end_capture
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -87,6 +88,10 @@ static int ensure_device(int device, DeviceState **out) {
 
 static int ensure_scratch(DeviceState &d, size_t bytes) {
     if (bytes <= d.scratch_bytes) return MAGB200_OK;
+    if (d.capturing) {
+        set_error("the split-K workspace would have to grow to %zu bytes during stream capture; run the same call once before capturing", bytes);
+        return MAGB200_ERR_INVALID_ARG;
+    }
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
     MAGB200_CUDA_TRY(cudaFree(d.scratch));
     d.scratch = nullptr; d.scratch_bytes = 0;
@@ -540,6 +545,43 @@ int magb200_cast_host(int device, const magb200_view_t *src, size_t src_bytes, c
     if ((rc = cast_device(*d, &ds, &dd, false))) return rc;
     MAGB200_CUDA_TRY(cudaMemcpyAsync(view_data(dst), d->staging[2], dst_bytes, cudaMemcpyDeviceToHost, d->stream));
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return MAGB200_OK;
+}
+
+int magb200_graph_begin_capture(int device) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (d->capturing) { set_error("graph capture is already active on device %d", device); return MAGB200_ERR_INVALID_ARG; }
+    MAGB200_CUDA_TRY(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+    d->capturing = true;
+    return MAGB200_OK;
+}
+int magb200_graph_end_capture(int device, void **out_graph) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!d->capturing || !out_graph) { set_error("graph_end_capture without a capture in progress"); return MAGB200_ERR_INVALID_ARG; }
+    d->capturing = false;
+    cudaGraph_t graph = nullptr;
+    MAGB200_CUDA_TRY(cudaStreamEndCapture(d->stream, &graph));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate", __FILE__, __LINE__);
+    *out_graph = (void *)exec;
+    return MAGB200_OK;
+}
+int magb200_graph_launch(int device, void *graph) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!graph) { set_error("graph_launch: null graph"); return MAGB200_ERR_INVALID_ARG; }
+    MAGB200_CUDA_TRY(cudaGraphLaunch((cudaGraphExec_t)graph, d->stream));
+    return MAGB200_OK;
+}
+int magb200_graph_destroy(void *graph) {
+    if (graph) MAGB200_CUDA_TRY(cudaGraphExecDestroy((cudaGraphExec_t)graph));
     return MAGB200_OK;
 }
 

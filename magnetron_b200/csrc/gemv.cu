@@ -108,10 +108,8 @@ __global__ void __launch_bounds__(kThreads) skinny_km_kernel(const SkinnyArgs a)
     // stage the activation chunk (raw bits, any strides)
     {
         const typename E::bits *A = reinterpret_cast<const typename E::bits *>(a.A) + offA;
-        for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
-            int64_t m = idx / kc, k = idx - m * kc;
-            xs[m * a.kch + k] = A[m * a.sAm + (k0 + k) * a.sAk];
-        }
+        for (int m = 0; m < M; ++m)
+            for (int64_t k = threadIdx.x; k < kc; k += kThreads) xs[m * a.kch + k] = A[m * a.sAm + (k0 + k) * a.sAk];
     }
     __syncthreads();
 
@@ -188,8 +186,7 @@ template <int DT> __device__ __forceinline__ void mma_16816(float (&c)[4], uint3
 // r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
 // k+4..7: slots (2t, 2t+1) <- first pair, slots (2t+8, 2t+9) <- second pair, the same in A and B.
 template <int DT, int KW>
-__global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int64_t xstride,
-                                                                 const int64_t tiles_per_pass) {
+__global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
     constexpr int RW = kWarps / KW;
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem);                      // [M][xstride]
@@ -198,14 +195,23 @@ __global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArg
     const int split = blockIdx.y;
     const int64_t batch = blockIdx.z;
     const int64_t k0 = (int64_t)split * a.kch;
-    const int64_t kc = min(a.kch, a.K - k0);
+    const int kc = (int)min(a.kch, a.K - k0);      // a CTA's K range always fits 32 bits (bounded by shared memory)
     int64_t offA, offB;
     batch_offsets(a, batch, offA, offB);
     {
-        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA;
-        for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
-            int64_t m = idx / kc, k = idx - m * kc;
-            xs[m * xstride + k] = A[m * a.sAm + (k0 + k) * a.sAk];
+        // stage the activation rows: 16-byte copies when the rows are unit-stride and aligned, else element-wise
+        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
+        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
+        if (vec) {
+            const int chunks = kc >> 3;  // kc is a multiple of 8
+            for (int m = 0; m < M; ++m) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
+                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
+                for (int c = threadIdx.x; c < chunks; c += kThreads) dst[c] = src[c];
+            }
+        } else {
+            for (int m = 0; m < M; ++m)
+                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
         }
     }
     __syncthreads();
@@ -213,41 +219,54 @@ __global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArg
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rw = warp / KW, kw = warp % KW;
     const int g = lane >> 2, t = lane & 3;
-    int64_t per = (kc + KW - 1) / KW;
+    int per = (kc + KW - 1) / KW;
     per = (per + 31) / 32 * 32;
-    const int64_t ks = min(kc, (int64_t)kw * per), ke = min(kc, ks + per);
+    const int ks = min(kc, kw * per), ke = min(kc, ks + per);
     const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
-    const uint16_t *xrow = xs + (int64_t)g * xstride;
-    const int64_t num_tiles = (a.N + 15) / 16;
+    const uint16_t *xrow = xs + g * xstride;
+    const bool has_x = g < M;
 
-    for (int64_t pass = 0; pass * tiles_per_pass < num_tiles; ++pass) {
-        const int64_t tile = pass * tiles_per_pass + (int64_t)blockIdx.x * RW + rw;
-        const bool active = tile < num_tiles;
+    // 16-row tiles are dealt out evenly: unit u (a row-warp slot of some CTA) takes tiles [u*T/U, (u+1)*T/U).
+    // Every warp of a CTA runs the same number of rounds (the K-slice reduction below has CTA barriers).
+    const int64_t T = (a.N + 15) / 16;
+    const int64_t U = (int64_t)gridDim.x * RW;
+    const int64_t u = (int64_t)blockIdx.x * RW + rw;
+    const int64_t t_begin = u * T / U, t_end = (u + 1) * T / U;
+    const int64_t rounds = (T + U - 1) / U;
+
+    for (int64_t round = 0; round < rounds; ++round) {
+        const int64_t tile = t_begin + round;
+        const bool active = tile < t_end;
         const int64_t r0 = tile * 16;
         float c[4] = {0.f, 0.f, 0.f, 0.f};
         if (active) {
             const uint16_t *pa = Bbase + min(r0 + g, a.N - 1) * a.ldb;       // clamp: tail rows are loaded twice, stored once
             const uint16_t *pb = Bbase + min(r0 + g + 8, a.N - 1) * a.ldb;
+            // The trip count is the same for all 32 lanes (mma.sync needs the whole warp); a lane whose 8 K values
+            // fall beyond the slice contributes zeros.
 #pragma unroll 4
-            for (int64_t k = ks + t * 8; k < ke; k += 32) {
-                const uint4 wa = ldg_stream(reinterpret_cast<const uint4 *>(pa + k));
-                const uint4 wb = ldg_stream(reinterpret_cast<const uint4 *>(pb + k));
-                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-                if (g < M) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+            for (int kb = ks; kb < ke; kb += 32) {
+                const int k = kb + t * 8;
+                uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa, xv = wa;
+                if (k < ke) {
+                    wa = ldg_stream(reinterpret_cast<const uint4 *>(pa + k));
+                    wb = ldg_stream(reinterpret_cast<const uint4 *>(pb + k));
+                    if (has_x) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+                }
                 mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
                 mma_16816<DT>(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
             }
         }
         if constexpr (KW > 1) {
             // sum the K slices in slice order (reproducible), then the kw == 0 warp stores
-            float *mine = red + ((size_t)kw * RW + rw) * 128 + lane * 4;
+            float *mine = red + (kw * RW + rw) * 128 + lane * 4;
             mine[0] = c[0]; mine[1] = c[1]; mine[2] = c[2]; mine[3] = c[3];
             __syncthreads();
             if (kw == 0) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float s = 0.f;
-                    for (int w = 0; w < KW; ++w) s += red[((size_t)w * RW + rw) * 128 + lane * 4 + i];
+                    for (int w = 0; w < KW; ++w) s += red[(w * RW + rw) * 128 + lane * 4 + i];
                     c[i] = s;
                 }
             }
@@ -284,10 +303,9 @@ __global__ void __launch_bounds__(kThreads) skinny_nm_kernel(const SkinnyArgs a)
     int64_t offA, offB;
     batch_offsets(a, batch, offA, offB);
 
-    for (int64_t idx = threadIdx.x; idx < (int64_t)M * kc; idx += kThreads) {
-        int64_t m = idx / kc, k = idx - m * kc;
-        xs[m * a.kch + k] = load_as_f32<DT>(a.A, offA + m * a.sAm + (k0 + k) * a.sAk);
-    }
+    for (int m = 0; m < M; ++m)
+        for (int64_t k = threadIdx.x; k < kc; k += kThreads)
+            xs[m * a.kch + k] = load_as_f32<DT>(a.A, offA + m * a.sAm + (k0 + k) * a.sAk);
     for (int idx = threadIdx.x; idx < M * CB; idx += kThreads) red[idx] = 0.f;
     __syncthreads();
 
@@ -417,11 +435,15 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
         pl.xstride = (kch + 63) / 64 * 64 + 32;
         pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0);
+        // grid.x: a whole number of CTAs per SM (three if every warp still gets two tiles, else two) so that all
+        // SMs stream the same share; fewer when there are not enough tiles
         const int RW = kWarps / KW;
-        int64_t blocks = (tiles + RW - 1) / RW;
-        int64_t cap = ((int64_t)kNumSMsB200 * 8) / ((int64_t)nsplit * p.batch_total);
-        if (cap < 1) cap = 1;
-        pl.gridx = (unsigned)(blocks < cap ? blocks : cap);
+        const int64_t blocks = (tiles + RW - 1) / RW;
+        const int64_t other = (int64_t)nsplit * p.batch_total;
+        int64_t want = (int64_t)kNumSMsB200 * (tiles >= (int64_t)kNumSMsB200 * 3 * RW * 2 ? 3 : 2);
+        want = (want + other - 1) / other;
+        if (want < 1) want = 1;
+        pl.gridx = (unsigned)(blocks < want ? blocks : want);
         return pl.nsplit <= 65535;
     }
     if (km) {
@@ -492,12 +514,10 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
     int rc = MAGB200_OK;
     if (pl.mma) {
         if constexpr (DT != MAGB200_F32) {
-            const int RW = kWarps / pl.KW;
-            const int64_t tiles_per_pass = (int64_t)pl.gridx * RW;
 #define LAUNCH_KW(KWV)                                                                                   \
     case KWV:                                                                                            \
         if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
-        skinny_km_mma_kernel<DT, KWV><<<grid, kThreads, pl.smem, st>>>(a, M, pl.xstride, tiles_per_pass); \
+        skinny_km_mma_kernel<DT, KWV><<<grid, kThreads, pl.smem, st>>>(a, M, (int)pl.xstride);        \
         break;
             switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
 #undef LAUNCH_KW
