@@ -186,7 +186,7 @@ template <int DT> __device__ __forceinline__ void mma_16816(float (&c)[4], uint3
 // r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
 // k+4..7: slots (2t, 2t+1) <- first pair, slots (2t+8, 2t+9) <- second pair, the same in A and B.
 template <int DT, int KW>
-__global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
+__global__ void __launch_bounds__(kThreads, 3) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
     constexpr int RW = kWarps / KW;
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem);                      // [M][xstride]
@@ -242,11 +242,24 @@ __global__ void __launch_bounds__(kThreads) skinny_km_mma_kernel(const SkinnyArg
         if (active) {
             const uint16_t *pa = Bbase + min(r0 + g, a.N - 1) * a.ldb;       // clamp: tail rows are loaded twice, stored once
             const uint16_t *pb = Bbase + min(r0 + g + 8, a.N - 1) * a.ldb;
-            // The trip count is the same for all 32 lanes (mma.sync needs the whole warp); a lane whose 8 K values
-            // fall beyond the slice contributes zeros.
+            // The trip count is the same for all 32 lanes (mma.sync needs the whole warp). Full 32-wide K chunks run
+            // without predicates so the compiler can keep eight 16-byte loads in flight per lane; the ragged last
+            // chunk (K slice not a multiple of 32) is one predicated step in which out-of-range lanes feed zeros.
+            const uint4 *pa4 = reinterpret_cast<const uint4 *>(pa + ks) + t;
+            const uint4 *pb4 = reinterpret_cast<const uint4 *>(pb + ks) + t;
+            const uint4 *px4 = reinterpret_cast<const uint4 *>(xrow + ks) + t;
+            const int nfull = (ke - ks) >> 5;
 #pragma unroll 4
-            for (int kb = ks; kb < ke; kb += 32) {
-                const int k = kb + t * 8;
+            for (int i = 0; i < nfull; ++i) {
+                const uint4 wa = ldg_stream(pa4 + 4 * i);
+                const uint4 wb = ldg_stream(pb4 + 4 * i);
+                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                if (has_x) xv = px4[4 * i];
+                mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+                mma_16816<DT>(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+            }
+            if ((ke - ks) & 31) {
+                const int k = ks + (nfull << 5) + t * 8;
                 uint4 wa = make_uint4(0u, 0u, 0u, 0u), wb = wa, xv = wa;
                 if (k < ke) {
                     wa = ldg_stream(reinterpret_cast<const uint4 *>(pa + k));
@@ -435,12 +448,11 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
         pl.xstride = (kch + 63) / 64 * 64 + 32;
         pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0);
-        // grid.x: a whole number of CTAs per SM (three if every warp still gets two tiles, else two) so that all
-        // SMs stream the same share; fewer when there are not enough tiles
         const int RW = kWarps / KW;
         const int64_t blocks = (tiles + RW - 1) / RW;
         const int64_t other = (int64_t)nsplit * p.batch_total;
-        int64_t want = (int64_t)kNumSMsB200 * (tiles >= (int64_t)kNumSMsB200 * 3 * RW * 2 ? 3 : 2);
+        // many short CTAs (one or two tiles per warp) let the hardware scheduler even out the SMs
+        int64_t want = (int64_t)kNumSMsB200 * 32;
         want = (want + other - 1) / other;
         if (want < 1) want = 1;
         pl.gridx = (unsigned)(blocks < want ? blocks : want);

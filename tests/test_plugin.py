@@ -24,9 +24,10 @@ def deploy_dir():
     """A directory laid out like an installed magnetron: core + cpu module + our cuda module side by side
     (the loader looks for libmagnetron_<id>.so next to libmagnetron_core.so, magnetron/core/mag_backend.c:209-220)."""
     d = tempfile.mkdtemp(prefix="magdeploy_")
+    # real copies, not symlinks: the core resolves its own real path to find its modules (magnetron/core/mag_os.c:32-54)
     for name in ("libmagnetron_core.so", "libmagnetron_cpu.so"):
-        os.symlink(os.path.join(R.REF_DIR, name), os.path.join(d, name))
-    os.symlink(PLUGIN, os.path.join(d, "libmagnetron_cuda.so"))
+        shutil.copy2(os.path.join(R.REF_DIR, name), os.path.join(d, name))
+    shutil.copy2(PLUGIN, os.path.join(d, "libmagnetron_cuda.so"))
     yield d
     shutil.rmtree(d, ignore_errors=True)
 
@@ -67,7 +68,7 @@ class CudaApi(R.MagApi):
     """The same driver on "cuda:0", with data movement through the module's additive exports."""
 
     def __init__(self, deploy_dir):
-        super().__init__("cuda:0", lib_dir=deploy_dir, log_level=1)
+        super().__init__("cuda:0", lib_dir=deploy_dir, log_level=int(os.environ.get("MAG_TEST_LOG_LEVEL", "1")))
         self.mod = plugin_handle(deploy_dir)
         self.mod.mag_b200_upload.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
         self.mod.mag_b200_download.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
