@@ -126,6 +126,18 @@ void     magb200_launch_count_reset(void);
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
 
+/* Decode-shaped matmul (M <= 8) that allocates nothing, for callers that are not allowed to call
+ * cudaMalloc (a plug-in inside another framework's stream-ordered region, a serving loop that must not touch
+ * the allocator once warm). No counterpart in the reference: its CPU backend takes split buffers from a
+ * thread-local arena. Same operands and result as magb200_matmul; launches on `cuda_stream` (a
+ * cudaStream_t; NULL = the default stream) and returns without synchronising. The split-K partial sums go
+ * to a 4 MiB array built into the library (held by every GPU that loads it): problems whose partials
+ * (splits x batch x M x N floats) exceed it fail with MAGB200_ERR_TOO_LARGE. The first call on a device
+ * resolves the array's address and should be made before any stream capture. All calls share the array;
+ * calls whose kernels overlap on the GPU race, so keep them on one stream. */
+int  magb200_matmul_skinny_noalloc(int device, void *cuda_stream, const magb200_view_t *x, const magb200_view_t *y,
+                                   const magb200_view_t *r);
+
 /* ---- host-buffer convenience: one call = upload operands, matmul, download result ------------
  * This is the call a CPU-side user of the reference makes (operands and result in host memory,
  * magnetron/core/mag_op_stubs.c:1249); the views' `base` fields are HOST addresses here. Synchronous. */

@@ -267,6 +267,17 @@ static int build_problem(const magb200_view_t *x, const magb200_view_t *y, const
     return MAGB200_OK;
 }
 
+// Host-only canonicalisation for entry points that bring their own stream and scratch: same validation and
+// folding as magb200_matmul, no device state touched. Problems that keep more than three batch dims are refused.
+int canonicalize_skinny_problem(const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r, GemmProblem *out) {
+    FullProblem fp;
+    int rc = build_problem(x, y, r, fp);
+    if (rc) return rc;
+    if (fp.n_outer != 0) { set_error("matmul: more than three independent batch dims are not supported by this entry point"); return MAGB200_ERR_INVALID_ARG; }
+    *out = fp.g;
+    return MAGB200_OK;
+}
+
 static int route(const GemmProblem &g, int forced, int *kernel) {
     const bool sk = g.M <= 8 && skinny_supported(g);
     const bool tc = tcgen05_supported(g);
