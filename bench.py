@@ -350,13 +350,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-decode", action="store_true", help="only the headline prefill step (used under ncu)")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--workload", default="auto", choices=["auto", "prefill", "tp"],
+                    help="auto: Qwen3-8B prefill layer on one GPU, Qwen3-32B tensor-parallel layer on several")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     pk = peaks()
 
-    if args.gpus > 1 or world > 1:
+    if args.gpus > 1 or world > 1 or args.workload == "tp":
         from magnetron_b200 import tp_bench
         return tp_bench.main(args, pk)
 

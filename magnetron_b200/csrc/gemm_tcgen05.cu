@@ -127,6 +127,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Tile order: tiles are walked in groups of kGroupM tile rows, column by column inside a group, so the CTAs that run
+// at the same time share a few A row panels and a band of B column panels that together fit in L2 (walking N fastest over
+// a wide N would stream all of B once per wave).
+constexpr int kGroupM = 8;
+__device__ __forceinline__ void decode_tile(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t &batch, int64_t &tm, int64_t &tn) {
+    const int64_t per_batch = tiles_m * tiles_n;
+    batch = tile / per_batch;
+    const int64_t t = tile - batch * per_batch;
+    const int64_t per_group = (int64_t)kGroupM * tiles_n;
+    const int64_t group = t / per_group;
+    const int64_t first_m = group * kGroupM;
+    const int64_t rows = (tiles_m - first_m) < kGroupM ? (tiles_m - first_m) : kGroupM;
+    const int64_t local = t - group * per_group;
+    tn = local / rows;
+    tm = first_m + (local - tn * rows);
+}
+
 template <int BN> struct Cfg {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
@@ -174,8 +191,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t tiles_per_batch = args.tiles_m * args.tiles_n;
-
     if (warp == 0) {
         // ===================== TMA producer (one thread) =====================
         if (lane == 0) {
@@ -183,9 +198,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x) {
-                const int64_t batch = tile / tiles_per_batch;
-                const int64_t trem = tile - batch * tiles_per_batch;
-                const int64_t tm = trem / args.tiles_n, tn = trem - tm * args.tiles_n;
+                int64_t batch, tm, tn;
+                decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
                 const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
                 int bc[kMaxBatchDims] = {0, 0, 0};
                 {
@@ -270,9 +284,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
         for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
             const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
-            const int64_t batch = tile / tiles_per_batch;
-            const int64_t trem = tile - batch * tiles_per_batch;
-            const int64_t tm = trem / args.tiles_n, tn = trem - tm * args.tiles_n;
+            int64_t batch, tm, tn;
+            decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
             const int64_t row = tm * BM + quarter * 32 + lane;
             const int64_t n0 = tn * BN;
             // every lane waits (each needs the acquire), then the warp agrees on one outcome so that the
@@ -425,13 +438,23 @@ bool describe(const GemmProblem &p, bool is_a, int BN, OperandDesc &o, int &mn_m
 }
 
 int pick_bn(const GemmProblem &p) {
-    // Largest tile that still gives every SM work; small outputs take narrower tiles.
+    // Estimated time = waves x cost of one tile. A 128x256 tile is the efficient one (the narrower tiles read as many
+    // bytes of A per MMA but produce half / a quarter of the output, so they run into shared-memory and L2 bandwidth);
+    // narrower tiles only win when they save whole waves on a small output.
     const int64_t tm = (p.M + BM - 1) / BM;
-    for (int bn : {256, 128}) {
-        if (p.N >= bn && tm * ((p.N + bn - 1) / bn) * p.batch_total >= kNumSMsB200) return bn;
+    int best = 256;
+    double best_cost = 1e300;
+    const int cand[3] = {256, 128, 64};
+    const double tile_cost[3] = {1.0, 0.62, 0.40};
+    for (int i = 0; i < 3; ++i) {
+        const int bn = cand[i];
+        if (bn > 64 && p.N <= bn / 2) continue;  // more than half of the tile would be padding
+        const int64_t tiles = tm * ((p.N + bn - 1) / bn) * p.batch_total;
+        const double waves = (double)((tiles + kNumSMsB200 - 1) / kNumSMsB200);
+        const double cost = waves * tile_cost[i];
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
     }
-    if (p.N > 128) return 128;  // few tiles either way: prefer fewer TMEM columns / more stages
-    return p.N > 64 ? 128 : 64;
+    return best;
 }
 
 template <int BN, int DT>

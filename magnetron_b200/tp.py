@@ -1,0 +1,159 @@
+"""Tensor-parallel linear layers over the GPUs of one box: one process per GPU, NCCL through torch.distributed.
+
+magnetron has no multi-device code (its README lists multi-GPU as future work); this module is the new host
+logic around the unchanged single-GPU matmul. The path shards in two ways:
+
+  column sharding (on N)  each rank holds rows [n0, n1) of a row-major [N, K] weight and computes
+                          y[:, n0:n1] = x @ W[n0:n1].T  -- independent GEMMs, no exchange; an all-gather only if
+                          the caller wants the full output on every rank;
+  row sharding (on K)     each rank holds columns [k0, k1) of the weight and the matching slice of the input,
+                          computes a partial y over its K range, and one all-reduce (sum) makes the result.
+
+Paired the Megatron way (column-sharded QKV / gate+up feed row-sharded o / down) a transformer layer needs two
+all-reduces and no gather. To hide them, the row-sharded GEMM is cut into chunks of M and each chunk's all-reduce is
+issued asynchronously while the next chunk multiplies.
+
+Device memory is held in torch tensors (so NCCL can see it); the matmuls go through the C ABI of this package on
+torch's current stream. There is no CPU path: `TPLayer` raises without the CUDA library. The `matmul` argument
+exists so that the collective plumbing can be exercised on CPU ranks (gloo) with a stand-in product.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class ShardedLinear:
+    name: str
+    n: int            # out features of the full weight
+    k: int            # in features of the full weight
+    kind: str         # "col": shard N, "row": shard K
+    granule: int = 128  # shard boundaries fall on multiples of this (head_dim keeps heads whole)
+
+
+# One Qwen3-32B layer: hidden 5120, 64 query heads + 8 KV heads of head_dim 128, intermediate 25600
+QWEN3_32B_LAYER = (
+    ShardedLinear("qkv", (64 + 8 + 8) * 128, 5120, "col"),
+    ShardedLinear("o", 5120, 64 * 128, "row"),
+    ShardedLinear("gate_up", 2 * 25600, 5120, "col"),
+    ShardedLinear("down", 5120, 25600, "row"),
+)
+
+
+def shard_range(total: int, world: int, rank: int, granule: int = 1) -> tuple[int, int]:
+    """[lo, hi) of `total` owned by `rank`: units of `granule` dealt out as evenly as possible, the first
+    `units % world` ranks taking one more."""
+    if total % granule:
+        raise ValueError(f"{total} is not a multiple of the shard granule {granule}")
+    units = total // granule
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    return lo * granule, hi * granule
+
+
+def local_shape(spec: ShardedLinear, world: int, rank: int) -> tuple[int, int]:
+    """(N_local, K_local) of the weight shard a rank holds."""
+    if spec.kind == "col":
+        lo, hi = shard_range(spec.n, world, rank, spec.granule)
+        return hi - lo, spec.k
+    lo, hi = shard_range(spec.k, world, rank, spec.granule)
+    return spec.n, hi - lo
+
+
+def layer_flops(specs: Sequence[ShardedLinear], m: int) -> float:
+    return sum(2.0 * m * s.n * s.k for s in specs)
+
+
+def cabi_matmul(device: int) -> Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]:
+    """out[M,N] = x[M,K] @ w[N,K].T on `device` through magb200_matmul, on torch's current stream."""
+    import magnetron_b200 as mb
+    L = mb.lib()
+    mb.check(L.magb200_device_init(device))
+    mb.check(L.magb200_set_stream(device, C.c_void_p(torch.cuda.current_stream(device).cuda_stream)))
+    dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16, torch.float32: mb.FLOAT32}
+
+    def view(t: torch.Tensor, shape=None, strides=None):
+        return mb.make_view(t.data_ptr(), dt[t.dtype], shape or tuple(t.shape), strides or tuple(t.stride()))
+
+    def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        n, k = w.shape
+        wt = view(w, (k, n), (w.stride(1), w.stride(0)))      # the W.T view: no copy
+        mb.check(L.magb200_matmul(device, C.byref(view(x)), C.byref(wt), C.byref(view(out))))
+
+    return matmul
+
+
+class TPLayer:
+    """The sharded linears of one layer on this rank, with resident weight shards and preallocated outputs."""
+
+    def __init__(self, specs: Sequence[ShardedLinear], m: int, *, device: torch.device, dtype=torch.bfloat16,
+                 matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4):
+        self.specs, self.m, self.group = tuple(specs), m, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if matmul is None:
+            if device.type != "cuda":
+                raise RuntimeError("TPLayer runs on CUDA devices only: there is no CPU path")
+            matmul = cabi_matmul(device.index or 0)
+        self.matmul = matmul
+        self.chunks = max(1, min(chunks, m // 512)) if m >= 1024 else 1
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.w, self.x, self.y = {}, {}, {}
+        for s in self.specs:
+            n_loc, k_loc = local_shape(s, self.world, self.rank)
+            # the full weight is drawn from one seeded stream and sliced, so every world size multiplies the
+            # same matrix; only the local shard is kept on the device
+            full = torch.randn((s.n, s.k), generator=gen, dtype=torch.float32) * 0.02 if s.n * s.k <= (1 << 27) else None
+            if full is not None:
+                if s.kind == "col":
+                    lo, hi = shard_range(s.n, self.world, self.rank, s.granule)
+                    shard = full[lo:hi]
+                else:
+                    lo, hi = shard_range(s.k, self.world, self.rank, s.granule)
+                    shard = full[:, lo:hi]
+                self.w[s.name] = shard.to(dtype).contiguous().to(device)
+            else:  # too large to materialise on the host in one piece: seeded per shard
+                g2 = torch.Generator(device="cpu").manual_seed(seed * 1000 + self.rank)
+                self.w[s.name] = (torch.randn((n_loc, k_loc), generator=g2, dtype=torch.float32) * 0.02).to(dtype).to(device)
+            xin = torch.randn((m, k_loc), generator=torch.Generator(device="cpu").manual_seed(seed + 17), dtype=torch.float32)
+            self.x[s.name] = xin.to(dtype).to(device)
+            self.y[s.name] = torch.empty((m, n_loc), dtype=dtype, device=device)
+
+    # -- one linear ---------------------------------------------------------------------------
+    def column(self, name: str, gather: bool = False):
+        self.matmul(self.x[name], self.w[name], self.y[name])
+        if gather and self.world > 1:
+            parts = [torch.empty_like(self.y[name]) for _ in range(self.world)]
+            dist.all_gather(parts, self.y[name], group=self.group)
+            return parts
+        return self.y[name]
+
+    def row(self, name: str):
+        """Partial product over this rank's K range, then a sum all-reduce; cut into chunks of M so that the
+        all-reduce of chunk i runs while chunk i+1 multiplies."""
+        x, w, y = self.x[name], self.w[name], self.y[name]
+        if self.world == 1:
+            self.matmul(x, w, y)
+            return y
+        works = []
+        step = (self.m + self.chunks - 1) // self.chunks
+        for lo in range(0, self.m, step):
+            hi = min(self.m, lo + step)
+            self.matmul(x[lo:hi], w, y[lo:hi])
+            works.append(dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        for wk in works:
+            wk.wait()
+        return y
+
+    def step(self, gather_outputs: bool = False) -> None:
+        for s in self.specs:
+            if s.kind == "col":
+                self.column(s.name, gather=gather_outputs)
+            else:
+                self.row(s.name)

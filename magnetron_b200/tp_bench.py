@@ -1,0 +1,99 @@
+"""Multi-GPU leg of bench.py: the sharded GEMMs of one Qwen3-32B layer, one rank per GPU (torchrun).
+
+`value` = whole-job TFLOP/s of the layer (7.99 TFLOP at M = 8192) with column-sharded QKV and gate/up, row-sharded o
+and down, and the two all-reduces of the paired schedule inside the timed region; time is the maximum over ranks of
+CUDA-event time. The same line reports the variant that also all-gathers the column-sharded outputs, the token sweep
+M in {1, 8, 512}. `bench.py --gpus 1 --workload tp` runs the same layer unsharded as the scaling yardstick.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from magnetron_b200 import tp
+
+
+def _time_steps(fn, steps, warmup, device):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    ms = torch.tensor([a.elapsed_time(b)], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def main(args, pk):
+    import magnetron_b200 as mb
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            import bench
+            r = bench.cpu_reference(max(1, min(args.steps, 40)), min(args.warmup, 2))
+            line = {"impl": "reference", "metric": "bf16 matmul TFLOP/s", "value": r["value"] if r else None, "unit": "TFLOP/s",
+                    "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_pass"] if r else None,
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {"workload": "qwen3-32b-tp layer GEMMs; CPU sample = bounded Qwen3-8B-shaped GEMMs (see cpu_baseline.sample)"},
+                    "cpu_baseline": r, "e2e": {"value": r["value"] if r else None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            print(json.dumps(line if r else {"impl": "reference", "unavailable": "oracle/_ref is not built on this machine"}))
+        return
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if not dist.is_initialized():
+        for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29517"), ("RANK", "0"), ("WORLD_SIZE", "1")):
+            os.environ.setdefault(k, v)
+        dist.init_process_group("nccl", device_id=device)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    M = 8192
+    specs = tp.QWEN3_32B_LAYER
+    flops = tp.layer_flops(specs, M)
+    layer = tp.TPLayer(specs, M, device=device)
+    mb.lib().magb200_launch_count_reset()
+    ms = _time_steps(lambda: layer.step(False), steps, warmup, device)
+    launches = int(mb.lib().magb200_launch_count()) * steps // (steps + warmup)
+    ms_gather = _time_steps(lambda: layer.step(True), max(2, steps // 2), 2, device)
+    value = flops * steps / ms / 1e9
+    sweep = {}
+    del layer
+    torch.cuda.empty_cache()
+    for m in (1, 8, 512):
+        lay = tp.TPLayer(specs, m, device=device)
+        t = _time_steps(lambda: lay.step(False), max(steps, 20), warmup, device)
+        wbytes = sum(2 * s.n * s.k for s in specs)
+        sweep[f"M{m}"] = {"ms_per_step": t / max(steps, 20), "tflops": tp.layer_flops(specs, m) * max(steps, 20) / t / 1e9,
+                          "weight_gbs_all_gpus": wbytes * max(steps, 20) / t / 1e6}
+        del lay
+        torch.cuda.empty_cache()
+    dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": "bf16 matmul TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "qwen3-32b-tp: QKV [10240x5120] and gate/up [51200x5120] column-sharded on N, o [5120x8192] and "
+                                   "down [5120x25600] row-sharded on K with an NCCL all-reduce (paired schedule, all-reduce chunked over M "
+                                   "and overlapped), M=8192, seed 5", "parallelism": f"tp{world}",
+                       "l2": "inputs larger than L2 (975 MB of weights per layer across ranks)"},
+            "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "host-buffer end-to-end is measured on the 1-GPU line; the sharded layer keeps activations on the device"},
+            "gpu_launches": launches,
+            "with_output_allgather": {"ms_per_step": ms_gather / max(2, steps // 2), "tflops": flops * max(2, steps // 2) / ms_gather / 1e9},
+            "token_sweep": sweep,
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": pk["tensor_burst"], "unit": "TFLOP/s per GPU",
+                         "frac": value / world / pk["tensor_burst"], "traffic": None, "peak_source": pk["source"] + " burst cuBLAS bf16"},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,94 @@
+"""Host-side logic of the tensor-parallel layer on CPU: shard planner, and world_size-2 gloo ranks that run the
+column / row sharded schedule with a stand-in local product and must reproduce the unsharded result."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from magnetron_b200 import tp
+
+
+def test_shard_ranges_cover_and_respect_granule():
+    for total, world, g in [(10240, 8, 128), (51200, 4, 128), (8192, 8, 128), (25600, 8, 128), (5120, 3, 128), (640, 8, 128)]:
+        pieces = [tp.shard_range(total, world, r, g) for r in range(world)]
+        assert pieces[0][0] == 0 and pieces[-1][1] == total
+        for (a, b), (c, d) in zip(pieces, pieces[1:]):
+            assert b == c and a % g == 0 and b % g == 0
+        sizes = [b - a for a, b in pieces]
+        assert max(sizes) - min(sizes) <= g
+    with pytest.raises(ValueError):
+        tp.shard_range(1000, 4, 0, 128)
+
+
+def test_layer_flops_and_local_shapes():
+    assert tp.layer_flops(tp.QWEN3_32B_LAYER, 8192) == pytest.approx(2 * 8192 * 4.8758e8, rel=1e-3)
+    qkv, o, gu, down = tp.QWEN3_32B_LAYER
+    assert tp.local_shape(qkv, 8, 0) == (1280, 5120) and tp.local_shape(o, 8, 3) == (5120, 1024)
+    assert tp.local_shape(gu, 4, 1) == (12800, 5120) and tp.local_shape(down, 8, 7) == (5120, 3200)
+
+
+def test_no_cpu_path():
+    with pytest.raises(RuntimeError):
+        tp.TPLayer(tp.QWEN3_32B_LAYER[:1], 8, device=torch.device("cpu"))
+
+
+SMALL = (tp.ShardedLinear("qkv", 256, 64, "col", 32), tp.ShardedLinear("o", 64, 128, "row", 32),
+         tp.ShardedLinear("gate_up", 512, 64, "col", 32), tp.ShardedLinear("down", 64, 256, "row", 32))
+
+
+def _standin(x, w, out):
+    out.copy_((x.float() @ w.float().T).to(out.dtype))
+
+
+def _rank_main(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m = 1024   # large enough for the chunked, overlapped all-reduce path (2 chunks)
+        layer = tp.TPLayer(SMALL, m, device=torch.device("cpu"), dtype=torch.float32, matmul=_standin)
+        assert layer.chunks == 2
+        layer.step(False)
+        out = {}
+        for s in SMALL:
+            if s.kind == "col":
+                parts = layer.column(s.name, gather=True)
+                out[s.name] = torch.cat(parts, dim=1)
+            else:
+                out[s.name] = layer.y[s.name].clone()
+        # gather every rank's input slice so rank 0 can form the unsharded product
+        xs = {}
+        for s in SMALL:
+            if s.kind == "row":
+                parts = [torch.empty_like(layer.x[s.name]) for _ in range(world)]
+                dist.all_gather(parts, layer.x[s.name])
+                xs[s.name] = torch.cat(parts, dim=1)
+            else:
+                xs[s.name] = layer.x[s.name]
+        if rank == 0:
+            gen = torch.Generator(device="cpu").manual_seed(5)
+            ok = True
+            for s in SMALL:
+                full = torch.randn((s.n, s.k), generator=gen, dtype=torch.float32) * 0.02
+                want = xs[s.name] @ full.T
+                ok &= bool(torch.allclose(out[s.name], want, atol=1e-4, rtol=1e-4))
+            ret.put(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_layer():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert ret.get(timeout=5) is True
