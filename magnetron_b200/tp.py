@@ -75,7 +75,11 @@ def cabi_matmul(device: int) -> Callable[[torch.Tensor, torch.Tensor, torch.Tens
     import magnetron_b200 as mb
     L = mb.lib()
     mb.check(L.magb200_device_init(device))
-    mb.check(L.magb200_set_stream(device, C.c_void_p(torch.cuda.current_stream(device).cuda_stream)))
+    handle = torch.cuda.current_stream(device).cuda_stream
+    if not handle:
+        raise RuntimeError("make a torch.cuda.Stream current first: the default stream has a null handle, which the C ABI "
+                           "reads as 'use the library's own stream', and matmuls would then not be ordered with the collectives")
+    mb.check(L.magb200_set_stream(device, C.c_void_p(handle)))
     dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16, torch.float32: mb.FLOAT32}
 
     def view(t: torch.Tensor, shape=None, strides=None):

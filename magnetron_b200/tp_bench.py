@@ -49,8 +49,13 @@ def main(args, pk):
                     "cpu_baseline": r, "e2e": {"value": r["value"] if r else None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
             print(json.dumps(line if r else {"impl": "reference", "unavailable": "oracle/_ref is not built on this machine"}))
         return
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and not os.environ.get("MAGB200_KEEP_NCCL_DEBUG"):
+        os.environ["NCCL_DEBUG"] = "WARN"      # NCCL's banner goes to stdout and would sit in front of the JSON line
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    # a dedicated stream: the C ABI treats a null handle (torch's default stream) as "use the library's own stream",
+    # and the timing events, the matmuls and the collectives must all be ordered on one stream
+    torch.cuda.set_stream(torch.cuda.Stream(device))
     if not dist.is_initialized():
         for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29517"), ("RANK", "0"), ("WORLD_SIZE", "1")):
             os.environ.setdefault(k, v)
