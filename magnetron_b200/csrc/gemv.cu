@@ -298,6 +298,111 @@ __global__ void __launch_bounds__(kThreads, 3) skinny_km_mma_kernel(const Skinny
 }
 
 // ------------------------------------------------------------------------------------------------
+// K-major 16-bit weights, cp.async-pipelined: grid = (persistent CTAs, nsplit, batch)
+// ------------------------------------------------------------------------------------------------
+// Same fragment scheme as skinny_km_mma_kernel, for problems with plenty of 16-row tiles. The 128-bit weight loads
+// do not go to registers: each lane keeps a private ring of kAsyncDepth steps (two 16-byte cp.async copies per step)
+// in shared memory, so 16 loads per lane -- 8 KB per warp -- are in flight without costing registers, and the ring
+// runs on across tile boundaries (the sequence of (tile, K step) pairs of a warp is flattened), so there is no drain
+// between tiles. Slots are private to a lane: cp.async.wait_group is all the synchronisation the ring needs.
+constexpr int kAsyncDepth = 8;
+constexpr size_t kAsyncRingBytes = (size_t)kAsyncDepth * 2 * kThreads * 16;   // 64 KB
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const SkinnyArgs a, const int M, const int xstride) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(smem);                                  // [depth][2][256 lanes]
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kAsyncRingBytes);            // [M][xstride]
+
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int kc = (int)min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+    {
+        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
+        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
+        for (int m = 0; m < M; ++m) {
+            if (vec) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
+                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
+                for (int c = threadIdx.x; c < (kc >> 3); c += kThreads) dst[c] = src[c];
+            } else {
+                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
+            }
+        }
+    }
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t T = (a.N + 15) / 16;
+    const int64_t W = (int64_t)gridDim.x * kWarps;
+    const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t t_begin = w * T / W, t_end = (w + 1) * T / W;      // a contiguous, even share of the tiles
+    const int nk = (kc + 31) >> 5;                                     // 32-wide K steps per tile
+    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
+    const uint16_t *xrow = xs + g * xstride;
+    const bool has_x = g < M;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + (uint32_t)threadIdx.x * 16u;
+
+    // issue cursor (tile, K step, ring slot), advanced incrementally: no divisions in the steady state
+    int64_t i_tile = t_begin;
+    int i_ks = 0, i_slot = 0;
+    const uint16_t *pa = Bbase + min(i_tile * 16 + g, a.N - 1) * a.ldb;     // clamp: tail rows are loaded twice, stored once
+    const uint16_t *pb = Bbase + min(i_tile * 16 + g + 8, a.N - 1) * a.ldb;
+    auto issue = [&]() {
+        if (i_tile < t_end) {
+            const int k = i_ks * 32 + t * 8;
+            const uint32_t nbytes = (k < kc) ? 16u : 0u;               // beyond the K range: zero-fill, nothing is read
+            const int kk = (k < kc) ? k : 0;
+            const uint32_t dst = ring_u32 + (uint32_t)i_slot * (2u * kThreads * 16u);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(pa + kk), "r"(nbytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + kThreads * 16u), "l"(pb + kk), "r"(nbytes) : "memory");
+            if (++i_ks == nk) {
+                i_ks = 0;
+                ++i_tile;
+                pa = Bbase + min(i_tile * 16 + g, a.N - 1) * a.ldb;
+                pb = Bbase + min(i_tile * 16 + g + 8, a.N - 1) * a.ldb;
+            }
+        }
+        i_slot = (i_slot + 1) & (kAsyncDepth - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");          // one group per step, empty past the end
+    };
+
+    for (int q = 0; q < kAsyncDepth; ++q) issue();
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    int c_ks = 0, c_slot = 0;
+    for (int64_t tile = t_begin; tile < t_end;) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kAsyncDepth - 1) : "memory");
+        const uint4 *slot = ring + (size_t)c_slot * 2 * kThreads + threadIdx.x;
+        const uint4 wa = slot[0];
+        const uint4 wb = slot[kThreads];
+        const int k = c_ks * 32 + t * 8;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (has_x && k < kc) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+        mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+        mma_16816<DT>(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+        c_slot = (c_slot + 1) & (kAsyncDepth - 1);
+        issue();
+        if (++c_ks == nk) {
+            const int64_t r0 = tile * 16;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t n = r0 + g + (i >> 1) * 8;
+                const int m = 2 * t + (i & 1);
+                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i]);
+                c[i] = 0.f;
+            }
+            c_ks = 0;
+            ++tile;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------------
 // N-major weights: grid = (column blocks, nsplit, batch); a CTA covers 32*V columns
 // ------------------------------------------------------------------------------------------------
 template <int DT, int M>
@@ -397,6 +502,7 @@ constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
 struct Plan {
     bool km;       // K-major weights
     bool mma;      // K-major 16-bit weights through mma.sync
+    bool async;    // ... with the cp.async ring (plenty of tiles)
     int KW;        // warps along K per CTA (mma)
     int64_t xstride;
     int R;         // rows per warp (km)
@@ -420,6 +526,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         if (p.bsB[d] % V) return false;  // every batch slice of B must stay 16-byte aligned
     pl.km = km;
     pl.mma = false;
+    pl.async = false;
     if (km && DT != MAGB200_F32) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
         // activation rows live in shared memory with a pitch of 64 bytes mod 128 so that the 8 row groups
@@ -443,10 +550,23 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             kch = (kch + 255) / 256 * 256;
             nsplit = (int)((p.K + kch - 1) / kch);
         }
+        if (tiles * nsplit * p.batch_total >= warps_wanted / 2) {
+            // enough tiles for every warp of a persistent grid to stream several: the cp.async-pipelined kernel
+            pl.mma = true; pl.async = true; pl.KW = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
+            pl.xstride = (kch + 63) / 64 * 64 + 32;
+            pl.smem = kAsyncRingBytes + (size_t)M * pl.xstride * 2;
+            const int64_t other = (int64_t)nsplit * p.batch_total;
+            const int per_sm = pl.smem <= 110 * 1024 ? 2 : 1;
+            int64_t want = ((int64_t)kNumSMsB200 * per_sm + other - 1) / other;
+            if (want < 1) want = 1;
+            pl.gridx = (unsigned)want;
+            return pl.nsplit <= 65535;
+        }
         int KW = 1;
         while (KW < kWarps && tiles * KW * nsplit * p.batch_total < warps_wanted && kch / (KW * 2) >= 128) KW *= 2;
         pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
         pl.xstride = (kch + 63) / 64 * 64 + 32;
+
         pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0);
         const int RW = kWarps / KW;
         const int64_t blocks = (tiles + RW - 1) / RW;
@@ -524,7 +644,12 @@ template <int DT, int M>
 int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStream_t st) {
     dim3 grid(pl.gridx, pl.nsplit, (unsigned)p.batch_total);
     int rc = MAGB200_OK;
-    if (pl.mma) {
+    if (pl.async) {
+        if constexpr (DT != MAGB200_F32) {
+            if ((rc = set_smem(skinny_km_async_kernel<DT>, pl.smem))) return rc;
+            skinny_km_async_kernel<DT><<<grid, kThreads, pl.smem, st>>>(a, M, (int)pl.xstride);
+        }
+    } else if (pl.mma) {
         if constexpr (DT != MAGB200_F32) {
 #define LAUNCH_KW(KWV)                                                                                   \
     case KWV:                                                                                            \

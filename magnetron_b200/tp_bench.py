@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -49,8 +50,11 @@ def main(args, pk):
                     "cpu_baseline": r, "e2e": {"value": r["value"] if r else None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
             print(json.dumps(line if r else {"impl": "reference", "unavailable": "oracle/_ref is not built on this machine"}))
         return
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and not os.environ.get("MAGB200_KEEP_NCCL_DEBUG"):
-        os.environ["NCCL_DEBUG"] = "WARN"      # NCCL's banner goes to stdout and would sit in front of the JSON line
+    # NCCL prints its version banner on stdout at communicator start-up; stdout must carry the JSON line only, so it is
+    # pointed at stderr until the result is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     # a dedicated stream: the C ABI treats a null handle (torch's default stream) as "use the library's own stream",
@@ -99,6 +103,9 @@ def main(args, pk):
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": pk["tensor_burst"], "unit": "TFLOP/s per GPU",
                          "frac": value / world / pk["tensor_burst"], "traffic": None, "peak_source": pk["source"] + " burst cuBLAS bf16"},
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     dist.barrier()
     dist.destroy_process_group()
