@@ -62,7 +62,8 @@ typedef enum magb200_kernel_t {
     MAGB200_KERNEL_TCGEN05  = 1,  /* TMA-fed tcgen05.mma tiles, fp32 accumulators in TMEM               */
     MAGB200_KERNEL_SKINNY   = 2,  /* M <= 8 weight-streaming kernel (HBM bound)                          */
     MAGB200_KERNEL_SIMT     = 3,  /* exact-fp32 / arbitrary-stride tiled FFMA kernel                     */
-    MAGB200_KERNEL_SKINNY_SPLITK = 4 /* M <= 8, K split across CTAs with an fp32 scratch reduction       */
+    MAGB200_KERNEL_SKINNY_SPLITK = 4, /* M <= 8, K split across CTAs with an fp32 scratch reduction      */
+    MAGB200_KERNEL_TCGEN05_2SM = 5   /* 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2)           */
 } magb200_kernel_t;
 
 /* ---- library / device ------------------------------------------------------------------------ */

@@ -22,7 +22,7 @@ FLOAT32, FLOAT16, BFLOAT16 = 0, 1, 2          # mag_dtype_t values (include/magn
 DTYPE_SIZE = {FLOAT32: 4, FLOAT16: 2, BFLOAT16: 2}
 BITS_DTYPE = {FLOAT32: np.uint32, FLOAT16: np.uint16, BFLOAT16: np.uint16}
 MAX_DIMS = 16
-KERNEL_NAMES = {0: "none", 1: "tcgen05", 2: "skinny", 3: "simt", 4: "skinny_splitk"}
+KERNEL_NAMES = {0: "none", 1: "tcgen05", 2: "skinny", 3: "simt", 4: "skinny_splitk", 5: "tcgen05_2sm"}
 KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items()}
 
 _PKG = os.path.dirname(os.path.abspath(__file__))

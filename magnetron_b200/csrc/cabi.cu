@@ -281,11 +281,13 @@ int canonicalize_skinny_problem(const magb200_view_t *x, const magb200_view_t *y
 static int route(const GemmProblem &g, int forced, int *kernel) {
     const bool sk = g.M <= 8 && skinny_supported(g);
     const bool tc = tcgen05_supported(g);
-    int k = sk ? MAGB200_KERNEL_SKINNY : (tc ? MAGB200_KERNEL_TCGEN05 : MAGB200_KERNEL_SIMT);
+    int k = sk ? MAGB200_KERNEL_SKINNY
+               : (tc ? (tcgen05_2sm_preferred(g) ? MAGB200_KERNEL_TCGEN05_2SM : MAGB200_KERNEL_TCGEN05) : MAGB200_KERNEL_SIMT);
     if (forced) {
         if (forced == MAGB200_KERNEL_SKINNY_SPLITK) forced = MAGB200_KERNEL_SKINNY;
-        if ((forced == MAGB200_KERNEL_SKINNY && !sk) || (forced == MAGB200_KERNEL_TCGEN05 && !tc) ||
-            (forced != MAGB200_KERNEL_SKINNY && forced != MAGB200_KERNEL_TCGEN05 && forced != MAGB200_KERNEL_SIMT)) {
+        const bool can = (forced == MAGB200_KERNEL_SKINNY && sk) || (forced == MAGB200_KERNEL_TCGEN05 && tc) ||
+                         (forced == MAGB200_KERNEL_TCGEN05_2SM && tcgen05_2sm_supported(g)) || forced == MAGB200_KERNEL_SIMT;
+        if (!can) {
             set_error("matmul: forced kernel %d cannot run this problem (M=%lld N=%lld K=%lld)", forced, (long long)g.M, (long long)g.N, (long long)g.K);
             return MAGB200_ERR_INVALID_ARG;
         }
@@ -308,6 +310,9 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
         case MAGB200_KERNEL_TCGEN05:
             g_last_kernel = MAGB200_KERNEL_TCGEN05;
             return launch_gemm_tcgen05(g, d.stream, device, d.status);
+        case MAGB200_KERNEL_TCGEN05_2SM:
+            g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
+            return launch_gemm_tcgen05_2sm(g, d.stream, d.status);
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
             return launch_gemm_simt(g, d.stream);
@@ -521,7 +526,7 @@ int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }
 int magb200_force_kernel(int kernel) {
-    if (kernel < 0 || kernel > MAGB200_KERNEL_SKINNY_SPLITK) { set_error("force_kernel: unknown kernel %d", kernel); return MAGB200_ERR_INVALID_ARG; }
+    if (kernel < 0 || kernel > MAGB200_KERNEL_TCGEN05_2SM) { set_error("force_kernel: unknown kernel %d", kernel); return MAGB200_ERR_INVALID_ARG; }
     g_force.store(kernel);
     return MAGB200_OK;
 }

@@ -340,6 +340,258 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
+
+// =====================================================================================================================
+// Two-SM variant: a cluster of two CTAs computes one 256 x 256 tile with tcgen05.mma.cta_group::2.
+//
+// Why: a single-CTA 128 x 256 tile pulls 48 KB through L2 -> shared memory per 64-wide K block, about 96 bytes per clock
+// per SM, which is what bounds the one-CTA kernel. In a pair, CTA r loads only its 128 rows of A and its 128-column half of
+// B (32 KB per K block per SM); the MMA issued by the leader CTA reads both halves of B from the two shared memories and
+// writes each CTA's 128 accumulator rows into that CTA's TMEM. Loads are plain (non-multicast) TMA in the cta_group::2 form,
+// whose completion may be counted on the leader's mbarrier.
+//
+// Signalling across the pair (no multicast form is used anywhere):
+//   full[s]    lives in the leader; both CTAs' TMA loads complete on it; the leader's producer arms it with the byte count
+//              of both CTAs.
+//   empty[s]   one per CTA; the leader's MMA thread issues two tcgen05.commit per K block, one to its own barrier and one
+//              to the peer's (a shared::cluster address), so both producers learn at once that the stage is free.
+//   tfull[a]   accumulator a complete: likewise committed to both CTAs' barriers.
+//   tempty[a]  accumulator a drained: the 4 epilogue warps of BOTH CTAs arrive on the leader's barrier (count 8).
+// =====================================================================================================================
+constexpr int kThreads2 = 192;  // warp 0 TMA, warp 1 MMA (leader only), warps 2-5 epilogue
+constexpr int BN2 = 256;
+
+struct Cfg2 {
+    static constexpr int kABytes = BM * BK * 2;          // this CTA's 128 rows of A
+    static constexpr int kBBytes = (BN2 / 2) * BK * 2;   // this CTA's 128 columns of B
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = 6;
+    static constexpr int kTmemCols = 2 * BN2;
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_5d_2sm(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_2sm(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_2sm(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads2, 1)
+gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
+    using C = Cfg2;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    unsigned char *tiles_ptr = smem_raw + (tiles - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles_ptr + (size_t)C::kStages * C::kStageBytes);
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8u * C::kStages;
+    const uint32_t tfull0 = empty0 + 8u * C::kStages;
+    const uint32_t tempty0 = tfull0 + 16u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 2 * C::kStages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * C::kStages + 5);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull0 + 8u * i, 1); mbar_init(tempty0 + 8u * i, 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {  // both CTAs of the pair allocate, same warp index in each
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                // barriers of both CTAs exist before anyone signals across
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t num_pairs = gridDim.x >> 1;
+    const int64_t pair = blockIdx.x >> 1;
+
+    if (warp == 0) {
+        // ===================== TMA producer (one thread per CTA) =====================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint32_t full_leader0 = map_to_cta(full0, 0);
+            for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs) {
+                int64_t batch, tm, tn;
+                decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
+                const int m0 = (int)(tm * 2 * BM) + (int)rank * BM;        // this CTA's 128 rows of the 256-row tile
+                const int n0 = (int)(tn * BN2) + (int)rank * (BN2 / 2);    // this CTA's 128 columns of B
+                int bc[kMaxBatchDims] = {0, 0, 0};
+                {
+                    int64_t rem = batch;
+                    for (int d = args.nbatch - 1; d >= 0; --d) {
+                        int64_t q = rem / args.bshape[d];
+                        bc[d] = (int)(rem - q * args.bshape[d]);
+                        rem = q;
+                    }
+                }
+                const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
+                const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
+                for (int kb = 0; kb < args.num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = full_leader0 + 8u * stage;
+                    const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes;
+                    if (leader) {
+                        mbar_arrive_expect_tx(full0 + 8u * stage, 2u * (uint32_t)C::kStageBytes);
+                    }
+                    const int k0 = kb * BK;
+                    if (!args.a_mn) {
+                        tma_load_5d_2sm(sa, &tmA, full, k0, m0, a2, a1, a0);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c) tma_load_5d_2sm(sa + c * 8192, &tmA, full, m0 + c * 64, k0, a2, a1, a0);
+                    }
+                    if (!args.b_mn) {
+                        tma_load_5d_2sm(sb, &tmB, full, k0, n0, b2, b1, b0);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < (BN2 / 2) / 64; ++c) tma_load_5d_2sm(sb + c * 8192, &tmB, full, n0 + c * 64, k0, b2, b1, b0);
+                    }
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer (one thread of the leader CTA) =====================
+        if (leader && lane == 0) {
+            const uint32_t fmt = (DT == MAGB200_BF16) ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)args.a_mn << 15) |
+                                   ((uint32_t)args.b_mn << 16) | ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t a_lbo = args.a_mn ? 8192u : 16u, a_step = args.a_mn ? 2048u : 32u;
+            const uint32_t b_lbo = args.b_mn ? 8192u : 16u, b_step = args.b_mn ? 2048u : 32u;
+            const uint32_t empty_peer0 = map_to_cta(empty0, 1), tfull_peer0 = map_to_cta(tfull0, 1);
+            int stage = 0;
+            uint32_t phase = 0, titer = 0;
+            bool ok = true;
+            for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs, ++titer) {
+                const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN2;
+                for (int kb = 0; kb < args.num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = make_smem_desc(sa + k * a_step, a_lbo, 1024u);
+                        const uint64_t bd = make_smem_desc(sb + k * b_step, b_lbo, 1024u);
+                        tcgen05_mma_f16_2sm(tmem_d, ad, bd, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    tcgen05_commit_2sm(empty0 + 8u * stage);        // stage free: tell this CTA's producer ...
+                    tcgen05_commit_2sm(empty_peer0 + 8u * stage);   // ... and the peer's
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) { tcgen05_commit_2sm(tfull0 + 8u * acc); tcgen05_commit_2sm(tfull_peer0 + 8u * acc); }
+            }
+        }
+    } else {
+        // ===================== epilogue (4 warps per CTA, this CTA's 128 accumulator rows) =====================
+        const int quarter = warp & 3;
+        uint32_t titer = 0;
+        bool ok = true;
+        const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
+        const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
+        for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs, ++titer) {
+            const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
+            int64_t batch, tm, tn;
+            decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
+            const int64_t row = tm * 2 * BM + (int64_t)rank * BM + quarter * 32 + lane;
+            const int64_t n0 = tn * BN2;
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint16_t *crow = reinterpret_cast<uint16_t *>(args.C) + (batch * args.M + row) * args.N + n0;
+#pragma unroll 1
+            for (int c = 0; c < BN2; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c, r);
+                tmem_ld_wait();
+                if (row < args.M && n0 + c < args.N) {
+                    if (vec_ok && n0 + c + 32 <= args.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 8 epilogue warps
+        }
+    }
+
+    // ---- teardown: both CTAs meet (every wait above is bounded), then each frees its half of the allocation
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, kStatusTimeout);
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -476,6 +728,36 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     return MAGB200_OK;
 }
 
+
+template <int DT>
+int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st) {
+    auto kernel = gemm_tcgen05_2sm_kernel<DT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg2::kSmemBytes));
+        attr_set = true;
+    }
+    args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+    args.tiles_n = (p.N + BN2 - 1) / BN2;
+    args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    const int64_t max_pairs = kNumSMsB200 / 2;
+    const unsigned pairs = (unsigned)(args.total_tiles < max_pairs ? args.total_tiles : max_pairs);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(kThreads2, 1, 1);
+    cfg.dynamicSmemBytes = Cfg2::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
+    count_launch();
+    return MAGB200_OK;
+}
+
 }  // namespace
 
 bool tcgen05_supported(const GemmProblem &p) {
@@ -485,6 +767,43 @@ bool tcgen05_supported(const GemmProblem &p) {
     OperandDesc a, b;
     int amn, bmn;
     return describe(p, true, 128, a, amn) && describe(p, false, 128, b, bmn);
+}
+
+
+// The two-SM kernel pays when the output has at least one full wave of 256 x 256 tiles for the 74 CTA pairs; smaller
+// problems keep the one-CTA kernel with its narrower tiles (measured: 4096 x 1024 x 4096, 64 tiles, is 12 % faster there).
+bool tcgen05_2sm_supported(const GemmProblem &p) {
+    if (!tcgen05_supported(p)) return false;
+    if (p.M < 256 || p.N < 256) return false;
+    return true;
+}
+bool tcgen05_2sm_preferred(const GemmProblem &p) {
+    if (!tcgen05_2sm_supported(p)) return false;
+    const int64_t tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch_total;
+    return tiles >= kNumSMsB200 / 2;
+}
+
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int *status_word_dev) {
+    OperandDesc a, b;
+    int amn = 0, bmn = 0;
+    if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn)) {
+        set_error("tcgen05 matmul: operand layout cannot be described by a TMA tensor map");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = encode(a, p.dtype, &ta)) || (rc = encode(b, p.dtype, &tb))) return rc;
+    TcArgs args;
+    memset(&args, 0, sizeof(args));
+    args.C = p.C; args.M = p.M; args.N = p.N; args.K = p.K; args.dtype = p.dtype;
+    args.a_mn = amn; args.b_mn = bmn; args.nbatch = p.nbatch;
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        args.bshape[d] = d < p.nbatch ? p.bshape[d] : 1;
+        args.a_has[d] = a.has[d]; args.b_has[d] = b.has[d];
+    }
+    args.num_kb = (int)((p.K + BK - 1) / BK);
+    args.status = status_word_dev;
+    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16>(p, ta, tb, args, st) : launch_2sm<MAGB200_F16>(p, ta, tb, args, st);
 }
 
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int device, int *status_word_dev) {

@@ -550,6 +550,20 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             kch = (kch + 255) / 256 * 256;
             nsplit = (int)((p.K + kch - 1) / kch);
         }
+        // Long K with few 16-row tiles (e.g. a down projection, N = 5120, K = 25600): more K splits turn it into
+        // enough (tile, split) units for the persistent pipelined kernel; only done when that threshold is reached.
+        {
+            const int64_t base_units = tiles * p.batch_total;
+            int want = (int)((2 * warps_wanted + base_units - 1) / base_units);
+            const int cap = (int)(p.K / 1024);
+            if (want > cap) want = cap;
+            if (want > nsplit && base_units * want >= warps_wanted / 2) {
+                nsplit = want;
+                kch = (p.K + nsplit - 1) / nsplit;
+                kch = (kch + 255) / 256 * 256;
+                nsplit = (int)((p.K + kch - 1) / kch);
+            }
+        }
         if (tiles * nsplit * p.batch_total >= warps_wanted / 2) {
             // enough tiles for every warp of a persistent grid to stream several: the cp.async-pipelined kernel
             pl.mma = true; pl.async = true; pl.KW = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;

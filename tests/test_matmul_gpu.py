@@ -117,7 +117,7 @@ def test_single_op_workload_512x2048x2048(gpu, dname):
     xb, wb = bits(dt, rng, (512, 2048), 1.0), bits(dt, rng, (2048, 2048), 0.02)
     tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
     r = tx @ tw.T
-    assert mb.last_kernel() == ("tcgen05" if dt == O.BFLOAT16 else "simt")
+    assert mb.last_kernel() == ("tcgen05" if dt == O.BFLOAT16 else "simt")   # 16 tiles of 256x256: the one-CTA kernel
     got = r.to_bits()
     truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
     scale = np.abs(O.bits_to_f64(dt, xb)) @ np.abs(O.bits_to_f64(dt, wb)).T
@@ -147,7 +147,7 @@ def test_prefill_shapes_sampled(gpu, M, N, K):
     xb[5] = 0; xb[M - 1] = 0
     tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
     r = tx @ tw.T
-    assert mb.last_kernel() == "tcgen05"
+    assert mb.last_kernel() == "tcgen05_2sm"
     got = r.to_bits()
     rows = np.unique(np.concatenate([[0, 5, 127, 128, M - 1], rng.integers(0, M, 43)]))
     sampled_check(dt, xb, wb, got, rows, K)
@@ -186,7 +186,7 @@ def test_attention_broadcast_shapes(gpu, dname):
     tq, tk, tv = (mb.Tensor.from_bits(gpu, dt, a) for a in (q, k, v))
     kt = tk.transpose(2, 3).view((B, KV, 1, D, T))
     s = tq @ kt
-    assert mb.last_kernel() == "tcgen05" and s.shape == (B, KV, G, T, T)
+    assert mb.last_kernel().startswith("tcgen05") and s.shape == (B, KV, G, T, T)
     qf, kf, vf = (O.bits_to_f64(dt, a) for a in (q, k, v))
     truth = np.einsum("bhgtd,bhsd->bhgts", qf, kf)
     scale = np.einsum("bhgtd,bhsd->bhgts", np.abs(qf), np.abs(kf))
@@ -198,11 +198,51 @@ def test_attention_broadcast_shapes(gpu, dname):
     pb = O.f32_to_bits(dt, p.astype(np.float32))
     tp = mb.Tensor.from_bits(gpu, dt, pb)
     o = tp @ tv.view((B, KV, 1, T, D))
-    assert mb.last_kernel() == "tcgen05" and o.shape == (B, KV, G, T, D)
+    assert mb.last_kernel().startswith("tcgen05") and o.shape == (B, KV, G, T, D)
     pf = O.bits_to_f64(dt, pb)
     truth2 = np.einsum("bhgts,bhsd->bhgtd", pf, vf)
     m2 = O.error_metrics(dt, o.to_bits(), truth2, np.einsum("bhgts,bhsd->bhgtd", np.abs(pf), np.abs(vf)))
     assert m2["e"] <= unit_roundoff(dt) + T * 2.0 ** -24, m2
+
+
+TWO_SM_SHAPES = [
+    # (x storage shape, x transposed?, y storage shape, y is W.T?)  -- M, N >= 256 with tails in M, N and K
+    ((512, 256), False, (512, 256), True),
+    ((300, 200), False, (260, 200), True),          # ragged M, N, K
+    ((1024, 4096), False, (768, 4096), True),       # several tiles per pair, long K
+    ((384, 320), False, (320, 520), False),         # contiguous [K,N] weight (N-major B)
+    ((192, 640), True, (512, 192), True),           # transposed activation (M-major A)
+    ((3, 256, 128), False, (3, 128, 512), False),   # batched
+    ((2, 257, 72), False, (384, 72), True),         # batch folds into M = 514
+]
+
+
+@pytest.mark.parametrize("xs,xT,ys,wT", TWO_SM_SHAPES)
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_two_sm_kernel(gpu, xs, xT, ys, wT, dname):
+    """The CTA-pair kernel (tcgen05.mma.cta_group::2) forced on shapes with tails, both major-nesses and batches;
+    full fp64 truth."""
+    dt = cases.DTYPES[dname]
+    rng = np.random.default_rng(17)
+    xb, yb = bits(dt, rng, xs, 1.0), bits(dt, rng, ys, 0.1)
+    tx, ty = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, yb)
+    vx = tx.transpose(len(xs) - 2, len(xs) - 1) if xT else tx
+    vy = ty.transpose(len(ys) - 2, len(ys) - 1) if wT else ty
+    mb.force_kernel("tcgen05_2sm")
+    try:
+        r = vx @ vy
+        assert mb.last_kernel() == "tcgen05_2sm"
+        mb.synchronize(gpu)
+    finally:
+        mb.force_kernel(None)
+    xf, yf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, yb)
+    xf = np.swapaxes(xf, -1, -2) if xT else xf
+    yf = np.swapaxes(yf, -1, -2) if wT else yf
+    truth = np.matmul(xf, yf)
+    m = O.error_metrics(dt, r.to_bits(), truth, np.matmul(np.abs(xf), np.abs(yf)))
+    assert m["e"] <= unit_roundoff(dt) + xf.shape[-1] * 2.0 ** -24, m
+    for t in (r, tx, ty):
+        t.release()
 
 
 def test_host_buffer_matmul(gpu):
