@@ -557,7 +557,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             int want = (int)((2 * warps_wanted + base_units - 1) / base_units);
             const int cap = (int)(p.K / 1024);
             if (want > cap) want = cap;
-            if (want > nsplit && base_units * want >= warps_wanted / 2) {
+            if (base_units * nsplit < warps_wanted / 2 && want > nsplit && base_units * want >= warps_wanted / 2) {
                 nsplit = want;
                 kch = (p.K + nsplit - 1) / nsplit;
                 kch = (kch + 255) / 256 * 256;

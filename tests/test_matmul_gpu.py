@@ -147,7 +147,7 @@ def test_prefill_shapes_sampled(gpu, M, N, K):
     xb[5] = 0; xb[M - 1] = 0
     tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
     r = tx @ tw.T
-    assert mb.last_kernel() == "tcgen05_2sm"
+    assert mb.last_kernel() == ("tcgen05_2sm" if (M // 256) * (N // 256) >= 74 else "tcgen05")
     got = r.to_bits()
     rows = np.unique(np.concatenate([[0, 5, 127, 128, M - 1], rng.integers(0, M, 43)]))
     sampled_check(dt, xb, wb, got, rows, K)
