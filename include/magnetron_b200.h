@@ -77,6 +77,9 @@ int  magb200_synchronize(int device);
  * on `device`; NULL restores the library's own stream. */
 int  magb200_set_stream(int device, void *cuda_stream);
 void *magb200_get_stream(int device);
+/* Cap the number of CTAs the tensor-core matmuls launch on `device` (0 = all 148 SMs). A tensor-parallel caller leaves a
+ * few SMs free this way so that a collective running on another stream makes progress beside the persistent GEMM. */
+int  magb200_set_cta_limit(int device, int max_ctas);
 
 /* ---- storage: counterpart of mag_device_t::alloc_storage (magnetron/core/mag_backend.h:96) and of
  * the transfers the reference performs with memcpy on CPU storage (mag_copy_raw_,

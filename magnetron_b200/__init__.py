@@ -60,6 +60,7 @@ SIGNATURES = {
     "magb200_synchronize": (C.c_int, [C.c_int]),
     "magb200_set_stream": (C.c_int, [C.c_int, C.c_void_p]),
     "magb200_get_stream": (C.c_void_p, [C.c_int]),
+    "magb200_set_cta_limit": (C.c_int, [C.c_int, C.c_int]),
     "magb200_malloc": (C.c_int, [C.c_int, C.POINTER(C.c_void_p), C.c_size_t]),
     "magb200_free": (C.c_int, [C.c_int, C.c_void_p]),
     "magb200_upload": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),

@@ -41,6 +41,7 @@ struct DeviceState {
     size_t staging_bytes[3] = {0, 0, 0};
     char name[256] = "";
     bool capturing = false;          // between graph_begin_capture and graph_end_capture
+    int cta_limit = 0;               // 0: all SMs; else the tensor-core GEMMs launch at most this many CTAs
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -309,10 +310,10 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
         }
         case MAGB200_KERNEL_TCGEN05:
             g_last_kernel = MAGB200_KERNEL_TCGEN05;
-            return launch_gemm_tcgen05(g, d.stream, device, d.status);
+            return launch_gemm_tcgen05(g, d.stream, d.cta_limit, d.status);
         case MAGB200_KERNEL_TCGEN05_2SM:
             g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
-            return launch_gemm_tcgen05_2sm(g, d.stream, d.status);
+            return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status);
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
             return launch_gemm_simt(g, d.stream);
@@ -419,6 +420,15 @@ int magb200_synchronize(int device) {
     if (rc) return rc;
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
     return check_status_word(*d);
+}
+
+int magb200_set_cta_limit(int device, int max_ctas) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (max_ctas < 0 || max_ctas > kNumSMsB200) { set_error("set_cta_limit: %d is outside 0..%d", max_ctas, kNumSMsB200); return MAGB200_ERR_INVALID_ARG; }
+    d->cta_limit = max_ctas;
+    return MAGB200_OK;
 }
 
 int magb200_set_stream(int device, void *cuda_stream) {

@@ -112,10 +112,10 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk);
 bool tcgen05_supported(const GemmProblem &p);
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int device, int *status_word_dev);
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev);
 bool tcgen05_2sm_supported(const GemmProblem &p);
 bool tcgen05_2sm_preferred(const GemmProblem &p);
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int *status_word_dev);
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev);
 
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
                 const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);

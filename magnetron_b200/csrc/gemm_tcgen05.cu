@@ -710,7 +710,7 @@ int pick_bn(const GemmProblem &p) {
 }
 
 template <int BN, int DT>
-int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st) {
+int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit) {
     using C = Cfg<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, DT>;
     static bool attr_set = false;  // per template instantiation
@@ -721,7 +721,8 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     args.tiles_m = (p.M + BM - 1) / BM;
     args.tiles_n = (p.N + BN - 1) / BN;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
-    const unsigned grid = (unsigned)(args.total_tiles < kNumSMsB200 ? args.total_tiles : kNumSMsB200);
+    const int64_t max_ctas = cta_limit > 0 ? cta_limit : kNumSMsB200;
+    const unsigned grid = (unsigned)(args.total_tiles < max_ctas ? args.total_tiles : max_ctas);
     kernel<<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, args);
     count_launch();
     MAGB200_CUDA_TRY(cudaGetLastError());
@@ -730,7 +731,7 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
 
 
 template <int DT>
-int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st) {
+int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit) {
     auto kernel = gemm_tcgen05_2sm_kernel<DT>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -740,7 +741,7 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     args.tiles_n = (p.N + BN2 - 1) / BN2;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
-    const int64_t max_pairs = kNumSMsB200 / 2;
+    const int64_t max_pairs = (cta_limit > 1 ? cta_limit : kNumSMsB200) / 2;
     const unsigned pairs = (unsigned)(args.total_tiles < max_pairs ? args.total_tiles : max_pairs);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -783,7 +784,7 @@ bool tcgen05_2sm_preferred(const GemmProblem &p) {
     return tiles >= kNumSMsB200 / 2;
 }
 
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int *status_word_dev) {
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev) {
     OperandDesc a, b;
     int amn = 0, bmn = 0;
     if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn)) {
@@ -803,11 +804,10 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int *status_w
     }
     args.num_kb = (int)((p.K + BK - 1) / BK);
     args.status = status_word_dev;
-    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16>(p, ta, tb, args, st) : launch_2sm<MAGB200_F16>(p, ta, tb, args, st);
+    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16>(p, ta, tb, args, st, cta_limit) : launch_2sm<MAGB200_F16>(p, ta, tb, args, st, cta_limit);
 }
 
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int device, int *status_word_dev) {
-    (void)device;
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev) {
     const int bn = pick_bn(p);
     OperandDesc a, b;
     int amn = 0, bmn = 0;
@@ -829,8 +829,8 @@ int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int device, int *
     args.num_kb = (int)((p.K + BK - 1) / BK);
     args.status = status_word_dev;
 #define LAUNCH(BNV)                                                                                   \
-    return p.dtype == MAGB200_BF16 ? launch_cfg<BNV, MAGB200_BF16>(p, ta, tb, args, st)                \
-                                   : launch_cfg<BNV, MAGB200_F16>(p, ta, tb, args, st)
+    return p.dtype == MAGB200_BF16 ? launch_cfg<BNV, MAGB200_BF16>(p, ta, tb, args, st, cta_limit)                \
+                                   : launch_cfg<BNV, MAGB200_F16>(p, ta, tb, args, st, cta_limit)
     if (bn == 256) { LAUNCH(256); }
     if (bn == 128) { LAUNCH(128); }
     LAUNCH(64);

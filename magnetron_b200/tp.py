@@ -10,8 +10,10 @@ logic around the unchanged single-GPU matmul. The path shards in two ways:
                           computes a partial y over its K range, and one all-reduce (sum) makes the result.
 
 Paired the Megatron way (column-sharded QKV / gate+up feed row-sharded o / down) a transformer layer needs two
-all-reduces and no gather. To hide them, the row-sharded GEMM is cut into chunks of M and each chunk's all-reduce is
-issued asynchronously while the next chunk multiplies.
+all-reduces and no gather. To hide them the token dimension is cut into chunks that travel through the layer one after
+the other (rows are independent): while the all-reduce of chunk c is on the wire, chunk c+1 multiplies. The dependencies
+of a real layer are kept -- gate/up of a chunk starts only after that chunk's o-projection all-reduce -- and the GEMMs
+leave a few SMs free (magb200_set_cta_limit) so that the collective's kernel can run beside the persistent GEMM.
 
 Device memory is held in torch tensors (so NCCL can see it); the matmuls go through the C ABI of this package on
 torch's current stream. There is no CPU path: `TPLayer` raises without the CUDA library. The `matmul` argument
@@ -70,8 +72,9 @@ def layer_flops(specs: Sequence[ShardedLinear], m: int) -> float:
     return sum(2.0 * m * s.n * s.k for s in specs)
 
 
-def cabi_matmul(device: int) -> Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]:
-    """out[M,N] = x[M,K] @ w[N,K].T on `device` through magb200_matmul, on torch's current stream."""
+def cabi_matmul(device: int, reserve_sms: int = 0) -> Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]:
+    """out[M,N] = x[M,K] @ w[N,K].T on `device` through magb200_matmul, on torch's current stream. `reserve_sms` SMs are
+    left free by the tensor-core GEMMs for a collective that runs at the same time."""
     import magnetron_b200 as mb
     L = mb.lib()
     mb.check(L.magb200_device_init(device))
@@ -80,6 +83,7 @@ def cabi_matmul(device: int) -> Callable[[torch.Tensor, torch.Tensor, torch.Tens
         raise RuntimeError("make a torch.cuda.Stream current first: the default stream has a null handle, which the C ABI "
                            "reads as 'use the library's own stream', and matmuls would then not be ordered with the collectives")
     mb.check(L.magb200_set_stream(device, C.c_void_p(handle)))
+    mb.check(L.magb200_set_cta_limit(device, 148 - reserve_sms if reserve_sms else 0))
     dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16, torch.float32: mb.FLOAT32}
 
     def view(t: torch.Tensor, shape=None, strides=None):
@@ -97,14 +101,14 @@ class TPLayer:
     """The sharded linears of one layer on this rank, with resident weight shards and preallocated outputs."""
 
     def __init__(self, specs: Sequence[ShardedLinear], m: int, *, device: torch.device, dtype=torch.bfloat16,
-                 matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4):
+                 matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4, reserve_sms: int = 0):
         self.specs, self.m, self.group = tuple(specs), m, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if matmul is None:
             if device.type != "cuda":
                 raise RuntimeError("TPLayer runs on CUDA devices only: there is no CPU path")
-            matmul = cabi_matmul(device.index or 0)
+            matmul = cabi_matmul(device.index or 0, reserve_sms)
         self.matmul = matmul
         self.chunks = max(1, min(chunks, m // 512)) if m >= 1024 else 1
         gen = torch.Generator(device="cpu").manual_seed(seed)
@@ -161,3 +165,37 @@ class TPLayer:
                 self.column(s.name, gather=gather_outputs)
             else:
                 self.row(s.name)
+
+    def step_pipelined(self) -> None:
+        """One layer, token chunks in flight: [col, row, all-reduce] pairs per chunk; the column GEMM that follows a
+        row-sharded one waits for that chunk's all-reduce (as the next sub-block of a transformer layer must), everything
+        else of the next chunk is issued first so that it overlaps the collective."""
+        if self.world == 1 or self.chunks == 1:
+            return self.step(False)
+        pairs = [(self.specs[i], self.specs[i + 1]) for i in range(0, len(self.specs) - 1, 2)
+                 if self.specs[i].kind == "col" and self.specs[i + 1].kind == "row"]
+        if 2 * len(pairs) != len(self.specs):
+            return self.step(False)
+        step = (self.m + self.chunks - 1) // self.chunks
+        bounds = [(lo, min(self.m, lo + step)) for lo in range(0, self.m, step)]
+        pending = {}   # (pair index, chunk) -> work of the all-reduce that the next pair of that chunk depends on
+
+        def run_pair(pi, ci):
+            col, row = pairs[pi]
+            lo, hi = bounds[ci]
+            if pi > 0:
+                pending.pop((pi - 1, ci)).wait()                       # this chunk's previous all-reduce
+            self.matmul(self.x[col.name][lo:hi], self.w[col.name], self.y[col.name][lo:hi])
+            self.matmul(self.x[row.name][lo:hi], self.w[row.name], self.y[row.name][lo:hi])
+            pending[(pi, ci)] = dist.all_reduce(self.y[row.name][lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        # skewed order: pair p of chunk c is issued together with pair p-1 of chunk c+1, so each all-reduce has one
+        # pair of GEMMs of the neighbouring chunk to hide behind
+        n_p, n_c = len(pairs), len(bounds)
+        for wave in range(n_c + n_p - 1):
+            for pi in range(n_p):
+                ci = wave - pi
+                if 0 <= ci < n_c:
+                    run_pair(pi, ci)
+        for wk in pending.values():
+            wk.wait()

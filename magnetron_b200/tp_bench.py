@@ -55,6 +55,8 @@ def main(args, pk):
     sys.stdout.flush()
     saved_stdout = os.dup(1)
     os.dup2(2, 1)
+    if world > 1:   # before the communicator exists: the collective's kernel must fit in the SMs the GEMMs leave free
+        os.environ.setdefault("NCCL_MAX_CTAS", str(max(int(os.environ.get("MAGB200_TP_RESERVE_SMS", "16")), 8)))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     # a dedicated stream: the C ABI treats a null handle (torch's default stream) as "use the library's own stream",
@@ -68,11 +70,19 @@ def main(args, pk):
     M = 8192
     specs = tp.QWEN3_32B_LAYER
     flops = tp.layer_flops(specs, M)
-    layer = tp.TPLayer(specs, M, device=device)
+    reserve = int(os.environ.get("MAGB200_TP_RESERVE_SMS", "16")) if world > 1 else 0
+    layer = tp.TPLayer(specs, M, device=device, reserve_sms=reserve)
     mb.lib().magb200_launch_count_reset()
-    ms = _time_steps(lambda: layer.step(False), steps, warmup, device)
+    ms_plain = _time_steps(lambda: layer.step(False), max(2, steps // 2), 2, device)
+    mb.lib().magb200_launch_count_reset()
+    ms = _time_steps(layer.step_pipelined, steps, warmup, device)
     launches = int(mb.lib().magb200_launch_count()) * steps // (steps + warmup)
     ms_gather = _time_steps(lambda: layer.step(True), max(2, steps // 2), 2, device)
+    pipelined_tflops = flops * steps / ms / 1e9
+    plain_tflops = flops * max(2, steps // 2) / ms_plain / 1e9
+    schedule = "token chunks pipelined through the layer" if pipelined_tflops >= plain_tflops else "op by op, all-reduce chunked over M"
+    if plain_tflops > pipelined_tflops:   # the headline is the faster of the two legal schedules; both are reported
+        ms = ms_plain * steps / max(2, steps // 2)
     value = flops * steps / ms / 1e9
     sweep = {}
     del layer
@@ -92,12 +102,16 @@ def main(args, pk):
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "qwen3-32b-tp: QKV [10240x5120] and gate/up [51200x5120] column-sharded on N, o [5120x8192] and "
-                                   "down [5120x25600] row-sharded on K with an NCCL all-reduce (paired schedule, all-reduce chunked over M "
-                                   "and overlapped), M=8192, seed 5", "parallelism": f"tp{world}",
+                                   "down [5120x25600] row-sharded on K with an NCCL all-reduce (paired schedule, token chunks pipelined through the "
+                                   "layer so all-reduces overlap the next chunk's GEMMs), M=8192, seed 5", "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2 (975 MB of weights per layer across ranks)"},
             "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "host-buffer end-to-end is measured on the 1-GPU line; the sharded layer keeps activations on the device"},
             "gpu_launches": launches,
+            "schedule": schedule,
+            "op_by_op_schedule": {"ms_per_step": ms_plain / max(2, steps // 2), "tflops": plain_tflops},
+            "pipelined_schedule": {"tflops": pipelined_tflops},
+            "reserved_sms_for_collectives": reserve,
             "with_output_allgather": {"ms_per_step": ms_gather / max(2, steps // 2), "tflops": flops * max(2, steps // 2) / ms_gather / 1e9},
             "token_sweep": sweep,
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": pk["tensor_burst"], "unit": "TFLOP/s per GPU",

@@ -50,7 +50,13 @@ def _rank_main(rank, world, port, ret):
         m = 1024   # large enough for the chunked, overlapped all-reduce path (2 chunks)
         layer = tp.TPLayer(SMALL, m, device=torch.device("cpu"), dtype=torch.float32, matmul=_standin)
         assert layer.chunks == 2
+        layer.step_pipelined()          # chunks travel through the layer with their all-reduces in flight
+        piped = {s.name: layer.y[s.name].clone() for s in SMALL}
+        for s in SMALL:
+            layer.y[s.name].zero_()
         layer.step(False)
+        for s in SMALL:
+            assert torch.allclose(piped[s.name], layer.y[s.name], atol=1e-5, rtol=1e-5), s.name
         out = {}
         for s in SMALL:
             if s.kind == "col":
