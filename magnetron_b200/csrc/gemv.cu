@@ -47,6 +47,28 @@ struct SkinnyArgs {
     int64_t batch_total;
 };
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream is still running. Everything that does not depend on the predecessor's output (index set-up,
+// the first weight loads) runs before pdl_wait(); the activations are read only after it. pdl_launch_dependents() lets
+// the successor start its own independent part early. Decode is a chain of microsecond kernels, so this hides most of
+// the launch latency between them.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+    return MAGB200_OK;
+}
+
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -186,18 +208,53 @@ template <int DT> __device__ __forceinline__ void mma_16816(float (&c)[4], uint3
 // r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
 // k+4..7: slots (2t, 2t+1) <- first pair, slots (2t+8, 2t+9) <- second pair, the same in A and B.
 template <int DT, int KW>
-__global__ void __launch_bounds__(kThreads, 3) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
+__global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
     constexpr int RW = kWarps / KW;
+    constexpr int kPre = 4;                                                  // weight steps loaded ahead of the activations
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem);                      // [M][xstride]
     float *red = reinterpret_cast<float *>(smem + (size_t)M * xstride * 2);  // [KW][RW][128] when KW > 1
 
+    pdl_launch_dependents();
     const int split = blockIdx.y;
     const int64_t batch = blockIdx.z;
     const int64_t k0 = (int64_t)split * a.kch;
     const int kc = (int)min(a.kch, a.K - k0);      // a CTA's K range always fits 32 bits (bounded by shared memory)
     int64_t offA, offB;
     batch_offsets(a, batch, offA, offB);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rw = warp / KW, kw = warp % KW;
+    const int g = lane >> 2, t = lane & 3;
+    int per = (kc + KW - 1) / KW;
+    per = (per + 31) / 32 * 32;
+    const int ks = min(kc, kw * per), ke = min(kc, ks + per);
+    const int nfull = (ke - ks) >> 5;
+    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
+    const uint16_t *xrow = xs + g * xstride;
+    const bool has_x = g < M;
+
+    // 16-row tiles are dealt out evenly: unit u (a row-warp slot of some CTA) takes tiles [u*T/U, (u+1)*T/U).
+    // Every warp of a CTA runs the same number of rounds (the K-slice reduction below has CTA barriers).
+    const int64_t T = (a.N + 15) / 16;
+    const int64_t U = (int64_t)gridDim.x * RW;
+    const int64_t u = (int64_t)blockIdx.x * RW + rw;
+    const int64_t t_begin = u * T / U, t_end = (u + 1) * T / U;
+    const int64_t rounds = (T + U - 1) / U;
+
+    // The weights do not depend on the previous kernel: the first steps of the first tile are in flight before the
+    // activations are even staged (and, under programmatic dependent launch, before the previous kernel has finished).
+    uint4 pre_a[kPre], pre_b[kPre];
+    const int npre = (t_begin < t_end) ? min(nfull, kPre) : 0;
+    if (npre > 0) {
+        const uint4 *qa = reinterpret_cast<const uint4 *>(Bbase + min(t_begin * 16 + g, a.N - 1) * a.ldb + ks) + t;
+        const uint4 *qb = reinterpret_cast<const uint4 *>(Bbase + min(t_begin * 16 + g + 8, a.N - 1) * a.ldb + ks) + t;
+#pragma unroll
+        for (int i = 0; i < kPre; ++i)
+            if (i < npre) { pre_a[i] = ldg_stream(qa + 4 * i); pre_b[i] = ldg_stream(qb + 4 * i); }
+    }
+
+    pdl_wait();
     {
         // stage the activation rows: 16-byte copies when the rows are unit-stride and aligned, else element-wise
         const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
@@ -216,24 +273,6 @@ __global__ void __launch_bounds__(kThreads, 3) skinny_km_mma_kernel(const Skinny
     }
     __syncthreads();
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rw = warp / KW, kw = warp % KW;
-    const int g = lane >> 2, t = lane & 3;
-    int per = (kc + KW - 1) / KW;
-    per = (per + 31) / 32 * 32;
-    const int ks = min(kc, kw * per), ke = min(kc, ks + per);
-    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
-    const uint16_t *xrow = xs + g * xstride;
-    const bool has_x = g < M;
-
-    // 16-row tiles are dealt out evenly: unit u (a row-warp slot of some CTA) takes tiles [u*T/U, (u+1)*T/U).
-    // Every warp of a CTA runs the same number of rounds (the K-slice reduction below has CTA barriers).
-    const int64_t T = (a.N + 15) / 16;
-    const int64_t U = (int64_t)gridDim.x * RW;
-    const int64_t u = (int64_t)blockIdx.x * RW + rw;
-    const int64_t t_begin = u * T / U, t_end = (u + 1) * T / U;
-    const int64_t rounds = (T + U - 1) / U;
-
     for (int64_t round = 0; round < rounds; ++round) {
         const int64_t tile = t_begin + round;
         const bool active = tile < t_end;
@@ -248,9 +287,21 @@ __global__ void __launch_bounds__(kThreads, 3) skinny_km_mma_kernel(const Skinny
             const uint4 *pa4 = reinterpret_cast<const uint4 *>(pa + ks) + t;
             const uint4 *pb4 = reinterpret_cast<const uint4 *>(pb + ks) + t;
             const uint4 *px4 = reinterpret_cast<const uint4 *>(xrow + ks) + t;
-            const int nfull = (ke - ks) >> 5;
+            int first = 0;
+            if (round == 0) {
+#pragma unroll
+                for (int i = 0; i < kPre; ++i) {
+                    if (i < npre) {
+                        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                        if (has_x) xv = px4[4 * i];
+                        mma_16816<DT>(c, pre_a[i].x, pre_b[i].x, pre_a[i].y, pre_b[i].y, xv.x, xv.y);
+                        mma_16816<DT>(c, pre_a[i].z, pre_b[i].z, pre_a[i].w, pre_b[i].w, xv.z, xv.w);
+                    }
+                }
+                first = npre;
+            }
 #pragma unroll 4
-            for (int i = 0; i < nfull; ++i) {
+            for (int i = first; i < nfull; ++i) {
                 const uint4 wa = ldg_stream(pa4 + 4 * i);
                 const uint4 wb = ldg_stream(pb4 + 4 * i);
                 uint4 xv = make_uint4(0u, 0u, 0u, 0u);
@@ -314,26 +365,13 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
     uint4 *ring = reinterpret_cast<uint4 *>(smem);                                  // [depth][2][256 lanes]
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kAsyncRingBytes);            // [M][xstride]
 
+    pdl_launch_dependents();
     const int split = blockIdx.y;
     const int64_t batch = blockIdx.z;
     const int64_t k0 = (int64_t)split * a.kch;
     const int kc = (int)min(a.kch, a.K - k0);
     int64_t offA, offB;
     batch_offsets(a, batch, offA, offB);
-    {
-        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
-        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
-        for (int m = 0; m < M; ++m) {
-            if (vec) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
-                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
-                for (int c = threadIdx.x; c < (kc >> 3); c += kThreads) dst[c] = src[c];
-            } else {
-                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
-            }
-        }
-    }
-    __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -372,6 +410,23 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
     };
 
     for (int q = 0; q < kAsyncDepth; ++q) issue();
+
+    // the weight copies above do not depend on the previous kernel; the activations do
+    pdl_wait();
+    {
+        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
+        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
+        for (int m = 0; m < M; ++m) {
+            if (vec) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
+                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
+                for (int c = threadIdx.x; c < (kc >> 3); c += kThreads) dst[c] = src[c];
+            } else {
+                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
+            }
+        }
+    }
+    __syncthreads();
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     int c_ks = 0, c_slot = 0;
     for (int64_t tile = t_begin; tile < t_end;) {
@@ -489,6 +544,8 @@ __global__ void __launch_bounds__(kThreads) skinny_nm_kernel(const SkinnyArgs a)
 template <int DT>
 __global__ void __launch_bounds__(kThreads) skinny_finalize_kernel(const float *__restrict__ partial, void *__restrict__ C,
                                                                    int64_t total, int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();   // the partial sums come from the kernel before this one
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
         float s = 0.f;
@@ -661,14 +718,14 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
     if (pl.async) {
         if constexpr (DT != MAGB200_F32) {
             if ((rc = set_smem(skinny_km_async_kernel<DT>, pl.smem))) return rc;
-            skinny_km_async_kernel<DT><<<grid, kThreads, pl.smem, st>>>(a, M, (int)pl.xstride);
+            if ((rc = launch_pdl(skinny_km_async_kernel<DT>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc;
         }
     } else if (pl.mma) {
         if constexpr (DT != MAGB200_F32) {
 #define LAUNCH_KW(KWV)                                                                                   \
     case KWV:                                                                                            \
         if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
-        skinny_km_mma_kernel<DT, KWV><<<grid, kThreads, pl.smem, st>>>(a, M, (int)pl.xstride);        \
+        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
         break;
             switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
 #undef LAUNCH_KW
@@ -721,7 +778,7 @@ int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scra
     if (pl.nsplit > 1) {
         int64_t blocks = (total + kThreads - 1) / kThreads;
         if (blocks > kNumSMsB200 * 8) blocks = kNumSMsB200 * 8;
-        skinny_finalize_kernel<DT><<<(unsigned)blocks, kThreads, 0, st>>>(scratch, p.C, total, pl.nsplit);
+        if (int rc2 = launch_pdl(skinny_finalize_kernel<DT>, dim3((unsigned)blocks), dim3(kThreads), 0, st, (const float *)scratch, p.C, total, pl.nsplit)) return rc2;
         count_launch();
         MAGB200_CUDA_TRY(cudaGetLastError());
     }

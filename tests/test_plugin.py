@@ -3,6 +3,8 @@ reference's own C API (mag_ctx_create("cuda:0"), mag_transpose, mag_view, mag_ma
 import ctypes as C
 import os
 import shutil
+import subprocess
+import sys
 import tempfile
 
 import numpy as np
@@ -14,6 +16,7 @@ from oracle import ref_driver as R
 from tests import cases
 from tests.common import unit_roundoff
 
+ROOT_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PLUGIN = os.path.join(os.path.dirname(mb.lib_path()), "libmagnetron_cuda.so")
 needs_ref = pytest.mark.skipif(not (R.available() and os.path.exists(PLUGIN)),
                                reason="needs oracle/_ref (reference core) and the built backend module")
@@ -64,110 +67,29 @@ def test_context_without_gpu_falls_back_to_cpu_cleanly(deploy_dir):
         api.close()
 
 
-class CudaApi(R.MagApi):
-    """The same driver on "cuda:0", with data movement through the module's additive exports."""
-
-    def __init__(self, deploy_dir):
-        super().__init__("cuda:0", lib_dir=deploy_dir, log_level=int(os.environ.get("MAG_TEST_LOG_LEVEL", "1")))
-        self.mod = plugin_handle(deploy_dir)
-        self.mod.mag_b200_upload.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
-        self.mod.mag_b200_download.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
-        self.mod.mag_b200_synchronize.argtypes = [C.c_void_p]
-
-    def from_bits(self, dtype, bits):
-        bits = np.ascontiguousarray(bits, dtype=R.DTYPE_NP[dtype])
-        t = self.empty(dtype, bits.shape if bits.ndim else (1,))
-        assert self.mod.mag_b200_upload(t.ptr, bits.ctypes.data, bits.nbytes) == 0
-        return t
-
-    def to_bits(self, t):
-        c = t if self.lib.mag_tensor_is_contiguous(t.ptr) else self.contiguous(t)
-        out = np.empty(c.shape, dtype=R.DTYPE_NP[c.dtype])
-        assert self.mod.mag_b200_download(c.ptr, out.ctypes.data, out.nbytes) == 0
-        if c is not t:
-            c.release()
-        return out
+def run_in_fresh_process(case: str, deploy_dir: str):
+    res = subprocess.run([sys.executable, "-m", "tests.plugin_driver", case, deploy_dir], cwd=ROOT_DIR,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and f"OK {case}" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
 
 @pytest.mark.gpu
 @needs_ref
 def test_matmul_and_cast_through_the_reference_api(deploy_dir, gpu):
-    api = CudaApi(deploy_dir)
-    try:
-        assert "B200" in api.device_name
-        dt = R.BFLOAT16
-        rng = np.random.default_rng(0)
-        xb = O.f32_to_bits(dt, cases.gen_storage(rng, (512, 2048), 1.0))
-        wb = O.f32_to_bits(dt, cases.gen_storage(rng, (2048, 2048), 0.02))
-        x, w = api.from_bits(dt, xb), api.from_bits(dt, wb)
-        wt = api.transpose(w, 0, 1)                       # W.T: shape (K,N), strides (1,K)
-        assert wt.strides == (1, 2048)
-        r = api.matmul(x, wt)
-        got = api.to_bits(r)
-        xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
-        m = O.error_metrics(dt, got, xf @ wf.T, np.abs(xf) @ np.abs(wf).T)
-        assert m["e"] <= unit_roundoff(dt) + 2048 * 2.0 ** -24, m
-        # cast both ways, bit exact with the oracle
-        f = api.cast(r, R.FLOAT32)
-        assert np.array_equal(api.to_bits(f), O.cast_bits(dt, R.FLOAT32, got))
-        x32 = api.from_bits(R.FLOAT32, cases.cast_inputs_f32(1, 1 << 16))
-        h = api.cast(x32, R.FLOAT16)
-        assert np.array_equal(api.to_bits(h), O.cast_bits(R.FLOAT32, R.FLOAT16, cases.cast_inputs_f32(1, 1 << 16)))
-        # strided view -> contiguous (MAG_OP_CLONE), then a decode-shaped product
-        wc = api.contiguous(wt)
-        assert np.array_equal(api.to_bits(wc), np.ascontiguousarray(wb.T))
-        x1 = api.from_bits(dt, xb[:1])
-        r1 = api.matmul(x1, wt)
-        m1 = O.error_metrics(dt, api.to_bits(r1), xf[:1] @ wf.T, np.abs(xf[:1]) @ np.abs(wf).T)
-        assert m1["e"] <= unit_roundoff(dt) + 2048 * 2.0 ** -24, m1
-        for t in (r1, x1, wc, h, x32, f, r, wt, w, x):
-            t.release()
-    finally:
-        api.close()   # leak detection on: every storage must have been returned
+    """x @ W.T, casts, contiguous() of a strided view and a decode-shaped product through mag_* calls on "cuda:0";
+    the context is destroyed with leak detection on."""
+    run_in_fresh_process("matmul_cast", deploy_dir)
 
 
 @pytest.mark.gpu
 @needs_ref
 def test_gqa_broadcast_views_through_the_reference_api(deploy_dir, gpu):
-    """Q.reshape(B,KV,G,T,D) @ K.transpose(2,3).view(B,KV,1,D,T): the view solver's stride-0 broadcast dim
-    arrives at the backend untouched."""
-    api = CudaApi(deploy_dir)
-    try:
-        dt = R.FLOAT16
-        B, KV, G, T, D = 1, 2, 4, 128, 64
-        rng = np.random.default_rng(4)
-        q = O.f32_to_bits(dt, cases.gen_storage(rng, (B, KV, G, T, D), 1.0))
-        k = O.f32_to_bits(dt, cases.gen_storage(rng, (B, KV, T, D), 1.0))
-        tq, tk = api.from_bits(dt, q), api.from_bits(dt, k)
-        kt = api.transpose(tk, 2, 3)
-        kv = api.view(kt, (B, KV, 1, D, T))
-        assert kv.strides[2] == 0
-        s = api.matmul(tq, kv)
-        assert s.shape == (B, KV, G, T, T)
-        qf, kf = O.bits_to_f64(dt, q), O.bits_to_f64(dt, k)
-        truth = np.einsum("bhgtd,bhsd->bhgts", qf, kf)
-        m = O.error_metrics(dt, api.to_bits(s), truth, np.einsum("bhgtd,bhsd->bhgts", np.abs(qf), np.abs(kf)))
-        assert m["e"] <= unit_roundoff(dt) + D * 2.0 ** -24, m
-        for t in (s, kv, kt, tk, tq):
-            t.release()
-    finally:
-        api.close()
+    """Q.reshape(B,KV,G,T,D) @ K.transpose(2,3).view(B,KV,1,D,T): the view solver's stride-0 dim reaches the backend."""
+    run_in_fresh_process("gqa_views", deploy_dir)
 
 
 @pytest.mark.gpu
 @needs_ref
 def test_unsupported_opcode_returns_a_status(deploy_dir, gpu):
     """Opcodes outside the path come back as a status code, not as an abort."""
-    api = CudaApi(deploy_dir)
-    try:
-        api.lib.mag_softmax.restype = C.c_int
-        api.lib.mag_softmax.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p]
-        x = api.from_bits(R.FLOAT32, np.zeros((4, 4), np.uint32))
-        err, out = R.MagError(), C.c_void_p()
-        st = api.lib.mag_softmax(C.byref(err), C.byref(out), x.ptr)
-        assert st != 0
-        if out.value:
-            api.lib.mag_tensor_decref(out.value)
-        x.release()
-    finally:
-        api.close(True)
+    run_in_fresh_process("unsupported_op", deploy_dir)
