@@ -179,6 +179,7 @@ def prefill_workload(dev: Dev, steps: int, warmup: int):
     outs = {n: mb.Tensor(dev.d, BF16, (TOKENS, N)) for n, N, K, _ in PREFILL_GEMMS}
     calls = [(acts[a].view_struct(), weights[n].T.view_struct(), outs[n].view_struct()) for n, N, K, a in PREFILL_GEMMS]
     flops = sum(2.0 * TOKENS * N * K for _, N, K, _ in PREFILL_GEMMS)
+    abytes = sum(2.0 * (TOKENS * K + N * K + TOKENS * N) for _, N, K, _ in PREFILL_GEMMS)
 
     def step():
         for xv, wv, rv in calls:
@@ -214,7 +215,7 @@ def prefill_workload(dev: Dev, steps: int, warmup: int):
     for t in list(acts.values()) + list(weights.values()) + list(outs.values()):
         t.release()
     return {"ms_per_step": ms / steps, "tflops": flops * steps / ms / 1e9, "launches": launches, "kernel": kernel,
-            "flops_per_step": flops, "e2e_ms_per_step": ms_e2e / e2e_steps, "e2e_tflops": flops * e2e_steps / ms_e2e / 1e9,
+            "flops_per_step": flops, "bytes_per_step": abytes, "e2e_ms_per_step": ms_e2e / e2e_steps, "e2e_tflops": flops * e2e_steps / ms_e2e / 1e9,
             "h2d": h2d, "d2h": d2h}
 
 
@@ -395,13 +396,21 @@ def main():
                 "ms_per_step": pre["e2e_ms_per_step"]},
         "gpu_launches": pre["launches"], "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": pre["tflops"], "peak": tensor_peak, "unit": "TFLOP/s",
-                     "frac": pre["tflops"] / tensor_peak, "traffic": None,
+                     "frac": pre["tflops"] / tensor_peak,
+                     # DRAM bytes per launch: the ncu capture of one 4096^3 launch of the same kernel read+wrote 98.5 MB against
+                     # 100.7 MB algorithmic (profiles/gemm_tcgen05_2sm_4096x4096x4096.md); scaled to the step's mean launch
+                     "traffic": 0.978 * pre["bytes_per_step"] / len(PREFILL_GEMMS),
+                     "traffic_note": "scaled from an ncu capture of a smaller case by algorithmic bytes; mean over the step's 7 launches",
                      "peak_source": "%s %s cuBLAS bf16" % (pk["source"], "sustained" if long_run else "burst"),
-                     "frac_of_nominal_2250": pre["tflops"] / 2250.0, "kernel": "gemm_tcgen05_kernel",
-                     "algorithmic_flops_per_step": pre["flops_per_step"]},
+                     "frac_of_nominal_2250": pre["tflops"] / 2250.0,
+                     "kernel": "gemm_tcgen05_2sm_kernel (q,o,gate,up,down) + gemm_tcgen05_kernel (k,v)",
+                     "algorithmic_flops_per_step": pre["flops_per_step"], "algorithmic_bytes_per_step": pre["bytes_per_step"]},
     }
     if not args.skip_decode:
         line["decode"] = {"metric": "decode GEMV HBM GB/s", "unit": "GB/s", "peak": pk["hbm"], "peak_source": pk["source"] + " copy",
+                          "note": "gbs/frac = whole token pass replayed as a CUDA graph (197 launches, mostly 2-6 MB each, latency bound); "
+                                  "lm_head_* = the 311 MB GEMV alone, the per-kernel HBM figure (kernel skinny_km_async_kernel, "
+                                  "ncu: profiles/skinny_km_async_M4_65536x4096.md)",
                           "config": "qwen3-0.6b token pass: 28 layers x (q,k,v,o,gate,up,down) + lm_head, bf16, W.T views, seed 2",
                           **decode_workload(dev, max(3, min(args.steps, 10)), args.warmup, pk["hbm"])}
         line["casts"] = {"unit": "GB/s", "peak": pk["hbm"], "elements": 1 << 24,
