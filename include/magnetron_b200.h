@@ -130,6 +130,18 @@ void     magb200_launch_count_reset(void);
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
 
+/* ---- tensor-parallel row-sharded linear, fused with its exchange ---------------------------------
+ * No counterpart in the reference (it has no multi-device code). A row-sharded (K-sharded) linear needs the sum of
+ * every rank's partial [M,N] product. Instead of a GEMM followed by an all-reduce, the GEMM's epilogue pushes each
+ * finished tile straight into the staging buffer of the rank that owns those rows (ordinary stores through peer
+ * mappings, under the main loop), and after a cross-rank barrier (the caller's, e.g. a symmetric-memory barrier)
+ * magb200_reduce_broadcast sums the `nranks` partial blocks in fp32, rounds once and writes the finished rows into
+ * every rank's output. `peer_stage[i]` / `peer_out[i]` are device addresses valid on THIS device for rank i's
+ * buffers (peer-mapped; [nranks][M/nranks][N] and [M][N] elements). M must be divisible by nranks. */
+int  magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_view_t *y, void *const *peer_stage, int nranks, int rank);
+int  magb200_reduce_broadcast(int device, const void *stage, void *const *peer_out, int nranks, int rank, int64_t rows_per_rank,
+                              int64_t n, int dtype);
+
 /* Decode-shaped matmul (M <= 8) that allocates nothing, for callers that are not allowed to call
  * cudaMalloc (a plug-in inside another framework's stream-ordered region, a serving loop that must not touch
  * the allocator once warm). No counterpart in the reference: its CPU backend takes split buffers from a

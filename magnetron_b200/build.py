@@ -21,7 +21,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "lib")
 OBJ = os.path.join(PKG, "build")
-CU_SOURCES = ["cabi.cu", "cast.cu", "gemv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "skinny_noalloc.cu"]
+CU_SOURCES = ["cabi.cu", "cast.cu", "gemv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "skinny_noalloc.cu", "tp_reduce.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

@@ -532,6 +532,48 @@ int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y,
     return matmul_device(*d, device, x, y, r);
 }
 
+int magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_view_t *y, void *const *peer_stage, int nranks, int rank) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!peer_stage || nranks < 1 || nranks > 8 || rank < 0 || rank >= nranks) { set_error("matmul_scatter: bad rank %d of %d", rank, nranks); return MAGB200_ERR_INVALID_ARG; }
+    if ((rc = check_view(x, "matmul x")) || (rc = check_view(y, "matmul y"))) return rc;
+    if (x->rank != 2 || y->rank != 2) { set_error("matmul_scatter: 2-D operands only"); return MAGB200_ERR_INVALID_ARG; }
+    // the partial product has no home of its own: describe it as an [M,N] view of this rank's staging buffer for validation
+    magb200_view_t r;
+    memset(&r, 0, sizeof(r));
+    r.base = peer_stage[rank]; r.dtype = x->dtype; r.rank = 2;
+    r.shape[0] = x->shape[0]; r.shape[1] = y->shape[1]; r.strides[0] = y->shape[1]; r.strides[1] = 1;
+    FullProblem fp;
+    if ((rc = build_problem(x, y, &r, fp))) return rc;
+    const GemmProblem &g = fp.g;
+    if (g.nbatch != 0 || fp.n_outer != 0 || !tcgen05_supported(g) || g.M % nranks || g.N % 8) {
+        set_error("matmul_scatter: needs a 16-bit, TMA-describable, unbatched problem with M divisible by the rank count and N by 8 "
+                  "(M=%lld N=%lld K=%lld ranks=%d)", (long long)g.M, (long long)g.N, (long long)g.K, nranks);
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    ScatterTarget sc;
+    sc.ranks = nranks; sc.rank = rank; sc.rows_per_rank = g.M / nranks;
+    for (int i = 0; i < 8; ++i) sc.stage[i] = i < nranks ? peer_stage[i] : nullptr;
+    for (int i = 0; i < nranks; ++i)
+        if (!sc.stage[i] || ((uintptr_t)sc.stage[i] & 15u)) { set_error("matmul_scatter: staging pointer of rank %d is null or misaligned", i); return MAGB200_ERR_INVALID_ARG; }
+    if (tcgen05_2sm_preferred(g)) {
+        g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
+        return launch_gemm_tcgen05_2sm(g, d->stream, d->cta_limit, d->status, &sc);
+    }
+    g_last_kernel = MAGB200_KERNEL_TCGEN05;
+    return launch_gemm_tcgen05(g, d->stream, d->cta_limit, d->status, &sc);
+}
+
+int magb200_reduce_broadcast(int device, const void *stage, void *const *peer_out, int nranks, int rank, int64_t rows_per_rank,
+                             int64_t n, int dtype) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!stage || !peer_out || rows_per_rank < 1 || n < 1) { set_error("reduce_broadcast: null pointer or empty block"); return MAGB200_ERR_INVALID_ARG; }
+    return launch_reduce_broadcast(dtype, stage, peer_out, nranks, rank, rows_per_rank * n, d->stream);
+}
+
 int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }

@@ -112,10 +112,17 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk);
 bool tcgen05_supported(const GemmProblem &p);
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev);
+// Destination of a scatter epilogue: every rank's staging buffer [ranks][rows_per_rank][N] (device or peer-mapped pointers)
+struct ScatterTarget {
+    int ranks, rank;
+    int64_t rows_per_rank;
+    void *stage[8];
+};
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr);
 bool tcgen05_2sm_supported(const GemmProblem &p);
 bool tcgen05_2sm_preferred(const GemmProblem &p);
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev);
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr);
+int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems, cudaStream_t stream);
 
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
                 const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);

@@ -32,6 +32,7 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr int kStatusTimeout = 1;
+constexpr int kMaxScatterRanks = 8;
 
 struct TcArgs {
     void *C;
@@ -44,7 +45,22 @@ struct TcArgs {
     int64_t tiles_m, tiles_n, total_tiles;
     int num_kb;
     int *status;
+    // scatter epilogue (tensor-parallel row-sharded GEMM): rows of block o go to rank o's staging buffer, slot `rank`
+    int scatter_ranks;                  // 0: plain epilogue into C
+    int scatter_rank;
+    int64_t rows_per_rank;
+    void *peer_stage[kMaxScatterRanks]; // staging buffer of every rank: [ranks][rows_per_rank][N] elements
 };
+
+// Where output row `row` of batch `batch` starts. In scatter mode the row belongs to the rank that owns its row block and
+// lands in that rank's staging buffer (an ordinary store through a peer mapping), in the slot of the sending rank.
+__device__ __forceinline__ uint16_t *output_row(const TcArgs &a, int64_t batch, int64_t row) {
+    if (a.scatter_ranks == 0) return reinterpret_cast<uint16_t *>(a.C) + (batch * a.M + row) * a.N;
+    const int64_t owner = row / a.rows_per_rank;
+    const int64_t local = row - owner * a.rows_per_rank;
+    return reinterpret_cast<uint16_t *>(a.peer_stage[owner < a.scatter_ranks ? owner : 0]) +
+           ((int64_t)a.scatter_rank * a.rows_per_rank + local) * a.N;
+}
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -293,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
-            uint16_t *crow = reinterpret_cast<uint16_t *>(args.C) + (batch * args.M + row) * args.N + n0;
+            uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
@@ -545,7 +561,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
-            uint16_t *crow = reinterpret_cast<uint16_t *>(args.C) + (batch * args.M + row) * args.N + n0;
+            uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
 #pragma unroll 1
             for (int c = 0; c < BN2; c += 32) {
                 uint32_t r[32];
@@ -784,7 +800,7 @@ bool tcgen05_2sm_preferred(const GemmProblem &p) {
     return tiles >= kNumSMsB200 / 2;
 }
 
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev) {
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
     OperandDesc a, b;
     int amn = 0, bmn = 0;
     if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn)) {
@@ -804,10 +820,14 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
     }
     args.num_kb = (int)((p.K + BK - 1) / BK);
     args.status = status_word_dev;
+    if (scatter) {
+        args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
+        for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
+    }
     return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16>(p, ta, tb, args, st, cta_limit) : launch_2sm<MAGB200_F16>(p, ta, tb, args, st, cta_limit);
 }
 
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev) {
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
     const int bn = pick_bn(p);
     OperandDesc a, b;
     int amn = 0, bmn = 0;
@@ -828,6 +848,10 @@ int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, in
     }
     args.num_kb = (int)((p.K + BK - 1) / BK);
     args.status = status_word_dev;
+    if (scatter) {
+        args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
+        for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
+    }
 #define LAUNCH(BNV)                                                                                   \
     return p.dtype == MAGB200_BF16 ? launch_cfg<BNV, MAGB200_BF16>(p, ta, tb, args, st, cta_limit)                \
                                    : launch_cfg<BNV, MAGB200_F16>(p, ta, tb, args, st, cta_limit)

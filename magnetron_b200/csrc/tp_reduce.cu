@@ -1,0 +1,76 @@
+// Second half of the fused row-sharded linear: sum the partial row blocks that the peers' GEMM epilogues pushed into this
+// rank's staging buffer, round once, and write the finished rows into every rank's output (ordinary 128-bit stores through
+// peer mappings: an all-gather without a separate collective).
+//
+// Staging layout on every rank: [ranks][rows_per_rank * N] elements; slot s holds rank s's partial product for the row
+// block this rank owns. Partials arrive already rounded to the 16-bit storage type; they are summed in fp32 in slot order
+// (reproducible) and rounded once more -- fewer roundings than a ring all-reduce, which rounds at every hop.
+#include "common.cuh"
+
+namespace magb200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = 8;
+
+struct PeerOut { void *p[kMaxRanks]; };
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads) reduce_broadcast_kernel(const uint4 *__restrict__ stage, PeerOut out, int ranks, int rank,
+                                                                   int64_t block_vecs) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < block_vecs; i += stride) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int s = 0; s < ranks; ++s) {
+            const uint4 v = __ldcs(stage + (int64_t)s * block_vecs + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if constexpr (DT == MAGB200_BF16) {
+                    acc[2 * j] += __uint_as_float(w[j] << 16);
+                    acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+                    acc[2 * j] += f.x;
+                    acc[2 * j + 1] += f.y;
+                }
+            }
+        }
+        uint4 o;
+        o.x = pack2_from_f32<DT>(acc[0], acc[1]);
+        o.y = pack2_from_f32<DT>(acc[2], acc[3]);
+        o.z = pack2_from_f32<DT>(acc[4], acc[5]);
+        o.w = pack2_from_f32<DT>(acc[6], acc[7]);
+        for (int d = 0; d < ranks; ++d)
+            reinterpret_cast<uint4 *>(out.p[d])[(int64_t)rank * block_vecs + i] = o;
+    }
+}
+
+}  // namespace
+
+int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems,
+                            cudaStream_t stream) {
+    if (ranks < 1 || ranks > kMaxRanks || rank < 0 || rank >= ranks) { set_error("reduce_broadcast: bad rank %d of %d", rank, ranks); return MAGB200_ERR_INVALID_ARG; }
+    if (block_elems % 8 || ((uintptr_t)stage & 15u)) { set_error("reduce_broadcast: the row block must be a multiple of 8 elements and 16-byte aligned"); return MAGB200_ERR_INVALID_ARG; }
+    PeerOut out;
+    for (int i = 0; i < kMaxRanks; ++i) out.p[i] = i < ranks ? peer_out[i] : nullptr;
+    for (int i = 0; i < ranks; ++i)
+        if (!out.p[i] || ((uintptr_t)out.p[i] & 15u)) { set_error("reduce_broadcast: output pointer of rank %d is null or misaligned", i); return MAGB200_ERR_INVALID_ARG; }
+    const int64_t vecs = block_elems / 8;
+    int64_t blocks = (vecs + kThreads - 1) / kThreads;
+    if (blocks > kNumSMsB200 * 8) blocks = kNumSMsB200 * 8;
+    if (blocks < 1) return MAGB200_OK;
+    if (dtype == MAGB200_BF16)
+        reduce_broadcast_kernel<MAGB200_BF16><<<(unsigned)blocks, kThreads, 0, stream>>>((const uint4 *)stage, out, ranks, rank, vecs);
+    else if (dtype == MAGB200_F16)
+        reduce_broadcast_kernel<MAGB200_F16><<<(unsigned)blocks, kThreads, 0, stream>>>((const uint4 *)stage, out, ranks, rank, vecs);
+    else { set_error("reduce_broadcast: 16-bit dtypes only"); return MAGB200_ERR_INVALID_ARG; }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
+}  // namespace magb200

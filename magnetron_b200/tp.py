@@ -97,11 +97,49 @@ def cabi_matmul(device: int, reserve_sms: int = 0) -> Callable[[torch.Tensor, to
     return matmul
 
 
+class FusedRowLinear:
+    """Row-sharded linear whose exchange is fused into the GEMM: the tensor-core kernel's epilogue stores every finished
+    tile into the staging buffer of the rank that owns those rows (peer-mapped symmetric memory, under the main loop), a
+    symmetric-memory barrier orders the ranks, then `magb200_reduce_broadcast` sums the partial blocks and writes the
+    finished rows into every rank's output. Symmetric memory and the barrier come from torch (plumbing); both kernels are
+    this package's."""
+
+    def __init__(self, m: int, n: int, dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        import magnetron_b200 as mb
+        self.mb, self.L = mb, mb.lib()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if m % self.world:
+            raise ValueError(f"token count {m} must be divisible by the {self.world} ranks")
+        self.m, self.n, self.dev = m, n, device.index or 0
+        self.stage = symm_mem.empty((self.world, m // self.world, n), dtype=dtype, device=device)
+        self.out = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self.h_stage = symm_mem.rendezvous(self.stage, self.group)
+        self.h_out = symm_mem.rendezvous(self.out, self.group)
+        self.stage_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.h_stage.buffer_ptrs])
+        self.out_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.h_out.buffer_ptrs])
+        self.dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16}[dtype]
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        mb = self.mb
+        n, k = w.shape
+        xv = mb.make_view(x.data_ptr(), self.dt, tuple(x.shape), tuple(x.stride()))
+        wv = mb.make_view(w.data_ptr(), self.dt, (k, n), (w.stride(1), w.stride(0)))
+        mb.check(self.L.magb200_matmul_scatter(self.dev, C.byref(xv), C.byref(wv), self.stage_ptrs, self.world, self.rank))
+        self.h_stage.barrier(channel=0)       # every rank's partial tiles have landed
+        mb.check(self.L.magb200_reduce_broadcast(self.dev, C.c_void_p(self.stage.data_ptr()), self.out_ptrs, self.world, self.rank,
+                                                 self.m // self.world, self.n, self.dt))
+        self.h_out.barrier(channel=1)         # every rank's rows have landed, and every staging buffer may be reused
+        return self.out
+
+
 class TPLayer:
     """The sharded linears of one layer on this rank, with resident weight shards and preallocated outputs."""
 
     def __init__(self, specs: Sequence[ShardedLinear], m: int, *, device: torch.device, dtype=torch.bfloat16,
-                 matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4, reserve_sms: int = 0):
+                 matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4, reserve_sms: int = 0,
+                 fused: bool = False):
         self.specs, self.m, self.group = tuple(specs), m, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -111,6 +149,7 @@ class TPLayer:
             matmul = cabi_matmul(device.index or 0, reserve_sms)
         self.matmul = matmul
         self.chunks = max(1, min(chunks, m // 512)) if m >= 1024 else 1
+        self.fused = {}
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.w, self.x, self.y = {}, {}, {}
         for s in self.specs:
@@ -131,7 +170,11 @@ class TPLayer:
                 self.w[s.name] = (torch.randn((n_loc, k_loc), generator=g2, dtype=torch.float32) * 0.02).to(dtype).to(device)
             xin = torch.randn((m, k_loc), generator=torch.Generator(device="cpu").manual_seed(seed + 17), dtype=torch.float32)
             self.x[s.name] = xin.to(dtype).to(device)
-            self.y[s.name] = torch.empty((m, n_loc), dtype=dtype, device=device)
+            if fused and s.kind == "row" and self.world > 1 and m % self.world == 0 and m >= 256:
+                self.fused[s.name] = FusedRowLinear(m, s.n, dtype, device, group)
+                self.y[s.name] = self.fused[s.name].out
+            else:
+                self.y[s.name] = torch.empty((m, n_loc), dtype=dtype, device=device)
 
     # -- one linear ---------------------------------------------------------------------------
     def column(self, name: str, gather: bool = False):
@@ -163,6 +206,16 @@ class TPLayer:
         for s in self.specs:
             if s.kind == "col":
                 self.column(s.name, gather=gather_outputs)
+            else:
+                self.row(s.name)
+
+    def step_fused(self) -> None:
+        """Op by op, the row-sharded linears through the fused GEMM + exchange kernels."""
+        for s in self.specs:
+            if s.kind == "col":
+                self.column(s.name)
+            elif s.name in self.fused:
+                self.fused[s.name](self.x[s.name], self.w[s.name])
             else:
                 self.row(s.name)
 

@@ -245,6 +245,40 @@ def test_two_sm_kernel(gpu, xs, xT, ys, wT, dname):
         t.release()
 
 
+@pytest.mark.parametrize("ranks,M,N,K", [(2, 512, 512, 512), (4, 1024, 384, 2048), (8, 2048, 5120, 1024)])
+def test_fused_row_sharded_linear_emulated_ranks(gpu, ranks, M, N, K):
+    """The fused row-sharded linear (scatter epilogue + reduce-broadcast) with all ranks emulated on one GPU: rank r
+    multiplies its K slice and pushes row block o of the partial product into rank o's staging slot r; every owner then sums
+    its slots and writes its rows into every rank's output. All outputs must be identical and match the unsharded product."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(23)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.05)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    R_ = M // ranks
+    stages = [mb.Tensor(gpu, dt, (ranks, R_, N)) for _ in range(ranks)]
+    outs = [mb.Tensor(gpu, dt, (M, N)) for _ in range(ranks)]
+    stage_ptrs = (C.c_void_p * ranks)(*[t.ptr for t in stages])
+    out_ptrs = (C.c_void_p * ranks)(*[t.ptr for t in outs])
+    kp = K // ranks
+    for r in range(ranks):
+        xr = tx.slice(1, r * kp, kp)                 # this rank's K slice of the activations: a strided view
+        wr = tw.slice(1, r * kp, kp).T               # and of the weight, seen as W.T
+        mb.check(L.magb200_matmul_scatter(gpu, C.byref(xr.view_struct()), C.byref(wr.view_struct()), stage_ptrs, ranks, r))
+        assert mb.last_kernel().startswith("tcgen05")
+    for o in range(ranks):
+        mb.check(L.magb200_reduce_broadcast(gpu, stages[o].ptr, out_ptrs, ranks, o, R_, N, dt))
+    mb.synchronize(gpu)
+    got = [t.to_bits() for t in outs]
+    for g in got[1:]:
+        assert np.array_equal(g, got[0])
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    m = O.error_metrics(dt, got[0], xf @ wf.T, np.abs(xf) @ np.abs(wf).T)
+    assert m["e"] <= (ranks + 1) * unit_roundoff(dt) + K * 2.0 ** -24, m      # one rounding per partial + one for the sum
+    for t in stages + outs + [tx, tw]:
+        t.release()
+
+
 def test_host_buffer_matmul(gpu):
     dt = O.BFLOAT16
     rng = np.random.default_rng(8)
