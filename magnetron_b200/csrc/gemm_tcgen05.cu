@@ -383,7 +383,9 @@ struct Cfg2 {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = 6;
     static constexpr int kTmemCols = 2 * BN2;
-    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256;
+    static constexpr int kEpiPitch = 64 * 2 + 16;                 // 64 output columns per pass + 16 bytes: conflict-free both ways
+    static constexpr int kEpiWarpBytes = 32 * kEpiPitch;          // one epilogue warp stages its 32 rows
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256 + 4 * kEpiWarpBytes;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -561,14 +563,19 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
-            uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
+            if (vec_ok) {
+                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane), then 8 lanes write one
+                // row's 128 contiguous bytes, so global (and peer) stores are full 128-byte segments instead of 16-byte pieces
+                // scattered over 32 rows.
+                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + 256 + (size_t)(warp - 2) * C::kEpiWarpBytes;
+                const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
 #pragma unroll 1
-            for (int c = 0; c < BN2; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c, r);
-                tmem_ld_wait();
-                if (row < args.M && n0 + c < args.N) {
-                    if (vec_ok && n0 + c + 32 <= args.N) {
+                for (int c0 = 0; c0 < BN2; c0 += 64) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c0 + 32 * h, r);
+                        tmem_ld_wait();
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
                             uint4 o;
@@ -576,14 +583,35 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                             o.y = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
                             o.z = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
                             o.w = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                            *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + h * 64 + v * 16) = o;
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));
                     }
+                    __syncwarp();
+                    const int64_t col = n0 + c0 + (lane & 7) * 8;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3);
+                        const int64_t grow = row0 + rr;
+                        if (grow < args.M && col < args.N) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * C::kEpiPitch + (lane & 7) * 16);
+                            *reinterpret_cast<uint4 *>(output_row(args, batch, grow) + col) = v;
+                        }
+                    }
+                    __syncwarp();
                 }
+            } else {
+            uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
+#pragma unroll 1
+            for (int c = 0; c < BN2; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c, r);
+                tmem_ld_wait();
+                if (row < args.M && n0 + c < args.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));
+                }
+            }
             }
             tcgen05_fence_before();
             __syncwarp();
