@@ -6,8 +6,8 @@
 Outputs land in `magnetron_b200/lib/`:
   libmagnetron_b200.so   the C ABI of include/magnetron_b200.h (kernels + host front-end)
   libmagnetron_cuda.so   the same objects plus the magnetron backend module (C host code compiled
-                         against the magnetron headers found under $MAGNETRON_SRC, default
-                         /root/reference); skipped with a note when those headers are absent.
+                         against the magnetron headers found under $MAGNETRON_SRC); skipped with a note when
+                         those headers are absent.
 """
 from __future__ import annotations
 

@@ -90,6 +90,23 @@ template <> __device__ __forceinline__ uint32_t pack2_from_f32<MAGB200_F16>(floa
     return f32_bits_to_f16_bits(__float_as_uint(lo)) | (f32_bits_to_f16_bits(__float_as_uint(hi)) << 16);
 }
 
+// Matmul epilogues round with the hardware converters (one instruction per pair). They differ from the integer formulas above
+// only in the bit pattern of a NaN result (0x7FFF instead of 0x7FC0 / a payload): a matmul produces NaN only from NaN or
+// infinite inputs, and the reference's own NaN encoding there depends on which CPU specialisation stored the tile
+// (magnetron/cpu/mag_cpu_impl_ops_matmul.inl:655-662 vs :772-778), so there is no single pattern to match. Casts keep the
+// integer formulas and stay bit-exact.
+template <int DT> __device__ __forceinline__ uint32_t pack2_rn(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2_rn<MAGB200_BF16>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+template <> __device__ __forceinline__ uint32_t pack2_rn<MAGB200_F16>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
 // ---- canonical description of one matmul, produced by the front-end in cabi.cu -----------------
 constexpr int kMaxBatchDims = 3;
 struct GemmProblem {

@@ -320,10 +320,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
                             uint4 o;
-                            o.x = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            o.x = pack2_rn<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2_rn<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2_rn<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2_rn<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
                             *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
                         }
                     } else {
@@ -372,9 +372,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //   empty[s]   one per CTA; the leader's MMA thread issues two tcgen05.commit per K block, one to its own barrier and one
 //              to the peer's (a shared::cluster address), so both producers learn at once that the stage is free.
 //   tfull[a]   accumulator a complete: likewise committed to both CTAs' barriers.
-//   tempty[a]  accumulator a drained: the 4 epilogue warps of BOTH CTAs arrive on the leader's barrier (count 8).
+//   tempty[a]  accumulator a drained: the 8 epilogue warps of BOTH CTAs arrive on the leader's barrier (count 16).
 // =====================================================================================================================
-constexpr int kThreads2 = 192;  // warp 0 TMA, warp 1 MMA (leader only), warps 2-5 epilogue
+constexpr int kThreads2 = 320;  // warp 0 TMA, warp 1 MMA (leader only), warps 2-9 epilogue (two per TMEM lane quarter)
 constexpr int BN2 = 256;
 
 struct Cfg2 {
@@ -383,9 +383,11 @@ struct Cfg2 {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = 6;
     static constexpr int kTmemCols = 2 * BN2;
-    static constexpr int kEpiPitch = 64 * 2 + 16;                 // 64 output columns per pass + 16 bytes: conflict-free both ways
+    static constexpr int kEpiWarps = 8;                           // two warps per TMEM lane quarter, 128 columns each
+    static constexpr int kEpiCols = 32;                           // output columns per staging pass
+    static constexpr int kEpiPitch = kEpiCols * 2 + 16;           // 80 bytes: lanes 20 words apart, conflict-free row writes
     static constexpr int kEpiWarpBytes = 32 * kEpiPitch;          // one epilogue warp stages its 32 rows
-    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256 + 4 * kEpiWarpBytes;
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256 + kEpiWarps * kEpiWarpBytes;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -443,7 +445,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tfull0 + 8u * i, 1); mbar_init(tempty0 + 8u * i, 8); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull0 + 8u * i, 1); mbar_init(tempty0 + 8u * i, 2 * C::kEpiWarps); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -548,7 +550,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             }
         }
     } else {
-        // ===================== epilogue (4 warps per CTA, this CTA's 128 accumulator rows) =====================
+        // ===================== epilogue (8 warps per CTA, this CTA's 128 accumulator rows) =====================
         const int quarter = warp & 3;
         uint32_t titer = 0;
         bool ok = true;
@@ -563,37 +565,37 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
+            const int chalf = (warp - 2) >> 2;            // which 128-column half of the tile this warp drains
             if (vec_ok) {
-                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane), then 8 lanes write one
-                // row's 128 contiguous bytes, so global (and peer) stores are full 128-byte segments instead of 16-byte pieces
-                // scattered over 32 rows.
+                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane), then 4 lanes write one
+                // row's 64 contiguous bytes, so global (and peer) stores are whole segments instead of 16-byte pieces scattered
+                // over 32 rows. The next TMEM load is issued before the current patch is written out.
                 unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + 256 + (size_t)(warp - 2) * C::kEpiWarpBytes;
                 const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
+                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * (BN2 / 2);
+                uint32_t r[32];
+                tmem_ld_32x32(tbase, r);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN2; c0 += 64) {
+                for (int c0 = 0; c0 < BN2 / 2; c0 += C::kEpiCols) {
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c0 + 32 * h, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2_from_f32<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + h * 64 + v * 16) = o;
-                        }
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        o.x = pack2_rn<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                        o.y = pack2_rn<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                        o.z = pack2_rn<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                        o.w = pack2_rn<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + v * 16) = o;
                     }
+                    if (c0 + C::kEpiCols < BN2 / 2) tmem_ld_32x32(tbase + c0 + C::kEpiCols, r);   // in flight during the write-out
                     __syncwarp();
-                    const int64_t col = n0 + c0 + (lane & 7) * 8;
+                    const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 3) * 8;
 #pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rr = it * 4 + (lane >> 3);
+                    for (int it = 0; it < 4; ++it) {
+                        const int rr = it * 8 + (lane >> 2);
                         const int64_t grow = row0 + rr;
                         if (grow < args.M && col < args.N) {
-                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * C::kEpiPitch + (lane & 7) * 16);
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * C::kEpiPitch + (lane & 3) * 16);
                             *reinterpret_cast<uint4 *>(output_row(args, batch, grow) + col) = v;
                         }
                     }
@@ -602,7 +604,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             } else {
             uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
 #pragma unroll 1
-            for (int c = 0; c < BN2; c += 32) {
+            for (int c = chalf * (BN2 / 2); c < (chalf + 1) * (BN2 / 2); c += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c, r);
                 tmem_ld_wait();
@@ -615,7 +617,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 8 epilogue warps
+            if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 16 epilogue warps of the pair
         }
     }
 

@@ -40,10 +40,10 @@ __global__ void __launch_bounds__(kThreads) reduce_broadcast_kernel(const uint4 
             }
         }
         uint4 o;
-        o.x = pack2_from_f32<DT>(acc[0], acc[1]);
-        o.y = pack2_from_f32<DT>(acc[2], acc[3]);
-        o.z = pack2_from_f32<DT>(acc[4], acc[5]);
-        o.w = pack2_from_f32<DT>(acc[6], acc[7]);
+        o.x = pack2_rn<DT>(acc[0], acc[1]);
+        o.y = pack2_rn<DT>(acc[2], acc[3]);
+        o.z = pack2_rn<DT>(acc[4], acc[5]);
+        o.w = pack2_rn<DT>(acc[6], acc[7]);
         for (int d = 0; d < ranks; ++d)
             reinterpret_cast<uint4 *>(out.p[d])[(int64_t)rank * block_vecs + i] = o;
     }

@@ -65,7 +65,7 @@ def gate(dtype: int, got_bits, ref_bits, truth, scale, K: int):
 
 def reference_defect_mask(name: str, dtype: int, result_shape) -> np.ndarray:
     """Result elements on which the reference CPU backend itself is wrong at this snapshot (found by
-    comparing it with the fp64 truth; the probe and the causes are written up in DESIGN.md):
+    comparing it with the fp64 truth on plain contiguous inputs):
       * float32 / bfloat16 blocked kernel: when N is not a multiple of 8, the scalar loop that handles
         the last N % 8 columns reads the packed A panel as if it were row-major
         (magnetron/cpu/mag_cpu_impl_ops_matmul.inl:2744-2754, :2785-2796 against the k-major 8-row

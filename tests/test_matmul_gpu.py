@@ -279,6 +279,30 @@ def test_fused_row_sharded_linear_emulated_ranks(gpu, ranks, M, N, K):
         t.release()
 
 
+def test_attention_scores_full_size(gpu):
+    """Q[8x32x2048x128] @ K^T with K [8x8x2048x128] broadcast over 4 query heads per KV head (seed 4), at full size:
+    549 GFLOP, a 2.1 GB result. fp64 truth on sampled (batch, head, row) triples; the 4 query heads of a group really
+    read the same K (row of head g against K of its KV head)."""
+    dt = O.BFLOAT16
+    B, KV, G, T, D = 8, 8, 4, 2048, 128
+    rng = np.random.default_rng(4)
+    q = bits(dt, rng, (B, KV, G, T, D), 1.0)
+    k = bits(dt, rng, (B, KV, T, D), 1.0)
+    tq, tk = mb.Tensor.from_bits(gpu, dt, q), mb.Tensor.from_bits(gpu, dt, k)
+    s = tq @ tk.transpose(2, 3).view((B, KV, 1, D, T))
+    assert s.shape == (B, KV, G, T, T) and mb.last_kernel().startswith("tcgen05")
+    mb.synchronize(gpu)
+    for _ in range(24):
+        b, h, g, t = (int(rng.integers(0, n)) for n in (B, KV, G, T))
+        row = mb.Tensor(gpu, dt, (T,), base_ptr=s.ptr, offset=(((b * KV + h) * G + g) * T + t) * T, storage_elems=s.numel).to_bits()
+        qf, kf = O.bits_to_f64(dt, q[b, h, g, t]), O.bits_to_f64(dt, k[b, h])
+        truth = kf @ qf
+        m = O.error_metrics(dt, row, truth, np.abs(kf) @ np.abs(qf))
+        assert m["e"] <= unit_roundoff(dt) + D * 2.0 ** -24, (b, h, g, t, m)
+    for t_ in (s, tq, tk):
+        t_.release()
+
+
 def test_host_buffer_matmul(gpu):
     dt = O.BFLOAT16
     rng = np.random.default_rng(8)
