@@ -139,8 +139,9 @@ int  magb200_force_kernel(int kernel);
  * every rank's output. `peer_stage[i]` / `peer_out[i]` are device addresses valid on THIS device for rank i's
  * buffers (peer-mapped; [nranks][M/nranks][N] and [M][N] elements). M must be divisible by nranks. */
 int  magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_view_t *y, void *const *peer_stage, int nranks, int rank);
-int  magb200_reduce_broadcast(int device, const void *stage, void *const *peer_out, int nranks, int rank, int64_t rows_per_rank,
-                              int64_t n, int dtype);
+int  magb200_reduce_broadcast(int device, void *cuda_stream, const void *stage, void *const *peer_out, int nranks, int rank,
+                              int64_t rows_per_rank, int64_t n, int dtype);   /* cuda_stream NULL = the device's stream; another
+                              stream lets the exchange of one token chunk run beside the next chunk's GEMMs */
 
 /* Decode-shaped matmul (M <= 8) that allocates nothing, for callers that are not allowed to call
  * cudaMalloc (a plug-in inside another framework's stream-ordered region, a serving loop that must not touch

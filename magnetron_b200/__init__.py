@@ -79,7 +79,7 @@ SIGNATURES = {
     "magb200_launch_count_reset": (None, []),
     "magb200_force_kernel": (C.c_int, [C.c_int]),
     "magb200_matmul_scatter": (C.c_int, [C.c_int, _VP, _VP, C.POINTER(C.c_void_p), C.c_int, C.c_int]),
-    "magb200_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int]),
+    "magb200_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int]),
     "magb200_matmul_skinny_noalloc": (C.c_int, [C.c_int, C.c_void_p, _VP, _VP, _VP]),
     "magb200_matmul_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP, C.c_size_t, _VP]),
     "magb200_cast_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP]),

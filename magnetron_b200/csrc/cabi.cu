@@ -565,13 +565,13 @@ int magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_vi
     return launch_gemm_tcgen05(g, d->stream, d->cta_limit, d->status, &sc);
 }
 
-int magb200_reduce_broadcast(int device, const void *stage, void *const *peer_out, int nranks, int rank, int64_t rows_per_rank,
-                             int64_t n, int dtype) {
+int magb200_reduce_broadcast(int device, void *cuda_stream, const void *stage, void *const *peer_out, int nranks, int rank,
+                             int64_t rows_per_rank, int64_t n, int dtype) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
     if (!stage || !peer_out || rows_per_rank < 1 || n < 1) { set_error("reduce_broadcast: null pointer or empty block"); return MAGB200_ERR_INVALID_ARG; }
-    return launch_reduce_broadcast(dtype, stage, peer_out, nranks, rank, rows_per_rank * n, d->stream);
+    return launch_reduce_broadcast(dtype, stage, peer_out, nranks, rank, rows_per_rank * n, cuda_stream ? (cudaStream_t)cuda_stream : d->stream);
 }
 
 int magb200_last_kernel(void) { return g_last_kernel; }

@@ -121,17 +121,29 @@ class FusedRowLinear:
         self.out_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.h_out.buffer_ptrs])
         self.dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16}[dtype]
 
-    def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def scatter(self, x: torch.Tensor, w: torch.Tensor) -> None:
+        """First half, on the current stream: the GEMM whose epilogue pushes tiles to their owners, then the barrier after
+        which every rank's partial tiles have landed."""
         mb = self.mb
         n, k = w.shape
         xv = mb.make_view(x.data_ptr(), self.dt, tuple(x.shape), tuple(x.stride()))
         wv = mb.make_view(w.data_ptr(), self.dt, (k, n), (w.stride(1), w.stride(0)))
         mb.check(self.L.magb200_matmul_scatter(self.dev, C.byref(xv), C.byref(wv), self.stage_ptrs, self.world, self.rank))
-        self.h_stage.barrier(channel=0)       # every rank's partial tiles have landed
-        mb.check(self.L.magb200_reduce_broadcast(self.dev, C.c_void_p(self.stage.data_ptr()), self.out_ptrs, self.world, self.rank,
-                                                 self.m // self.world, self.n, self.dt))
-        self.h_out.barrier(channel=1)         # every rank's rows have landed, and every staging buffer may be reused
+        self.h_stage.barrier(channel=0)
+
+    def finish(self) -> torch.Tensor:
+        """Second half, on the current stream (which may be a side stream): sum the partial blocks, write the finished
+        rows to every rank, and the barrier after which all rows have landed and the staging buffers may be reused."""
+        stream = torch.cuda.current_stream(self.out.device).cuda_stream
+        self.mb.check(self.L.magb200_reduce_broadcast(self.dev, C.c_void_p(stream) if stream else None,
+                                                      C.c_void_p(self.stage.data_ptr()), self.out_ptrs, self.world, self.rank,
+                                                      self.m // self.world, self.n, self.dt))
+        self.h_out.barrier(channel=1)
         return self.out
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        self.scatter(x, w)
+        return self.finish()
 
 
 class TPLayer:
@@ -150,6 +162,8 @@ class TPLayer:
         self.matmul = matmul
         self.chunks = max(1, min(chunks, m // 512)) if m >= 1024 else 1
         self.fused = {}
+        self.fused_chunks = {}
+        self.side_stream = None
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.w, self.x, self.y = {}, {}, {}
         for s in self.specs:
@@ -173,6 +187,10 @@ class TPLayer:
             if fused and s.kind == "row" and self.world > 1 and m % self.world == 0 and m >= 256:
                 self.fused[s.name] = FusedRowLinear(m, s.n, dtype, device, group)
                 self.y[s.name] = self.fused[s.name].out
+                mc = m // self.chunks
+                if self.chunks > 1 and m % self.chunks == 0 and mc % self.world == 0:
+                    # one exchange object per token chunk, so chunks can be in flight at the same time
+                    self.fused_chunks[s.name] = [FusedRowLinear(mc, s.n, dtype, device, group) for _ in range(self.chunks)]
             else:
                 self.y[s.name] = torch.empty((m, n_loc), dtype=dtype, device=device)
 
@@ -218,6 +236,47 @@ class TPLayer:
                 self.fused[s.name](self.x[s.name], self.w[s.name])
             else:
                 self.row(s.name)
+
+    def step_fused_pipelined(self) -> None:
+        """Token chunks through the layer with the fused exchange: the scatter GEMM of a chunk runs on the main stream, its
+        reduce-broadcast on a side stream beside the next chunk's GEMMs (which leave SMs free for it); the column GEMM
+        that follows a row-sharded one waits for that chunk's exchange, as in a real layer."""
+        pairs = [(self.specs[i], self.specs[i + 1]) for i in range(0, len(self.specs) - 1, 2)
+                 if self.specs[i].kind == "col" and self.specs[i + 1].kind == "row"]
+        if 2 * len(pairs) != len(self.specs) or any(r.name not in self.fused_chunks for _, r in pairs):
+            return self.step_fused()
+        main = torch.cuda.current_stream()
+        if self.side_stream is None:
+            self.side_stream = torch.cuda.Stream(device=main.device)
+        side = self.side_stream
+        mc = self.m // self.chunks
+        done = {}
+
+        def run_pair(pi, ci):
+            col, row = pairs[pi]
+            lo, hi = ci * mc, (ci + 1) * mc
+            if pi > 0:
+                main.wait_event(done.pop((pi - 1, ci)))
+            self.matmul(self.x[col.name][lo:hi], self.w[col.name], self.y[col.name][lo:hi])
+            ex = self.fused_chunks[row.name][ci]
+            ex.scatter(self.x[row.name][lo:hi], self.w[row.name])
+            ready = torch.cuda.Event()
+            ready.record(main)
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                ex.finish()
+                ev = torch.cuda.Event()
+                ev.record(side)
+            done[(pi, ci)] = ev
+
+        n_p, n_c = len(pairs), self.chunks
+        for wave in range(n_c + n_p - 1):
+            for pi in range(n_p):
+                ci = wave - pi
+                if 0 <= ci < n_c:
+                    run_pair(pi, ci)
+        for ev in done.values():
+            main.wait_event(ev)
 
     def step_pipelined(self) -> None:
         """One layer, token chunks in flight: [col, row, all-reduce] pairs per chunk; the column GEMM that follows a

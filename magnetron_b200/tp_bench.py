@@ -78,14 +78,29 @@ def main(args, pk):
     ms = _time_steps(layer.step_pipelined, steps, warmup, device)
     launches = int(mb.lib().magb200_launch_count()) * steps // (steps + warmup)
     ms_gather = _time_steps(lambda: layer.step(True), max(2, steps // 2), 2, device)
-    fused_tflops, fused_err = None, None
+    fused_tflops, fused_err, fused_parts, fused_pipe_tflops, ms_fp, fp_variants = None, None, None, None, None, None
     if world > 1:
         layer = None
         torch.cuda.empty_cache()
         try:
-            layer = tp.TPLayer(specs, M, device=device, reserve_sms=0, fused=True)
+            layer = tp.TPLayer(specs, M, device=device, reserve_sms=0, fused=True, chunks=1)
             ms_fused = _time_steps(layer.step_fused, steps, warmup, device)
             fused_tflops = flops * steps / ms_fused / 1e9
+            # the same exchange with token chunks in flight: which chunk count and how many SMs left free for the
+            # side-stream kernels pays depends on the rank count, so the candidates are timed and the best kept
+            fp_variants = {}
+            for n_chunks in (2, 4):
+                lay = tp.TPLayer(specs, M, device=device, reserve_sms=0, fused=True, chunks=n_chunks)
+                for free_sms in (0, reserve):
+                    mb.check(mb.lib().magb200_set_cta_limit(local, 148 - free_sms if free_sms else 0))
+                    t = _time_steps(lay.step_fused_pipelined, steps, warmup, device)
+                    fp_variants[f"chunks{n_chunks}_free{free_sms}"] = flops * steps / t / 1e9
+                    if ms_fp is None or t < ms_fp:
+                        ms_fp = t
+                mb.check(mb.lib().magb200_set_cta_limit(local, 0))
+                del lay
+                torch.cuda.empty_cache()
+            fused_pipe_tflops = flops * steps / ms_fp / 1e9
             # cross-check of the fused exchange against NCCL on the same operands
             ref = {}
             for s_ in specs:
@@ -99,6 +114,32 @@ def main(args, pk):
                     err = (layer.y[s_.name].float() - acc).abs().max() / acc.abs().max().clamp_min(1e-9)
                     ref[s_.name] = float(err)
             fused_err = ref
+            # where the fused exchange spends its time: the scatter GEMMs alone, and the reduce-broadcast kernels alone
+            import ctypes as C
+            L = mb.lib()
+            fl = [layer.fused[s_.name] for s_ in specs if s_.name in layer.fused]
+            names = [s_.name for s_ in specs if s_.name in layer.fused]
+
+            def scatter_only():
+                for f, nm in zip(fl, names):
+                    x, w = layer.x[nm], layer.w[nm]
+                    xv = mb.make_view(x.data_ptr(), f.dt, tuple(x.shape), tuple(x.stride()))
+                    wv = mb.make_view(w.data_ptr(), f.dt, (w.shape[1], w.shape[0]), (w.stride(1), w.stride(0)))
+                    mb.check(L.magb200_matmul_scatter(f.dev, C.byref(xv), C.byref(wv), f.stage_ptrs, f.world, f.rank))
+
+            def reduce_only():
+                for f in fl:
+                    mb.check(L.magb200_reduce_broadcast(f.dev, None, C.c_void_p(f.stage.data_ptr()), f.out_ptrs, f.world, f.rank,
+                                                        f.m // f.world, f.n, f.dt))
+
+            def barrier_only():
+                for f in fl:
+                    f.h_stage.barrier(channel=0)
+                    f.h_out.barrier(channel=1)
+
+            fused_parts = {"scatter_gemms_ms": _time_steps(scatter_only, steps, 2, device) / steps,
+                           "reduce_broadcast_ms": _time_steps(reduce_only, steps, 2, device) / steps,
+                           "four_barriers_ms": _time_steps(barrier_only, steps, 2, device) / steps}
         except Exception as e:   # symmetric memory is torch plumbing: report instead of failing the run
             fused_err = {"error": repr(e)[:300]}
     pipelined_tflops = flops * steps / ms / 1e9
@@ -109,6 +150,9 @@ def main(args, pk):
     if fused_tflops and fused_tflops > max(plain_tflops, pipelined_tflops):
         schedule = "op by op, row-sharded GEMMs fused with their exchange (scatter epilogue + reduce-broadcast over peer memory)"
         ms = ms_fused
+    if fused_pipe_tflops and fused_pipe_tflops > max(plain_tflops, pipelined_tflops, fused_tflops or 0.0):
+        schedule = "token chunks pipelined through the layer, row-sharded GEMMs fused with their exchange (reduce-broadcast on a side stream)"
+        ms = ms_fp
     value = flops * steps / ms / 1e9
     sweep = {}
     del layer
@@ -137,7 +181,8 @@ def main(args, pk):
             "schedule": schedule,
             "op_by_op_schedule": {"ms_per_step": ms_plain / max(2, steps // 2), "tflops": plain_tflops},
             "pipelined_schedule": {"tflops": pipelined_tflops},
-            "fused_exchange_schedule": {"tflops": fused_tflops, "max_rel_diff_vs_nccl": fused_err},
+            "fused_exchange_schedule": {"tflops": fused_tflops, "max_rel_diff_vs_nccl": fused_err, "parts": fused_parts},
+            "fused_exchange_pipelined_schedule": {"tflops": fused_pipe_tflops, "variants": fp_variants},
             "reserved_sms_for_collectives": reserve,
             "with_output_allgather": {"ms_per_step": ms_gather / max(2, steps // 2), "tflops": flops * max(2, steps // 2) / ms_gather / 1e9},
             "token_sweep": sweep,

@@ -267,7 +267,7 @@ def test_fused_row_sharded_linear_emulated_ranks(gpu, ranks, M, N, K):
         mb.check(L.magb200_matmul_scatter(gpu, C.byref(xr.view_struct()), C.byref(wr.view_struct()), stage_ptrs, ranks, r))
         assert mb.last_kernel().startswith("tcgen05")
     for o in range(ranks):
-        mb.check(L.magb200_reduce_broadcast(gpu, stages[o].ptr, out_ptrs, ranks, o, R_, N, dt))
+        mb.check(L.magb200_reduce_broadcast(gpu, None, stages[o].ptr, out_ptrs, ranks, o, R_, N, dt))
     mb.synchronize(gpu)
     got = [t.to_bits() for t in outs]
     for g in got[1:]:
