@@ -384,8 +384,8 @@ struct Cfg2 {
     static constexpr int kStages = 6;
     static constexpr int kTmemCols = 2 * BN2;
     static constexpr int kEpiWarps = 8;                           // two warps per TMEM lane quarter, 128 columns each
-    static constexpr int kEpiCols = 32;                           // output columns per staging pass
-    static constexpr int kEpiPitch = kEpiCols * 2 + 16;           // 80 bytes: lanes 20 words apart, conflict-free row writes
+    static constexpr int kEpiCols = 64;                           // output columns per staging pass: 128-byte row segments
+    static constexpr int kEpiPitch = kEpiCols * 2;                // no padding: 16-byte chunks are XOR-swizzled by row instead
     static constexpr int kEpiWarpBytes = 32 * kEpiPitch;          // one epilogue warp stages its 32 rows
     static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256 + kEpiWarps * kEpiWarpBytes;
 };
@@ -567,35 +567,44 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             tcgen05_fence_after();
             const int chalf = (warp - 2) >> 2;            // which 128-column half of the tile this warp drains
             if (vec_ok) {
-                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane), then 4 lanes write one
-                // row's 64 contiguous bytes, so global (and peer) stores are whole segments instead of 16-byte pieces scattered
-                // over 32 rows. The next TMEM load is issued before the current patch is written out.
+                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
+                // kept at chunk c ^ (row & 7), conflict-free both ways), then 8 lanes write one row's 128 contiguous bytes, so
+                // global and peer stores are whole 128-byte segments. The next TMEM loads are issued before the write-out.
                 unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + 256 + (size_t)(warp - 2) * C::kEpiWarpBytes;
                 const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
                 const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * (BN2 / 2);
-                uint32_t r[32];
-                tmem_ld_32x32(tbase, r);
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32(tbase, ra);
+                tmem_ld_32x32(tbase + 32, rb);
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN2 / 2; c0 += C::kEpiCols) {
                     tmem_ld_wait();
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        uint4 o;
-                        o.x = pack2_rn<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                        o.y = pack2_rn<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                        o.z = pack2_rn<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                        o.w = pack2_rn<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + v * 16) = o;
+                        uint4 o, q;
+                        o.x = pack2_rn<DT>(__uint_as_float(ra[8 * v + 0]), __uint_as_float(ra[8 * v + 1]));
+                        o.y = pack2_rn<DT>(__uint_as_float(ra[8 * v + 2]), __uint_as_float(ra[8 * v + 3]));
+                        o.z = pack2_rn<DT>(__uint_as_float(ra[8 * v + 4]), __uint_as_float(ra[8 * v + 5]));
+                        o.w = pack2_rn<DT>(__uint_as_float(ra[8 * v + 6]), __uint_as_float(ra[8 * v + 7]));
+                        q.x = pack2_rn<DT>(__uint_as_float(rb[8 * v + 0]), __uint_as_float(rb[8 * v + 1]));
+                        q.y = pack2_rn<DT>(__uint_as_float(rb[8 * v + 2]), __uint_as_float(rb[8 * v + 3]));
+                        q.z = pack2_rn<DT>(__uint_as_float(rb[8 * v + 4]), __uint_as_float(rb[8 * v + 5]));
+                        q.w = pack2_rn<DT>(__uint_as_float(rb[8 * v + 6]), __uint_as_float(rb[8 * v + 7]));
+                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + ((v ^ (lane & 7)) << 4)) = o;
+                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + (((v + 4) ^ (lane & 7)) << 4)) = q;
                     }
-                    if (c0 + C::kEpiCols < BN2 / 2) tmem_ld_32x32(tbase + c0 + C::kEpiCols, r);   // in flight during the write-out
+                    if (c0 + C::kEpiCols < BN2 / 2) {   // in flight during the write-out
+                        tmem_ld_32x32(tbase + c0 + C::kEpiCols, ra);
+                        tmem_ld_32x32(tbase + c0 + C::kEpiCols + 32, rb);
+                    }
                     __syncwarp();
-                    const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 3) * 8;
+                    const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 7) * 8;
 #pragma unroll
-                    for (int it = 0; it < 4; ++it) {
-                        const int rr = it * 8 + (lane >> 2);
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3);
                         const int64_t grow = row0 + rr;
                         if (grow < args.M && col < args.N) {
-                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * C::kEpiPitch + (lane & 3) * 16);
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * C::kEpiPitch + (((lane & 7) ^ (rr & 7)) << 4));
                             *reinterpret_cast<uint4 *>(output_row(args, batch, grow) + col) = v;
                         }
                     }
