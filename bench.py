@@ -9,12 +9,13 @@ One JSON line on stdout. A "step" is one pass of the hot path over one batch of 
          (q, k, v, o, gate, up, down; bf16, fp32 accumulation, weights ~ N(0, 0.02^2) through the `W.T`
          view, activations ~ N(0,1), seed 3). `value` = TFLOP/s with everything resident in HBM;
          `e2e` = the same step with the activations coming from pinned host memory and every result
-         copied back, both copies inside the timed region. The same line carries the decode-shaped
+         copied back to it, both copies inside the timed region (on the library's copy streams, so they
+         overlap each other and the kernels). The same line carries the decode-shaped
          sweep (`decode`: Qwen3-0.6B, one token pass over 28 layers + lm_head, M in {1,2,4,8}, HBM GB/s)
          and the 16 Mi-element casts (`casts`), each with its own roofline fraction.
   N > 1  workload "qwen3-32b-tp": the four sharded GEMM groups of one Qwen3-32B layer at M = 8192
-         (QKV and gate/up column-sharded on N, o and down row-sharded on K with an NCCL all-reduce),
-         one rank per GPU. Total work is fixed, so scaling is "strong".
+         (QKV and gate/up column-sharded on N, o and down row-sharded on K with an NCCL all-reduce or the
+         fused scatter-epilogue exchange, whichever is faster), one rank per GPU. Total work is fixed, so scaling is "strong".
 
 `--impl reference` times the reference CPU backend (oracle/_ref, all host threads) on a bounded sample of
 the same workload and prints the same line with "impl": "reference".
@@ -199,14 +200,22 @@ def prefill_workload(dev: Dev, steps: int, warmup: int):
     h2d = sum(t.numel * 2 for t in acts.values())
     d2h = sum(o.numel * 2 for o in outs.values())
 
+    # Each activation is uploaded right before its first consumer and each result is downloaded right after its producer,
+    # on the library's copy streams: uploads, kernels and downloads of different operators overlap (the link is full
+    # duplex), the GEMMs with the largest results go first so the download stream never idles.
+    order = ["gate", "up", "q", "k", "v", "o", "down"]
+    by_name = {n: (a, c) for (n, N, K, a), c in zip(PREFILL_GEMMS, calls)}
+
     def step_e2e():
-        for name, t in acts.items():
-            mb.check(dev.L.magb200_upload_async(dev.d, t.ptr, pin[name], t.numel * 2))
-        for xv, wv, rv in calls:
+        uploaded = set()
+        for n in order:
+            a, (xv, wv, rv) = by_name[n]
+            if a not in uploaded:
+                uploaded.add(a)
+                mb.check(dev.L.magb200_upload_overlapped(dev.d, acts[a].ptr, pin[a], acts[a].numel * 2))
             dev.matmul(xv, wv, rv)
-        for n, o in outs.items():
-            mb.check(dev.L.magb200_download_async(dev.d, pin["out_" + n], o.ptr, o.numel * 2))
-        dev.sync()  # the caller reads the results on the host
+            mb.check(dev.L.magb200_download_overlapped(dev.d, pin["out_" + n], outs[n].ptr, outs[n].numel * 2))
+        dev.sync()  # the caller reads the results on the host; waits for the copy streams too
 
     e2e_steps = max(3, min(steps, 10))
     ms_e2e, _ = timed(dev, step_e2e, e2e_steps, 1)

@@ -90,6 +90,14 @@ int  magb200_upload(int device, void *dst_device, const void *src_host, size_t b
 int  magb200_download(int device, void *dst_host, const void *src_device, size_t bytes); /* stream-ordered, then synchronised */
 int  magb200_upload_async(int device, void *dst_device, const void *src_pinned_host, size_t bytes);
 int  magb200_download_async(int device, void *dst_pinned_host, const void *src_device, size_t bytes);
+/* Transfers on the library's two copy streams, so host<->device traffic of one operator runs beside the kernels of
+ * others and uploads run beside downloads (the link is full duplex). No reference counterpart: magnetron's module ABI
+ * has no transfer entry at all (magnetron/core/mag_backend.h:80-115).
+ * upload_overlapped: starts after the operators submitted so far (they may still read dst); operators submitted later
+ *   wait for it. download_overlapped: starts after the operators submitted so far; later operators do NOT wait for it,
+ *   so the caller must leave src_device untouched until magb200_synchronize, which also waits for both copy streams. */
+int  magb200_upload_overlapped(int device, void *dst_device, const void *src_pinned_host, size_t bytes);
+int  magb200_download_overlapped(int device, void *dst_pinned_host, const void *src_device, size_t bytes);
 int  magb200_host_alloc_pinned(void **out, size_t bytes);
 int  magb200_host_free_pinned(void *ptr);
 

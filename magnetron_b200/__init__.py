@@ -67,6 +67,8 @@ SIGNATURES = {
     "magb200_download": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
     "magb200_upload_async": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
     "magb200_download_async": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "magb200_upload_overlapped": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "magb200_download_overlapped": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]),
     "magb200_host_alloc_pinned": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "magb200_host_free_pinned": (C.c_int, [C.c_void_p]),
     "magb200_cast": (C.c_int, [C.c_int, _VP, _VP]),

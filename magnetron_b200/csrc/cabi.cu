@@ -42,6 +42,8 @@ struct DeviceState {
     char name[256] = "";
     bool capturing = false;          // between graph_begin_capture and graph_end_capture
     int cta_limit = 0;               // 0: all SMs; else the tensor-core GEMMs launch at most this many CTAs
+    cudaStream_t h2d_stream = nullptr;   // copy streams of the overlapped transfers (created on first use)
+    cudaStream_t d2h_stream = nullptr;
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -409,6 +411,8 @@ int magb200_device_shutdown(int device) {
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
     for (int i = 0; i < 3; ++i) if (d.staging[i]) { cudaFree(d.staging[i]); d.staging[i] = nullptr; d.staging_bytes[i] = 0; }
     cudaFree(d.scratch); cudaFree(d.status);
+    if (d.h2d_stream) { cudaStreamSynchronize(d.h2d_stream); cudaStreamDestroy(d.h2d_stream); }
+    if (d.d2h_stream) { cudaStreamSynchronize(d.d2h_stream); cudaStreamDestroy(d.d2h_stream); }
     cudaStreamDestroy(d.own_stream);
     d = DeviceState();
     return MAGB200_OK;
@@ -419,6 +423,8 @@ int magb200_synchronize(int device) {
     int rc = ensure_device(device, &d);
     if (rc) return rc;
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    if (d->d2h_stream) MAGB200_CUDA_TRY(cudaStreamSynchronize(d->d2h_stream));
+    if (d->h2d_stream) MAGB200_CUDA_TRY(cudaStreamSynchronize(d->h2d_stream));
     return check_status_word(*d);
 }
 
@@ -473,6 +479,37 @@ int magb200_download_async(int device, void *dst, const void *src, size_t bytes)
     int rc = ensure_device(device, &d);
     if (rc) return rc;
     MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d->stream));
+    return MAGB200_OK;
+}
+// `later` starts after everything submitted to `earlier` so far
+static int order_after(cudaStream_t later, cudaStream_t earlier) {
+    cudaEvent_t ev;
+    MAGB200_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(ev, earlier);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(later, ev, 0);
+    cudaEventDestroy(ev);   // released by the runtime once the recorded work has completed
+    if (e != cudaSuccess) return cuda_fail(e, "event ordering", __FILE__, __LINE__);
+    return MAGB200_OK;
+}
+static int copy_stream(DeviceState &d, cudaStream_t *slot) {
+    if (d.capturing) { set_error("overlapped transfers cannot be recorded into a graph"); return MAGB200_ERR_INVALID_ARG; }
+    if (!*slot) MAGB200_CUDA_TRY(cudaStreamCreateWithFlags(slot, cudaStreamNonBlocking));
+    return MAGB200_OK;
+}
+int magb200_upload_overlapped(int device, void *dst, const void *src, size_t bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc || (rc = copy_stream(*d, &d->h2d_stream))) return rc;
+    if ((rc = order_after(d->h2d_stream, d->stream))) return rc;          // earlier operators may still read dst
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d->h2d_stream));
+    return order_after(d->stream, d->h2d_stream);                          // later operators see the data
+}
+int magb200_download_overlapped(int device, void *dst, const void *src, size_t bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc || (rc = copy_stream(*d, &d->d2h_stream))) return rc;
+    if ((rc = order_after(d->d2h_stream, d->stream))) return rc;          // the producer of src has been submitted
+    MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d->d2h_stream));
     return MAGB200_OK;
 }
 int magb200_upload(int device, void *dst, const void *src, size_t bytes) {

@@ -166,7 +166,9 @@ template <int BN> struct Cfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128 / 256 / 512 columns
-    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kEpiCols = 64;                  // output columns per staging pass: 128-byte row segments
+    static constexpr int kEpiWarpBytes = 32 * kEpiCols * 2;   // one epilogue warp stages its 32 rows, chunks XOR-swizzled by row
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * kEpiWarpBytes;
 };
 
 template <int BN, int DT>
@@ -309,24 +311,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
-            uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
+            if (vec_ok) {
+                // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
+                // kept at chunk c ^ (row & 7)), then 8 lanes write one row's 128 contiguous bytes. The next TMEM loads are
+                // issued before the write-out.
+                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + 256 + (size_t)quarter * C::kEpiWarpBytes;
+                const int64_t row0 = tm * BM + quarter * 32;
+                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32(tbase, ra);
+                tmem_ld_32x32(tbase + 32, rb);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c, r);
-                tmem_ld_wait();
-                if (row < args.M && n0 + c < args.N) {
-                    if (vec_ok && n0 + c + 32 <= args.N) {
+                for (int c0 = 0; c0 < BN; c0 += C::kEpiCols) {
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2_rn<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2_rn<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2_rn<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2_rn<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o, q;
+                        o.x = pack2_rn<DT>(__uint_as_float(ra[8 * v + 0]), __uint_as_float(ra[8 * v + 1]));
+                        o.y = pack2_rn<DT>(__uint_as_float(ra[8 * v + 2]), __uint_as_float(ra[8 * v + 3]));
+                        o.z = pack2_rn<DT>(__uint_as_float(ra[8 * v + 4]), __uint_as_float(ra[8 * v + 5]));
+                        o.w = pack2_rn<DT>(__uint_as_float(ra[8 * v + 6]), __uint_as_float(ra[8 * v + 7]));
+                        q.x = pack2_rn<DT>(__uint_as_float(rb[8 * v + 0]), __uint_as_float(rb[8 * v + 1]));
+                        q.y = pack2_rn<DT>(__uint_as_float(rb[8 * v + 2]), __uint_as_float(rb[8 * v + 3]));
+                        q.z = pack2_rn<DT>(__uint_as_float(rb[8 * v + 4]), __uint_as_float(rb[8 * v + 5]));
+                        q.w = pack2_rn<DT>(__uint_as_float(rb[8 * v + 6]), __uint_as_float(rb[8 * v + 7]));
+                        *reinterpret_cast<uint4 *>(stg + lane * (C::kEpiCols * 2) + ((v ^ (lane & 7)) << 4)) = o;
+                        *reinterpret_cast<uint4 *>(stg + lane * (C::kEpiCols * 2) + (((v + 4) ^ (lane & 7)) << 4)) = q;
+                    }
+                    if (c0 + C::kEpiCols < BN) {   // in flight during the write-out
+                        tmem_ld_32x32(tbase + c0 + C::kEpiCols, ra);
+                        tmem_ld_32x32(tbase + c0 + C::kEpiCols + 32, rb);
+                    }
+                    __syncwarp();
+                    const int64_t col = n0 + c0 + (lane & 7) * 8;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3);
+                        const int64_t grow = row0 + rr;
+                        if (grow < args.M && col < args.N) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * (C::kEpiCols * 2) + (((lane & 7) ^ (rr & 7)) << 4));
+                            *reinterpret_cast<uint4 *>(output_row(args, batch, grow) + col) = v;
                         }
-                    } else {
+                    }
+                    __syncwarp();
+                }
+            } else {
+                uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c, r);
+                    tmem_ld_wait();
+                    if (row < args.M && n0 + c < args.N) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));

@@ -317,6 +317,49 @@ def test_host_buffer_matmul(gpu):
     assert m["e"] <= unit_roundoff(dt) + 256 * 2.0 ** -24
 
 
+def test_overlapped_transfers_keep_operator_order(gpu):
+    """Uploads and downloads on the copy streams: a chain upload -> matmul -> download, repeated with the same device
+    buffers and different host data, returns for every round exactly what the plain path returns."""
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(21)
+    L = mb.lib()
+    M, K, N = 512, 1024, 768
+    wb = bits(dt, rng, (N, K), 0.05)
+    tw = mb.Tensor.from_bits(gpu, dt, wb)
+    tx, to = mb.Tensor(gpu, dt, (M, K)), mb.Tensor(gpu, dt, (M, N))
+    rounds = 4
+    pin_x, pin_o = C.c_void_p(), C.c_void_p()
+    mb.check(L.magb200_host_alloc_pinned(C.byref(pin_x), rounds * M * K * 2))
+    mb.check(L.magb200_host_alloc_pinned(C.byref(pin_o), rounds * M * N * 2))
+    try:
+        hx = np.ctypeslib.as_array(C.cast(pin_x, C.POINTER(C.c_uint16)), shape=(rounds, M, K))
+        ho = np.ctypeslib.as_array(C.cast(pin_o, C.POINTER(C.c_uint16)), shape=(rounds, M, N))
+        ho[:] = 0
+        for r in range(rounds):
+            hx[r] = bits(dt, rng, (M, K), 1.0)
+        want = []
+        for r in range(rounds):
+            t = mb.Tensor.from_bits(gpu, dt, np.ascontiguousarray(hx[r]))
+            want.append((t @ tw.T).to_bits())
+            t.release()
+        # all rounds are queued without a synchronisation in between, one result buffer per round
+        outs = [mb.Tensor(gpu, dt, (M, N)) for _ in range(rounds)]
+        for r in range(rounds):
+            mb.check(L.magb200_upload_overlapped(gpu, tx.ptr, hx[r].ctypes.data, M * K * 2))
+            mb.check(L.magb200_matmul(gpu, C.byref(tx.view_struct()), C.byref(tw.T.view_struct()), C.byref(outs[r].view_struct())))
+            mb.check(L.magb200_download_overlapped(gpu, ho[r].ctypes.data, outs[r].ptr, M * N * 2))
+        mb.synchronize(gpu)
+        for r in range(rounds):
+            np.testing.assert_array_equal(ho[r], want[r])
+        for t in outs:
+            t.release()
+    finally:
+        L.magb200_host_free_pinned(pin_x)
+        L.magb200_host_free_pinned(pin_o)
+        for t in (tw, tx, to):
+            t.release()
+
+
 def test_graph_replay_matches_direct_calls(gpu):
     """A recorded sequence of decode-shaped matmuls replays to the same bits as the direct calls."""
     dt = O.BFLOAT16
