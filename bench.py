@@ -406,9 +406,9 @@ def main():
         "gpu_launches": pre["launches"], "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": pre["tflops"], "peak": tensor_peak, "unit": "TFLOP/s",
                      "frac": pre["tflops"] / tensor_peak,
-                     # DRAM bytes per launch: the ncu capture of one 4096^3 launch of the same kernel read+wrote 98.5 MB against
+                     # DRAM bytes per launch: the ncu capture of one 4096^3 launch of the same kernel read+wrote 105.3 MB against
                      # 100.7 MB algorithmic (profiles/gemm_tcgen05_2sm_4096x4096x4096.md); scaled to the step's mean launch
-                     "traffic": 0.978 * pre["bytes_per_step"] / len(PREFILL_GEMMS),
+                     "traffic": 1.046 * pre["bytes_per_step"] / len(PREFILL_GEMMS),
                      "traffic_note": "scaled from an ncu capture of a smaller case by algorithmic bytes; mean over the step's 7 launches",
                      "peak_source": "%s %s cuBLAS bf16" % (pk["source"], "sustained" if long_run else "burst"),
                      "frac_of_nominal_2250": pre["tflops"] / 2250.0,

@@ -300,6 +300,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t titer = 0;
         bool ok = true;
         const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
+        const bool staged = args.total_tiles > (int64_t)gridDim.x || args.scatter_ranks > 0;
         for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
             const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
             int64_t batch, tm, tn;
@@ -311,7 +312,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
             if (!ok) break;
             tcgen05_fence_after();
-            if (vec_ok) {
+            if (vec_ok && !staged) {
+                // single wave: nothing follows this tile, so the shortest path to global memory wins (16-byte stores per lane)
+                uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c, r);
+                    tmem_ld_wait();
+                    if (row < args.M) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (n0 + c + 8 * v < args.N) {
+                                uint4 o;
+                                o.x = pack2_rn<DT>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                o.y = pack2_rn<DT>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                o.z = pack2_rn<DT>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                o.w = pack2_rn<DT>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                            }
+                        }
+                    }
+                }
+            } else if (vec_ok) {
                 // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
                 // kept at chunk c ^ (row & 7)), then 8 lanes write one row's 128 contiguous bytes. The next TMEM loads are
                 // issued before the write-out.
