@@ -318,7 +318,8 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
             return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status);
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
-            return launch_gemm_simt(g, d.stream);
+            if (int rc = ensure_scratch(d, simt_scratch_bytes(g))) return rc;
+            return launch_gemm_simt(g, d.stream, d.scratch, d.scratch_bytes);
     }
 }
 

@@ -125,7 +125,8 @@ struct GemmProblem {
 };
 
 // kernel launchers (each returns a magb200_status_t); `stream` is the device's launch stream
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream);
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes);
+size_t simt_scratch_bytes(const GemmProblem &p);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk);
 bool tcgen05_supported(const GemmProblem &p);

@@ -7,33 +7,52 @@
 // multiple of 16 bytes, a misaligned base). Operands are gathered through their strides straight into
 // shared memory as fp32, so no packed copy of a strided view is ever made in HBM.
 //
-// Tile: 128x128x16 per 256-thread CTA, 8x8 accumulators per thread held as 2x2 blocks of 4x4 so the
-// shared-memory reads are conflict-free 128-bit loads.
+// Tile: 128x128x16 per 512-thread CTA, 8x4 accumulators per thread. A warp covers 4 row groups x 8
+// column groups, so its shared-memory reads are three 128-bit wavefronts per K step. The next K tile
+// is fetched from global memory into registers while the current one is multiplied, and shared memory
+// is double buffered: one barrier per K tile.
 //
 // fp32 accuracy: a single fp32 accumulator that walks the whole K loses several units in the last place
 // at K in the thousands, more than the reference's blocked CPU kernel does. For float32 the kernel
 // therefore sums each 16-wide K tile in a fresh accumulator and folds it into the running total with an
 // error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 16-term
 // tile. The 16-bit dtypes skip this: their error is set by the final rounding of the result.
+//
+// Few tiles (an output smaller than the GPU): K is split over several CTAs per tile; each writes its
+// (total, low) pair as fp32 and a second kernel adds the pairs in split order, again with TwoSum, and
+// rounds once.
 #include "common.cuh"
 
 namespace magb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256, PAD = 4;
+constexpr int BM = 128, BN = 128, BK = 16, THREADS = 512, PAD = 4;
+constexpr int kLoads = (BM * BK) / THREADS;   // elements of each operand tile a thread fetches: 4
+
+// s + e == a + b exactly
+__device__ __forceinline__ void two_sum(float a, float b, float &s, float &e) {
+    s = __fadd_rn(a, b);
+    const float bp = __fsub_rn(s, a);
+    e = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bp)), __fsub_rn(b, bp));
+}
 
 template <int DT>
-__global__ void __launch_bounds__(THREADS, 1) gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n) {
-    __shared__ __align__(16) float As[BK][BM + PAD];
-    __shared__ __align__(16) float Bs[BK][BN + PAD];
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial) {
+    __shared__ __align__(16) float As[2][BK][BM + PAD];
+    __shared__ __align__(16) float Bs[2][BK][BN + PAD];
 
-    const int64_t tile = blockIdx.x;
     const int64_t tiles_per_batch = tiles_m * tiles_n;
+    const int64_t tiles_total = tiles_per_batch * p.batch_total;
+    const int split = (int)((int64_t)blockIdx.x / tiles_total);
+    const int64_t tile = (int64_t)blockIdx.x - (int64_t)split * tiles_total;
     const int64_t batch = tile / tiles_per_batch;
     const int64_t trem = tile - batch * tiles_per_batch;
     const int64_t tm = trem / tiles_n, tn = trem - tm * tiles_n;
     const int64_t m0 = tm * BM, n0 = tn * BN;
+    const int64_t kbeg = (int64_t)split * kchunk;
+    const int64_t kend = (kbeg + kchunk < p.K) ? kbeg + kchunk : p.K;
 
     // batch index -> operand offsets; broadcast dims carry stride 0
     int64_t offA = 0, offB = 0;
@@ -47,114 +66,196 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_simt_kernel(const GemmProblem
             rem = q;
         }
     }
+    const int t = threadIdx.x;
+    const int lane = t & 31, warp = t >> 5;
+    const int tx = (warp & 3) * 8 + (lane & 7);    // column group: columns tx*4 .. tx*4+3
+    const int ty = (warp >> 2) * 4 + (lane >> 3);  // row group: rows ty*4 .. +3 and 64 + ty*4 .. +3
+
+    // ---- what this thread fetches of every K tile: kLoads elements of A and of B. One coordinate is fixed per thread,
+    // the other advances by a constant, so an element's address is base + i * step and a K tile later adds BK * stride.
+    const bool a_k_fast = (p.sAk == 1) || (p.sAm != 1);   // walk k fastest unless m is the unit-stride dim
+    const bool b_n_fast = (p.sBn == 1) || (p.sBk != 1);
+    int a_kk, a_mm, a_dk, a_dm, b_kk, b_nn, b_dk, b_dn;   // first element and per-load increments inside the tile
+    if (a_k_fast) { a_kk = t & 15; a_mm = t >> 4; a_dk = 0; a_dm = THREADS / 16; }
+    else          { a_mm = t & 127; a_kk = t >> 7; a_dm = 0; a_dk = THREADS / 128; }
+    if (b_n_fast) { b_nn = t & 127; b_kk = t >> 7; b_dn = 0; b_dk = THREADS / 128; }
+    else          { b_kk = t & 15; b_nn = t >> 4; b_dk = 0; b_dn = THREADS / 16; }
+    int64_t a_off = offA + (m0 + a_mm) * p.sAm + (kbeg + a_kk) * p.sAk;
+    int64_t b_off = offB + (kbeg + b_kk) * p.sBk + (n0 + b_nn) * p.sBn;
+    const int64_t a_step = (int64_t)a_dm * p.sAm + (int64_t)a_dk * p.sAk;
+    const int64_t b_step = (int64_t)b_dk * p.sBk + (int64_t)b_dn * p.sBn;
     const char *A = (const char *)p.A;
     const char *B = (const char *)p.B;
-    const int t = threadIdx.x;
-    const int tx = t & 15, ty = t >> 4;
+
+    float ra[kLoads], rb[kLoads];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int i = 0; i < kLoads; ++i) {
+            const bool okA = (m0 + a_mm + i * a_dm < p.M) && (k0 + a_kk + i * a_dk < kend);
+            const bool okB = (n0 + b_nn + i * b_dn < p.N) && (k0 + b_kk + i * b_dk < kend);
+            ra[i] = okA ? load_as_f32<DT>(A, a_off + i * a_step) : 0.f;
+            rb[i] = okB ? load_as_f32<DT>(B, b_off + i * b_step) : 0.f;
+        }
+        a_off += (int64_t)BK * p.sAk;
+        b_off += (int64_t)BK * p.sBk;
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < kLoads; ++i) {
+            As[buf][a_kk + i * a_dk][a_mm + i * a_dm] = ra[i];
+            Bs[buf][b_kk + i * b_dk][b_nn + i * b_dn] = rb[i];
+        }
+    };
 
     constexpr bool kCompensated = (DT == MAGB200_F32);
-    float acc[8][8];                                   // sum of the current K tile (fp32) or of all of K (16-bit)
-    float total[kCompensated ? 8 : 1][8], low[kCompensated ? 8 : 1][8];  // running total and its lost low part
+    float acc[8][4];                                   // sum of the current K tile (fp32) or of all of K (16-bit)
+    float total[kCompensated ? 8 : 1][4], low[kCompensated ? 8 : 1][4];  // running total and its lost low part
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             acc[i][j] = 0.f;
             if constexpr (kCompensated) { total[i][j] = 0.f; low[i][j] = 0.f; }
         }
 
-    const bool a_k_fast = (p.sAk == 1) || (p.sAm != 1);  // walk k fastest unless m is the unit-stride dim
-    const bool b_n_fast = (p.sBn == 1) || (p.sBk != 1);
-
-    for (int64_t k0 = 0; k0 < p.K; k0 += BK) {
-        // ---- gather the A tile (BM x BK) and the B tile (BK x BN) as fp32 ----
-#pragma unroll
-        for (int i = 0; i < (BM * BK) / THREADS; ++i) {
-            int e = t + i * THREADS;
-            int kk, mm;
-            if (a_k_fast) { kk = e & (BK - 1); mm = e >> 4; } else { mm = e & (BM - 1); kk = e >> 7; }
-            int64_t gm = m0 + mm, gk = k0 + kk;
-            float v = 0.f;
-            if (gm < p.M && gk < p.K) v = load_as_f32<DT>(A, offA + gm * p.sAm + gk * p.sAk);
-            As[kk][mm] = v;
-        }
-#pragma unroll
-        for (int i = 0; i < (BN * BK) / THREADS; ++i) {
-            int e = t + i * THREADS;
-            int kk, nn;
-            if (b_n_fast) { nn = e & (BN - 1); kk = e >> 7; } else { kk = e & (BK - 1); nn = e >> 4; }
-            int64_t gn = n0 + nn, gk = k0 + kk;
-            float v = 0.f;
-            if (gn < p.N && gk < p.K) v = load_as_f32<DT>(B, offB + gk * p.sBk + gn * p.sBn);
-            Bs[kk][nn] = v;
-        }
-        __syncthreads();
+    int buf = 0;
+    if (kbeg < kend) {
+        fetch(kbeg);
+        stash(0);
+    }
+    __syncthreads();
+    for (int64_t k0 = kbeg; k0 < kend; k0 += BK) {
+        const bool more = k0 + BK < kend;
+        if (more) fetch(k0 + BK);                      // global loads in flight under the multiply below
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
-            float a[8], b[8];
-            *reinterpret_cast<float4 *>(&a[0]) = *reinterpret_cast<const float4 *>(&As[kk][ty * 4]);
-            *reinterpret_cast<float4 *>(&a[4]) = *reinterpret_cast<const float4 *>(&As[kk][64 + ty * 4]);
-            *reinterpret_cast<float4 *>(&b[0]) = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4]);
-            *reinterpret_cast<float4 *>(&b[4]) = *reinterpret_cast<const float4 *>(&Bs[kk][64 + tx * 4]);
+            float a[8], b[4];
+            *reinterpret_cast<float4 *>(&a[0]) = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4]);
+            *reinterpret_cast<float4 *>(&a[4]) = *reinterpret_cast<const float4 *>(&As[buf][kk][64 + ty * 4]);
+            *reinterpret_cast<float4 *>(&b[0]) = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
         if constexpr (kCompensated) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // TwoSum: s + e == total + acc exactly
-                    const float s = __fadd_rn(total[i][j], acc[i][j]);
-                    const float bp = __fsub_rn(s, total[i][j]);
-                    const float e = __fadd_rn(__fsub_rn(total[i][j], __fsub_rn(s, bp)), __fsub_rn(acc[i][j], bp));
+                for (int j = 0; j < 4; ++j) {
+                    float s, e;
+                    two_sum(total[i][j], acc[i][j], s, e);
                     total[i][j] = s;
                     low[i][j] = __fadd_rn(low[i][j], e);
                     acc[i][j] = 0.f;
                 }
         }
+        if (more) stash(buf ^ 1);                      // the other buffer: nobody reads it during this tile
         __syncthreads();
-    }
-    if constexpr (kCompensated) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[i][j] = __fadd_rn(total[i][j], low[i][j]);
+        buf ^= 1;
     }
 
-    // ---- epilogue: one rounding to the result dtype, row-major C with ldc = N ----
+    // ---- epilogue: row-major C with ldc = N; one rounding to the result dtype, or the (total, low) pair of this K split
     char *C = (char *)p.C;
     const int64_t cbase = batch * p.M * p.N;
+    const int64_t elems = p.batch_total * p.M * p.N;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        int64_t gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        const int64_t gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
         if (gm >= p.M) continue;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int64_t gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
-            if (gn < p.N) store_from_f32<DT>(C, cbase + gm * p.N + gn, acc[i][j]);
+        for (int j = 0; j < 4; ++j) {
+            const int64_t gn = n0 + tx * 4 + j;
+            if (gn >= p.N) continue;
+            const int64_t idx = cbase + gm * p.N + gn;
+            if (nsplit == 1) {
+                float v = acc[i][j];
+                if constexpr (kCompensated) v = __fadd_rn(total[i][j], low[i][j]);
+                store_from_f32<DT>(C, idx, v);
+            } else {
+                float hi = acc[i][j], lo = 0.f;
+                if constexpr (kCompensated) { hi = total[i][j]; lo = low[i][j]; }
+                partial[((int64_t)split * 2 + 0) * elems + idx] = hi;
+                partial[((int64_t)split * 2 + 1) * elems + idx] = lo;
+            }
         }
     }
 }
 
+// partial[nsplit][2][elems] -> C[elems]: the splits' (total, low) pairs added in split order without losing the low parts
+template <int DT>
+__global__ void __launch_bounds__(256) simt_finalize_kernel(const float *__restrict__ partial, void *__restrict__ C, int64_t elems, int nsplit) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < elems; i += stride) {
+        float total = partial[i], low = partial[elems + i];
+        for (int s = 1; s < nsplit; ++s) {
+            float sum, e;
+            two_sum(total, partial[((int64_t)s * 2) * elems + i], sum, e);
+            total = sum;
+            low = __fadd_rn(low, __fadd_rn(e, partial[((int64_t)s * 2 + 1) * elems + i]));
+        }
+        store_from_f32<DT>(C, i, __fadd_rn(total, low));
+    }
+}
+
+struct SimtPlan { int64_t tiles_m, tiles_n, tiles; int nsplit; int64_t kchunk; };
+
+SimtPlan plan_simt(const GemmProblem &p) {
+    SimtPlan pl;
+    pl.tiles_m = (p.M + BM - 1) / BM;
+    pl.tiles_n = (p.N + BN - 1) / BN;
+    pl.tiles = pl.tiles_m * pl.tiles_n * p.batch_total;
+    pl.nsplit = 1;
+    // an output smaller than the GPU: cut K so that about one CTA per SM is busy, never below 256 K values per CTA
+    if (pl.tiles > 0 && pl.tiles * 2 <= kNumSMsB200 && p.K >= 512) {
+        int64_t s = kNumSMsB200 / pl.tiles;
+        if (s > p.K / 256) s = p.K / 256;
+        if (s > 16) s = 16;
+        if (s > 1) pl.nsplit = (int)s;
+    }
+    const int64_t kb = (p.K + BK - 1) / BK;
+    pl.kchunk = ((kb + pl.nsplit - 1) / pl.nsplit) * BK;
+    if (pl.kchunk < BK) pl.kchunk = BK;
+    while (pl.nsplit > 1 && (int64_t)(pl.nsplit - 1) * pl.kchunk >= p.K) --pl.nsplit;   // no empty split
+    return pl;
+}
+
 }  // namespace
 
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream) {
-    const int64_t tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-    const int64_t total = tiles_m * tiles_n * p.batch_total;
-    if (total <= 0) return MAGB200_OK;
-    if (total > 0x7FFFFFFFLL) {
-        set_error("matmul: %lld tiles exceed the grid limit", (long long)total);
+size_t simt_scratch_bytes(const GemmProblem &p) {
+    const SimtPlan pl = plan_simt(p);
+    return pl.nsplit > 1 ? (size_t)pl.nsplit * 2 * (size_t)(p.batch_total * p.M * p.N) * sizeof(float) : 0;
+}
+
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, size_t scratch_bytes) {
+    SimtPlan pl = plan_simt(p);
+    if (pl.tiles <= 0) return MAGB200_OK;
+    if (pl.nsplit > 1 && (!scratch || scratch_bytes < simt_scratch_bytes(p))) {   // no workspace: one CTA walks all of K
+        pl.nsplit = 1;
+        pl.kchunk = ((p.K + BK - 1) / BK) * BK;
+        if (pl.kchunk < BK) pl.kchunk = BK;
+    }
+    const int64_t grid = pl.tiles * pl.nsplit;
+    if (grid > 0x7FFFFFFFLL) {
+        set_error("matmul: %lld tiles exceed the grid limit", (long long)grid);
         return MAGB200_ERR_TOO_LARGE;
     }
+    const int64_t elems = p.batch_total * p.M * p.N;
+    int64_t fin_blocks = (elems + 255) / 256;
+    if (fin_blocks > kNumSMsB200 * 8) fin_blocks = kNumSMsB200 * 8;
+#define MAGB200_SIMT_LAUNCH(DT)                                                                                              \
+    gemm_simt_kernel<DT><<<(unsigned)grid, THREADS, 0, stream>>>(p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch); \
+    if (pl.nsplit > 1) {                                                                                                     \
+        count_launch();                                                                                                      \
+        simt_finalize_kernel<DT><<<(unsigned)fin_blocks, 256, 0, stream>>>(scratch, p.C, elems, pl.nsplit);                 \
+    }
     switch (p.dtype) {
-        case MAGB200_F32:  gemm_simt_kernel<MAGB200_F32><<<(unsigned)total, THREADS, 0, stream>>>(p, tiles_m, tiles_n); break;
-        case MAGB200_F16:  gemm_simt_kernel<MAGB200_F16><<<(unsigned)total, THREADS, 0, stream>>>(p, tiles_m, tiles_n); break;
-        case MAGB200_BF16: gemm_simt_kernel<MAGB200_BF16><<<(unsigned)total, THREADS, 0, stream>>>(p, tiles_m, tiles_n); break;
+        case MAGB200_F32:  MAGB200_SIMT_LAUNCH(MAGB200_F32) break;
+        case MAGB200_F16:  MAGB200_SIMT_LAUNCH(MAGB200_F16) break;
+        case MAGB200_BF16: MAGB200_SIMT_LAUNCH(MAGB200_BF16) break;
         default: set_error("matmul: unsupported dtype %d", p.dtype); return MAGB200_ERR_INVALID_ARG;
     }
+#undef MAGB200_SIMT_LAUNCH
     count_launch();
     MAGB200_CUDA_TRY(cudaGetLastError());
     return MAGB200_OK;

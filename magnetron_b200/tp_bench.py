@@ -79,6 +79,7 @@ def main(args, pk):
     launches = int(mb.lib().magb200_launch_count()) * steps // (steps + warmup)
     ms_gather = _time_steps(lambda: layer.step(True), max(2, steps // 2), 2, device)
     fused_tflops, fused_err, fused_parts, fused_pipe_tflops, ms_fp, fp_variants = None, None, None, None, None, None
+    fp_err = None
     if world > 1:
         layer = None
         torch.cuda.empty_cache()
@@ -98,6 +99,17 @@ def main(args, pk):
                     if ms_fp is None or t < ms_fp:
                         ms_fp = t
                 mb.check(mb.lib().magb200_set_cta_limit(local, 0))
+                # the chunked exchange against NCCL on the same operands (outputs of the last timed step)
+                torch.cuda.synchronize(device)
+                for s_ in specs:
+                    if s_.name in lay.fused_chunks:
+                        part = torch.empty((M, s_.n), dtype=torch.bfloat16, device=device)
+                        lay.matmul(lay.x[s_.name], lay.w[s_.name], part)
+                        acc = part.float()
+                        dist.all_reduce(acc)
+                        got = torch.cat([ex.out for ex in lay.fused_chunks[s_.name]], dim=0).float()
+                        err = float((got - acc).abs().max() / acc.abs().max().clamp_min(1e-9))
+                        fp_err = max(fp_err or 0.0, err)
                 del lay
                 torch.cuda.empty_cache()
             fused_pipe_tflops = flops * steps / ms_fp / 1e9
@@ -182,7 +194,7 @@ def main(args, pk):
             "op_by_op_schedule": {"ms_per_step": ms_plain / max(2, steps // 2), "tflops": plain_tflops},
             "pipelined_schedule": {"tflops": pipelined_tflops},
             "fused_exchange_schedule": {"tflops": fused_tflops, "max_rel_diff_vs_nccl": fused_err, "parts": fused_parts},
-            "fused_exchange_pipelined_schedule": {"tflops": fused_pipe_tflops, "variants": fp_variants},
+            "fused_exchange_pipelined_schedule": {"tflops": fused_pipe_tflops, "variants": fp_variants, "max_rel_diff_vs_nccl": fp_err},
             "reserved_sms_for_collectives": reserve,
             "with_output_allgather": {"ms_per_step": ms_gather / max(2, steps // 2), "tflops": flops * max(2, steps // 2) / ms_gather / 1e9},
             "token_sweep": sweep,
