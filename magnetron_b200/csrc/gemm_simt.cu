@@ -14,9 +14,9 @@
 //
 // fp32 accuracy: a single fp32 accumulator that walks the whole K loses several units in the last place
 // at K in the thousands, more than the reference's blocked CPU kernel does. For float32 the kernel
-// therefore sums each 16-wide K tile in a fresh accumulator and folds it into the running total with an
-// error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 16-term
-// tile. The 16-bit dtypes skip this: their error is set by the final rounding of the result.
+// therefore sums 32 products at a time in a fresh accumulator and folds it into the running total with an
+// error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 32-term
+// group. The 16-bit dtypes skip this: their error is set by the final rounding of the result.
 //
 // Few tiles (an output smaller than the GPU): K is split over several CTAs per tile; each writes its
 // (total, low) pair as fp32 and a second kernel adds the pairs in split order, again with TwoSum, and
@@ -37,7 +37,9 @@ __device__ __forceinline__ void two_sum(float a, float b, float &s, float &e) {
     e = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bp)), __fsub_rn(b, bp));
 }
 
-template <int DT>
+// AKF: the A tile is fetched walking k fastest (else m fastest); BNF: the B tile walking n fastest (else k fastest).
+// Compile-time modes make every shared-memory offset of the fetch a constant.
+template <int DT, bool AKF, bool BNF>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial) {
     __shared__ __align__(16) float As[2][BK][BM + PAD];
@@ -72,38 +74,50 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
     const int ty = (warp >> 2) * 4 + (lane >> 3);  // row group: rows ty*4 .. +3 and 64 + ty*4 .. +3
 
     // ---- what this thread fetches of every K tile: kLoads elements of A and of B. One coordinate is fixed per thread,
-    // the other advances by a constant, so an element's address is base + i * step and a K tile later adds BK * stride.
-    const bool a_k_fast = (p.sAk == 1) || (p.sAm != 1);   // walk k fastest unless m is the unit-stride dim
-    const bool b_n_fast = (p.sBn == 1) || (p.sBk != 1);
-    int a_kk, a_mm, a_dk, a_dm, b_kk, b_nn, b_dk, b_dn;   // first element and per-load increments inside the tile
-    if (a_k_fast) { a_kk = t & 15; a_mm = t >> 4; a_dk = 0; a_dm = THREADS / 16; }
-    else          { a_mm = t & 127; a_kk = t >> 7; a_dm = 0; a_dk = THREADS / 128; }
-    if (b_n_fast) { b_nn = t & 127; b_kk = t >> 7; b_dn = 0; b_dk = THREADS / 128; }
-    else          { b_kk = t & 15; b_nn = t >> 4; b_dk = 0; b_dn = THREADS / 16; }
-    int64_t a_off = offA + (m0 + a_mm) * p.sAm + (kbeg + a_kk) * p.sAk;
-    int64_t b_off = offB + (kbeg + b_kk) * p.sBk + (n0 + b_nn) * p.sBn;
-    const int64_t a_step = (int64_t)a_dm * p.sAm + (int64_t)a_dk * p.sAk;
-    const int64_t b_step = (int64_t)b_dk * p.sBk + (int64_t)b_dn * p.sBn;
-    const char *A = (const char *)p.A;
-    const char *B = (const char *)p.B;
+    // the other advances by a constant, so the elements sit at pointer + i * step, a K tile later adds BK * stride, and
+    // the row/column bounds are tested once (a bit per element); only the last K tile tests k.
+    constexpr int a_dk = AKF ? 0 : THREADS / 128, a_dm = AKF ? THREADS / 16 : 0;
+    constexpr int b_dk = BNF ? THREADS / 128 : 0, b_dn = BNF ? 0 : THREADS / 16;
+    const int a_kk = AKF ? (t & 15) : (t >> 7), a_mm = AKF ? (t >> 4) : (t & 127);
+    const int b_kk = BNF ? (t >> 7) : (t & 15), b_nn = BNF ? (t & 127) : (t >> 4);
+    constexpr int64_t es = (DT == MAGB200_F32) ? 4 : 2;
+    const char *pa = (const char *)p.A + (offA + (m0 + a_mm) * p.sAm + (kbeg + a_kk) * p.sAk) * es;
+    const char *pb = (const char *)p.B + (offB + (kbeg + b_kk) * p.sBk + (n0 + b_nn) * p.sBn) * es;
+    const int64_t a_step = ((int64_t)a_dm * p.sAm + (int64_t)a_dk * p.sAk) * es;
+    const int64_t b_step = ((int64_t)b_dk * p.sBk + (int64_t)b_dn * p.sBn) * es;
+    const int64_t a_tile = (int64_t)BK * p.sAk * es, b_tile = (int64_t)BK * p.sBk * es;
+    unsigned in_a = 0, in_b = 0;
+#pragma unroll
+    for (int i = 0; i < kLoads; ++i) {
+        if (m0 + a_mm + i * a_dm < p.M) in_a |= 1u << i;
+        if (n0 + b_nn + i * b_dn < p.N) in_b |= 1u << i;
+    }
 
     float ra[kLoads], rb[kLoads];
-    auto fetch = [&](int64_t k0) {
+    auto fetch = [&](int64_t k0, bool tail) {
+        const char *qa = pa, *qb = pb;
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
-            const bool okA = (m0 + a_mm + i * a_dm < p.M) && (k0 + a_kk + i * a_dk < kend);
-            const bool okB = (n0 + b_nn + i * b_dn < p.N) && (k0 + b_kk + i * b_dk < kend);
-            ra[i] = okA ? load_as_f32<DT>(A, a_off + i * a_step) : 0.f;
-            rb[i] = okB ? load_as_f32<DT>(B, b_off + i * b_step) : 0.f;
+            bool okA = (in_a >> i) & 1u, okB = (in_b >> i) & 1u;
+            if (tail) {
+                okA = okA && (k0 + a_kk + i * a_dk < kend);
+                okB = okB && (k0 + b_kk + i * b_dk < kend);
+            }
+            ra[i] = okA ? load_as_f32<DT>(qa, 0) : 0.f;
+            rb[i] = okB ? load_as_f32<DT>(qb, 0) : 0.f;
+            qa += a_step;
+            qb += b_step;
         }
-        a_off += (int64_t)BK * p.sAk;
-        b_off += (int64_t)BK * p.sBk;
+        pa += a_tile;
+        pb += b_tile;
     };
+    float *const sa = &As[0][a_kk][a_mm];
+    float *const sb = &Bs[0][b_kk][b_nn];
     auto stash = [&](int buf) {
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
-            As[buf][a_kk + i * a_dk][a_mm + i * a_dm] = ra[i];
-            Bs[buf][b_kk + i * b_dk][b_nn + i * b_dn] = rb[i];
+            sa[buf * (BK * (BM + PAD)) + i * (a_dk * (BM + PAD) + a_dm)] = ra[i];
+            sb[buf * (BK * (BN + PAD)) + i * (b_dk * (BN + PAD) + b_dn)] = rb[i];
         }
     };
 
@@ -119,14 +133,15 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
         }
 
     int buf = 0;
+    bool fold = false;                                 // fp32: fold after every second K tile (32 products per fresh accumulator)
     if (kbeg < kend) {
-        fetch(kbeg);
+        fetch(kbeg, true);
         stash(0);
     }
     __syncthreads();
     for (int64_t k0 = kbeg; k0 < kend; k0 += BK) {
         const bool more = k0 + BK < kend;
-        if (more) fetch(k0 + BK);                      // global loads in flight under the multiply below
+        if (more) fetch(k0 + BK, k0 + 2 * BK > kend);   // global loads in flight under the multiply below
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float a[8], b[4];
@@ -138,7 +153,7 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
-        if constexpr (kCompensated) {
+        if (kCompensated && (fold || !more)) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -153,6 +168,7 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
         if (more) stash(buf ^ 1);                      // the other buffer: nobody reads it during this tile
         __syncthreads();
         buf ^= 1;
+        fold = !fold;
     }
 
     // ---- epilogue: row-major C with ldc = N; one rounding to the result dtype, or the (total, low) pair of this K split
@@ -243,11 +259,16 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
     const int64_t elems = p.batch_total * p.M * p.N;
     int64_t fin_blocks = (elems + 255) / 256;
     if (fin_blocks > kNumSMsB200 * 8) fin_blocks = kNumSMsB200 * 8;
-#define MAGB200_SIMT_LAUNCH(DT)                                                                                              \
-    gemm_simt_kernel<DT><<<(unsigned)grid, THREADS, 0, stream>>>(p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch); \
-    if (pl.nsplit > 1) {                                                                                                     \
-        count_launch();                                                                                                      \
-        simt_finalize_kernel<DT><<<(unsigned)fin_blocks, 256, 0, stream>>>(scratch, p.C, elems, pl.nsplit);                 \
+    const bool akf = (p.sAk == 1) || (p.sAm != 1);   // walk k fastest unless m is the unit-stride dim
+    const bool bnf = (p.sBn == 1) || (p.sBk != 1);
+#define MAGB200_SIMT_GO(DT, AKF, BNF) \
+    gemm_simt_kernel<DT, AKF, BNF><<<(unsigned)grid, THREADS, 0, stream>>>(p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch)
+#define MAGB200_SIMT_LAUNCH(DT)                                                                              \
+    if (akf) { if (bnf) MAGB200_SIMT_GO(DT, true, true); else MAGB200_SIMT_GO(DT, true, false); }            \
+    else     { if (bnf) MAGB200_SIMT_GO(DT, false, true); else MAGB200_SIMT_GO(DT, false, false); }          \
+    if (pl.nsplit > 1) {                                                                                     \
+        count_launch();                                                                                      \
+        simt_finalize_kernel<DT><<<(unsigned)fin_blocks, 256, 0, stream>>>(scratch, p.C, elems, pl.nsplit);  \
     }
     switch (p.dtype) {
         case MAGB200_F32:  MAGB200_SIMT_LAUNCH(MAGB200_F32) break;
@@ -255,6 +276,7 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
         case MAGB200_BF16: MAGB200_SIMT_LAUNCH(MAGB200_BF16) break;
         default: set_error("matmul: unsupported dtype %d", p.dtype); return MAGB200_ERR_INVALID_ARG;
     }
+#undef MAGB200_SIMT_GO
 #undef MAGB200_SIMT_LAUNCH
     count_launch();
     MAGB200_CUDA_TRY(cudaGetLastError());
