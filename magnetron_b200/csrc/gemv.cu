@@ -352,17 +352,18 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
 // K-major 16-bit weights, cp.async-pipelined: grid = (persistent CTAs, nsplit, batch)
 // ------------------------------------------------------------------------------------------------
 // Same fragment scheme as skinny_km_mma_kernel, for problems with plenty of 16-row tiles. The 128-bit weight loads
-// do not go to registers: each lane keeps a private ring of kAsyncDepth steps (two 16-byte cp.async copies per step)
-// in shared memory, so 16 loads per lane -- 8 KB per warp -- are in flight without costing registers, and the ring
-// runs on across tile boundaries (the sequence of (tile, K step) pairs of a warp is flattened), so there is no drain
-// between tiles. Slots are private to a lane: cp.async.wait_group is all the synchronisation the ring needs.
-constexpr int kAsyncDepth = 8;
-constexpr size_t kAsyncRingBytes = (size_t)kAsyncDepth * 2 * kThreads * 16;   // 64 KB
+// do not go to registers: each lane keeps a private ring of kAsyncDepth steps in shared memory. A step covers 64 K
+// values of the lane's two rows (four 16-byte cp.async copies; the four lanes of a row fetch 128 contiguous bytes of
+// it), so 16 loads per lane -- 8 KB per warp -- are in flight without costing registers, and the ring runs on across
+// tile boundaries (the sequence of (tile, K step) pairs of a warp is flattened), so there is no drain between tiles.
+// Slots are private to a lane: cp.async.wait_group is all the synchronisation the ring needs.
+constexpr int kAsyncDepth = 4;
+constexpr size_t kAsyncRingBytes = (size_t)kAsyncDepth * 4 * kThreads * 16;   // 64 KB
 
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const SkinnyArgs a, const int M, const int xstride) {
     extern __shared__ __align__(16) unsigned char smem[];
-    uint4 *ring = reinterpret_cast<uint4 *>(smem);                                  // [depth][2][256 lanes]
+    uint4 *ring = reinterpret_cast<uint4 *>(smem);                                  // [depth][4][256 lanes]
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kAsyncRingBytes);            // [M][xstride]
 
     pdl_launch_dependents();
@@ -379,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
     const int64_t W = (int64_t)gridDim.x * kWarps;
     const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
     const int64_t t_begin = w * T / W, t_end = (w + 1) * T / W;      // a contiguous, even share of the tiles
-    const int nk = (kc + 31) >> 5;                                     // 32-wide K steps per tile
+    const int nk = (kc + 63) >> 6;                                     // 64-wide K steps per tile
     const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
     const uint16_t *xrow = xs + g * xstride;
     const bool has_x = g < M;
@@ -392,12 +393,14 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
     const uint16_t *pb = Bbase + min(i_tile * 16 + g + 8, a.N - 1) * a.ldb;
     auto issue = [&]() {
         if (i_tile < t_end) {
-            const int k = i_ks * 32 + t * 8;
-            const uint32_t nbytes = (k < kc) ? 16u : 0u;               // beyond the K range: zero-fill, nothing is read
-            const int kk = (k < kc) ? k : 0;
-            const uint32_t dst = ring_u32 + (uint32_t)i_slot * (2u * kThreads * 16u);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(pa + kk), "r"(nbytes) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + kThreads * 16u), "l"(pb + kk), "r"(nbytes) : "memory");
+            const int k = i_ks * 64 + t * 8, k2 = k + 32;
+            const uint32_t n1 = (k < kc) ? 16u : 0u, n2 = (k2 < kc) ? 16u : 0u;   // beyond the K range: zero-fill, nothing is read
+            const int kk = (k < kc) ? k : 0, kk2 = (k2 < kc) ? k2 : 0;
+            const uint32_t dst = ring_u32 + (uint32_t)i_slot * (4u * kThreads * 16u);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(pa + kk), "r"(n1) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + kThreads * 16u), "l"(pa + kk2), "r"(n2) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 2u * kThreads * 16u), "l"(pb + kk), "r"(n1) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 3u * kThreads * 16u), "l"(pb + kk2), "r"(n2) : "memory");
             if (++i_ks == nk) {
                 i_ks = 0;
                 ++i_tile;
@@ -427,18 +430,21 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
         }
     }
     __syncthreads();
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains: consecutive mma do not wait on each other
     int c_ks = 0, c_slot = 0;
     for (int64_t tile = t_begin; tile < t_end;) {
         asm volatile("cp.async.wait_group %0;" ::"n"(kAsyncDepth - 1) : "memory");
-        const uint4 *slot = ring + (size_t)c_slot * 2 * kThreads + threadIdx.x;
-        const uint4 wa = slot[0];
-        const uint4 wb = slot[kThreads];
-        const int k = c_ks * 32 + t * 8;
-        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        const uint4 *slot = ring + (size_t)c_slot * 4 * kThreads + threadIdx.x;
+        const uint4 wa = slot[0], wa2 = slot[kThreads];
+        const uint4 wb = slot[2 * kThreads], wb2 = slot[3 * kThreads];
+        const int k = c_ks * 64 + t * 8;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u), xv2 = make_uint4(0u, 0u, 0u, 0u);
         if (has_x && k < kc) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+        if (has_x && k + 32 < kc) xv2 = *reinterpret_cast<const uint4 *>(xrow + k + 32);
         mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
-        mma_16816<DT>(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+        mma_16816<DT>(c2, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+        mma_16816<DT>(c, wa2.x, wb2.x, wa2.y, wb2.y, xv2.x, xv2.y);
+        mma_16816<DT>(c2, wa2.z, wb2.z, wa2.w, wb2.w, xv2.z, xv2.w);
         c_slot = (c_slot + 1) & (kAsyncDepth - 1);
         issue();
         if (++c_ks == nk) {
@@ -447,8 +453,9 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
             for (int i = 0; i < 4; ++i) {
                 const int64_t n = r0 + g + (i >> 1) * 8;
                 const int m = 2 * t + (i & 1);
-                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i]);
+                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i] + c2[i]);
                 c[i] = 0.f;
+                c2[i] = 0.f;
             }
             c_ks = 0;
             ++tile;
@@ -622,7 +629,17 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             }
         }
         if (tiles * nsplit * p.batch_total >= warps_wanted / 2) {
-            // enough tiles for every warp of a persistent grid to stream several: the cp.async-pipelined kernel
+            // enough tiles for every warp of a persistent grid to stream several: the cp.async-pipelined kernel.
+            // Two CTAs per SM need the ring plus the activation rows within 110 KB: shorten the K chunk if necessary
+            // (more splits cost a few MB of partial sums, one CTA per SM costs half the loads in flight).
+            int64_t kch_two = ((int64_t)110 * 1024 - (int64_t)kAsyncRingBytes) / ((int64_t)M * 2) - 32;
+            kch_two -= kch_two % 256;
+            if (kch > kch_two && kch_two >= 1024) {
+                nsplit = (int)((p.K + kch_two - 1) / kch_two);
+                kch = (p.K + nsplit - 1) / nsplit;
+                kch = (kch + 255) / 256 * 256;
+                nsplit = (int)((p.K + kch - 1) / kch);
+            }
             pl.mma = true; pl.async = true; pl.KW = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
             pl.xstride = (kch + 63) / 64 * 64 + 32;
             pl.smem = kAsyncRingBytes + (size_t)M * pl.xstride * 2;
