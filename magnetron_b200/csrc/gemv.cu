@@ -634,11 +634,39 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             // (more splits cost a few MB of partial sums, one CTA per SM costs half the loads in flight).
             int64_t kch_two = ((int64_t)110 * 1024 - (int64_t)kAsyncRingBytes) / ((int64_t)M * 2) - 32;
             kch_two -= kch_two % 256;
-            if (kch > kch_two && kch_two >= 1024) {
+            const bool scarce = tiles * p.batch_total < warps_wanted;   // fewer row tiles than warps: K chunks are the only parallelism
+            if (scarce && kch > kch_two && kch_two >= 1024) {
                 nsplit = (int)((p.K + kch_two - 1) / kch_two);
                 kch = (p.K + nsplit - 1) / nsplit;
                 kch = (kch + 255) / 256 * 256;
                 nsplit = (int)((p.K + kch - 1) / kch);
+            }
+            // A warp streams whole (tile, K chunk) units; when the units do not divide evenly over the warps, the last
+            // part of the launch runs with few warps and little memory parallelism. For a long K try more splits and keep
+            // the cheapest by a cost in K steps fitted to measurements: 0.3 x the longest warp + 0.7 x the mean warp,
+            // plus what splitting costs (the second kernel, the partial sums).
+            if (scarce && p.K >= 4096 && kch_two >= 1024) {
+                auto cost_of = [&](int ns, int64_t kc_) {
+                    const int64_t gx = ((int64_t)kNumSMsB200 * 2 + (int64_t)ns * p.batch_total - 1) / ((int64_t)ns * p.batch_total);
+                    const double warps = (double)(gx * kWarps);
+                    const double steps = (double)((kc_ + 63) / 64);
+                    const double longest = (double)((tiles + (int64_t)warps - 1) / (int64_t)warps) * steps;
+                    const double mean = (double)tiles / warps * steps;
+                    return 0.3 * longest + 0.7 * mean + (ns > 1 ? 16.0 : 0.0) + 0.5 * ns;
+                };
+                int best_ns = nsplit;
+                int64_t best_kch = kch;
+                double best = cost_of(nsplit, kch);
+                for (int ns = nsplit + 1; ns <= 64 && p.K / ns >= 1024; ++ns) {
+                    int64_t kc_ = (p.K + ns - 1) / ns;
+                    kc_ = (kc_ + 255) / 256 * 256;
+                    const int ns_eff = (int)((p.K + kc_ - 1) / kc_);
+                    if (kc_ > kch_two) continue;
+                    const double cost = cost_of(ns_eff, kc_);
+                    if (cost < best - 1e-9) { best = cost; best_ns = ns_eff; best_kch = kc_; }
+                }
+                nsplit = best_ns;
+                kch = best_kch;
             }
             pl.mma = true; pl.async = true; pl.KW = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
             pl.xstride = (kch + 63) / 64 * 64 + 32;
