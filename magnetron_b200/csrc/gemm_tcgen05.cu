@@ -462,6 +462,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same arrive without the release fence. A release at cluster scope waits until the warp's earlier global stores are
+// performed; an epilogue warp that only hands back an accumulator it has finished reading (tcgen05.wait::ld has returned)
+// has nothing to publish, and with the fence every tile paid a store round trip before the next MMA could start.
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
@@ -655,6 +661,12 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     if (c0 + C::kEpiCols < BN2 / 2) {   // in flight during the write-out
                         tmem_ld_32x32(tbase + c0 + C::kEpiCols, ra);
                         tmem_ld_32x32(tbase + c0 + C::kEpiCols + 32, rb);
+                    } else {
+                        // the accumulator has been read completely: hand it back before the last write-out, so the next
+                        // tile's MMAs do not wait for this tile's stores
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
                     }
                     __syncwarp();
                     const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 7) * 8;
@@ -682,10 +694,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         if (n0 + c + j < args.N) store_from_f32<DT>(crow, c + j, __uint_as_float(r[j]));
                 }
             }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 16 epilogue warps of the pair
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 16 epilogue warps of the pair
         }
     }
 
