@@ -81,11 +81,42 @@ void *magb200_get_stream(int device);
  * few SMs free this way so that a collective running on another stream makes progress beside the persistent GEMM. */
 int  magb200_set_cta_limit(int device, int max_ctas);
 
+/* ---- failure handling ---------------------------------------------------------------------------
+ * Every wait inside a kernel (on an mbarrier of the TMA / tensor-core pipeline) is bounded: when it runs out the kernel
+ * raises a status word, stops issuing work, lets copies in flight land, frees its tensor memory and returns; the next
+ * magb200_synchronize / magb200_download reports MAGB200_ERR_TIMEOUT and the device stays usable. The reference has no
+ * counterpart (its CPU workers block on a condition variable, magnetron/cpu/mag_cpu_threadpool.c). The limit is one
+ * second unless changed here (1 ms .. 60 s, process wide). */
+int      magb200_set_wait_limit_ns(uint64_t ns);
+uint64_t magb200_get_wait_limit_ns(void);
+/* Test hooks, host side only -- nothing traps, faults or spins without a limit.
+ * test_leave_stage_unarmed: in the NEXT tensor-core matmul, the loads of K block `k_block` of each CTA's first tile are
+ *   never issued and their barrier is never armed, so the consumer's bounded wait runs out and the launch takes the
+ *   time-out path described above. -1 disarms.
+ * test_inject_fault: the next call that passes `site` fails with the given cudaError_t as if the CUDA runtime had
+ *   returned it (before any device is touched, so the error mapping can be tested without a GPU). */
+typedef enum magb200_fault_site_t {
+    MAGB200_FAULT_SITE_MALLOC = 1,   /* magb200_malloc */
+    MAGB200_FAULT_SITE_LAUNCH = 2    /* magb200_matmul */
+} magb200_fault_site_t;
+int  magb200_test_leave_stage_unarmed(int k_block);
+int  magb200_test_inject_fault(int site, int cuda_error);
+
 /* ---- storage: counterpart of mag_device_t::alloc_storage (magnetron/core/mag_backend.h:96) and of
  * the transfers the reference performs with memcpy on CPU storage (mag_copy_raw_,
  * magnetron/core/mag_op_stubs.c:1360-1375; mag_tensor_copy_data, magnetron/core/mag_tensor.c:232-250). */
 int  magb200_malloc(int device, void **out, size_t bytes);          /* 256-byte aligned device memory */
 int  magb200_free(int device, void *ptr);
+/* malloc / free go through a per-device pool: a freed block is kept (size classes, at most 12.5 % slack) and handed out
+ * again without a CUDA call or a synchronisation -- legal because every operator and copy of this library runs on the
+ * device's one launch stream, so the next user of a block is ordered after its last one. The reference frees with the
+ * storage's reference count (magnetron/cpu/mag_cpu.c:100-130); doing that with cudaFree would stall the stream per tensor.
+ * pool_stats: bytes handed out, bytes cached, and how many allocations were served from the cache / by cudaMalloc.
+ * pool_trim: waits for the device and returns every cached block to the driver. */
+int  magb200_pool_stats(int device, uint64_t *live_bytes, uint64_t *cached_bytes, uint64_t *hits, uint64_t *misses);
+int  magb200_pool_trim(int device);
+/* Free and total device memory as the driver reports them (cudaMemGetInfo); blocks cached by the pool count as used. */
+int  magb200_mem_info(int device, uint64_t *free_bytes, uint64_t *total_bytes);
 int  magb200_upload(int device, void *dst_device, const void *src_host, size_t bytes);   /* stream-ordered, then synchronised */
 int  magb200_download(int device, void *dst_host, const void *src_device, size_t bytes); /* stream-ordered, then synchronised */
 int  magb200_upload_async(int device, void *dst_device, const void *src_pinned_host, size_t bytes);

@@ -80,6 +80,13 @@ SIGNATURES = {
     "magb200_launch_count": (C.c_uint64, []),
     "magb200_launch_count_reset": (None, []),
     "magb200_force_kernel": (C.c_int, [C.c_int]),
+    "magb200_set_wait_limit_ns": (C.c_int, [C.c_uint64]),
+    "magb200_get_wait_limit_ns": (C.c_uint64, []),
+    "magb200_test_leave_stage_unarmed": (C.c_int, [C.c_int]),
+    "magb200_test_inject_fault": (C.c_int, [C.c_int, C.c_int]),
+    "magb200_pool_stats": (C.c_int, [C.c_int] + [C.POINTER(C.c_uint64)] * 4),
+    "magb200_pool_trim": (C.c_int, [C.c_int]),
+    "magb200_mem_info": (C.c_int, [C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "magb200_matmul_scatter": (C.c_int, [C.c_int, _VP, _VP, C.POINTER(C.c_void_p), C.c_int, C.c_int]),
     "magb200_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int]),
     "magb200_matmul_skinny_noalloc": (C.c_int, [C.c_int, C.c_void_p, _VP, _VP, _VP]),

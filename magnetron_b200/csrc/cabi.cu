@@ -5,6 +5,8 @@
 #include <stdarg.h>
 #include <stdlib.h>
 #include <atomic>
+#include <unordered_map>
+#include <vector>
 
 namespace magb200 {
 
@@ -28,10 +30,48 @@ int cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
 }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
+int num_sms() {
+    static std::atomic<int> cached[32];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 32) { (void)cudaGetLastError(); return kDefaultSMs; }
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); return kDefaultSMs; }
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
+// ---- host-side fault injection (tests of the error paths; nothing on the device is made to fail) -------------------
+// One pending fault per site: the next call that passes the site returns the given CUDA error as if the runtime had.
+static std::atomic<int> g_inject[3] = {{0}, {0}, {0}};   // index = magb200_fault_site_t
+static cudaError_t take_injected(int site) { return (cudaError_t)g_inject[site].exchange(0); }
+
+// ---- device memory pool ------------------------------------------------------------------------------------------------
+// magnetron allocates a storage buffer per tensor and frees it when the last reference goes
+// (magnetron/core/mag_tensor.c:88-93, magnetron/cpu/mag_cpu.c:100-130); with cudaMalloc / cudaFree behind that, every
+// intermediate of a layer costs a device synchronisation. Freed blocks are therefore kept in size classes (eight per power
+// of two, at most 12.5 % slack) and handed out again without any CUDA call. Reuse needs no synchronisation because every
+// operator and copy of this library runs on the device's one launch stream: whatever still reads a freed block was
+// submitted before whatever will write it next. Blocks go back to the driver at shutdown or when cudaMalloc runs dry.
+struct MemPool {
+    std::mutex mu;
+    std::unordered_map<size_t, std::vector<void *>> free_blocks;   // class size -> blocks
+    std::unordered_map<void *, size_t> live;                       // block -> class size
+    size_t cached_bytes = 0, live_bytes = 0;
+    uint64_t hits = 0, misses = 0;
+};
+static size_t size_class(size_t bytes) {
+    if (bytes <= 512) return 512;
+    int top = 63 - __builtin_clzll((unsigned long long)(bytes - 1));   // bytes in (2^top, 2^(top+1)]
+    const size_t step = (size_t)1 << (top - 2);                         // an eighth of the upper power of two
+    return (bytes + step - 1) / step * step;
+}
+
 // ---- per-device state ---------------------------------------------------------------------------
 constexpr int kMaxDevices = 16;
+struct AddrRange { uintptr_t lo, hi; };
 struct DeviceState {
-    bool ready = false;
+    std::atomic<bool> ready{false};
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;   // launch stream (own_stream unless the caller installed one)
     float *scratch = nullptr;        // split-K partial sums
@@ -44,6 +84,22 @@ struct DeviceState {
     int cta_limit = 0;               // 0: all SMs; else the tensor-core GEMMs launch at most this many CTAs
     cudaStream_t h2d_stream = nullptr;   // copy streams of the overlapped transfers (created on first use)
     cudaStream_t d2h_stream = nullptr;
+    bool d2h_pending = false;            // overlapped downloads submitted since the last synchronize
+    // Results written by the decode kernels launched since the last fully ordered operation. Those kernels let their
+    // successors start early, so they may still be running when a later decode kernel begins: a weight operand inside one
+    // of these ranges must not be fetched ahead of the kernel's wait for its predecessors.
+    AddrRange in_flight[32];
+    int n_in_flight = 0;
+    bool in_flight_overflow = false;
+    MemPool *pool = nullptr;
+
+    void reset() {
+        own_stream = stream = nullptr; scratch = nullptr; scratch_bytes = 0; status = nullptr;
+        for (int i = 0; i < 3; ++i) { staging[i] = nullptr; staging_bytes[i] = 0; }
+        name[0] = 0; capturing = false; cta_limit = 0; h2d_stream = d2h_stream = nullptr; d2h_pending = false;
+        n_in_flight = 0; in_flight_overflow = false;
+        ready.store(false, std::memory_order_release);
+    }
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -57,9 +113,9 @@ static int ensure_device(int device, DeviceState **out) {
     int rc = check_device(device);
     if (rc) return rc;
     DeviceState &d = g_dev[device];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_mu);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             int n = 0;
             cudaError_t e = cudaGetDeviceCount(&n);
             if (e != cudaSuccess || device >= n) {
@@ -81,7 +137,8 @@ static int ensure_device(int device, DeviceState **out) {
             MAGB200_CUDA_TRY(cudaMemset(d.status, 0, 256));
             d.scratch_bytes = 32ull << 20;
             MAGB200_CUDA_TRY(cudaMalloc(&d.scratch, d.scratch_bytes));
-            d.ready = true;
+            if (!d.pool) d.pool = new MemPool();
+            d.ready.store(true, std::memory_order_release);
         }
     }
     MAGB200_CUDA_TRY(cudaSetDevice(device));
@@ -95,13 +152,37 @@ static int ensure_scratch(DeviceState &d, size_t bytes) {
         set_error("the split-K workspace would have to grow to %zu bytes during stream capture; run the same call once before capturing", bytes);
         return MAGB200_ERR_INVALID_ARG;
     }
-    MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    // kernels submitted to an earlier launch stream (before magb200_set_stream) may still use the old buffer
+    MAGB200_CUDA_TRY(cudaDeviceSynchronize());
     MAGB200_CUDA_TRY(cudaFree(d.scratch));
     d.scratch = nullptr; d.scratch_bytes = 0;
     size_t want = bytes + (bytes >> 2);
     MAGB200_CUDA_TRY(cudaMalloc(&d.scratch, want));
     d.scratch_bytes = want;
     return MAGB200_OK;
+}
+
+// ---- which results may still be in flight under programmatic dependent launch -----------------------------------------
+static void ordered_point(DeviceState &d) { d.n_in_flight = 0; d.in_flight_overflow = false; }   // a fully ordered launch or copy
+static void note_early_result(DeviceState &d, const void *ptr, size_t bytes) {
+    if (d.n_in_flight < 32) { d.in_flight[d.n_in_flight].lo = (uintptr_t)ptr; d.in_flight[d.n_in_flight].hi = (uintptr_t)ptr + bytes; ++d.n_in_flight; }
+    else d.in_flight_overflow = true;
+}
+// Byte range an operand of the canonical problem can touch: base .. last addressed element.
+static AddrRange weight_range(const GemmProblem &g) {
+    int64_t reach = (g.K - 1) * g.sBk + (g.N - 1) * g.sBn;
+    for (int i = 0; i < g.nbatch; ++i) reach += (g.bshape[i] - 1) * g.bsB[i];
+    AddrRange r;
+    r.lo = (uintptr_t)g.B;
+    r.hi = r.lo + (size_t)(reach + 1) * dtype_size(g.dtype);
+    return r;
+}
+static bool weights_settled(const DeviceState &d, const GemmProblem &g) {
+    if (d.in_flight_overflow) return false;
+    const AddrRange w = weight_range(g);
+    for (int i = 0; i < d.n_in_flight; ++i)
+        if (w.lo < d.in_flight[i].hi && d.in_flight[i].lo < w.hi) return false;
+    return true;
 }
 
 static int check_status_word(DeviceState &d) {
@@ -153,6 +234,20 @@ static int check_view(const magb200_view_t *v, const char *what) {
     for (int i = 0; i < v->rank; ++i)
         if (v->shape[i] < 1 || v->strides[i] < 0) { set_error("%s: dim %d has extent %lld stride %lld", what, i, (long long)v->shape[i], (long long)v->strides[i]); return MAGB200_ERR_INVALID_ARG; }
     if (v->offset < 0) { set_error("%s: negative storage offset", what); return MAGB200_ERR_INVALID_ARG; }
+    return MAGB200_OK;
+}
+// Bytes of storage a view reaches, from the storage base: (offset + sum (shape-1)*stride + 1) elements.
+static size_t view_reach_bytes(const magb200_view_t *v) {
+    int64_t last = v->offset;
+    for (int i = 0; i < v->rank; ++i) last += (v->shape[i] - 1) * v->strides[i];
+    return (size_t)(last + 1) * dtype_size(v->dtype);
+}
+static int check_view_fits(const magb200_view_t *v, size_t storage_bytes, const char *what) {
+    const size_t need = view_reach_bytes(v);
+    if (need > storage_bytes) {
+        set_error("%s: the view reaches %zu bytes into a storage buffer of %zu", what, need, storage_bytes);
+        return MAGB200_ERR_INVALID_ARG;
+    }
     return MAGB200_OK;
 }
 static inline char *view_data(const magb200_view_t *v) { return (char *)v->base + v->offset * (int64_t)dtype_size(v->dtype); }
@@ -306,19 +401,23 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
             int rc = ensure_scratch(d, skinny_scratch_bytes(g));
             if (rc) return rc;
             int split = 0;
-            rc = launch_skinny(g, d.stream, d.scratch, d.scratch_bytes, &split);
+            rc = launch_skinny(g, d.stream, d.scratch, d.scratch_bytes, &split, weights_settled(d, g));
             g_last_kernel = split ? MAGB200_KERNEL_SKINNY_SPLITK : MAGB200_KERNEL_SKINNY;
+            note_early_result(d, g.C, (size_t)(g.batch_total * g.M * g.N) * dtype_size(g.dtype));
             return rc;
         }
         case MAGB200_KERNEL_TCGEN05:
             g_last_kernel = MAGB200_KERNEL_TCGEN05;
+            ordered_point(d);
             return launch_gemm_tcgen05(g, d.stream, d.cta_limit, d.status);
         case MAGB200_KERNEL_TCGEN05_2SM:
             g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
+            ordered_point(d);
             return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status);
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
             if (int rc = ensure_scratch(d, simt_scratch_bytes(g))) return rc;
+            ordered_point(d);
             return launch_gemm_simt(g, d.stream, d.scratch, d.scratch_bytes);
     }
 }
@@ -360,6 +459,7 @@ static int cast_device(DeviceState &d, const magb200_view_t *src, const magb200_
     if (n != view_numel(dst)) { set_error("cast: element counts differ (%lld vs %lld)", (long long)n, (long long)view_numel(dst)); return MAGB200_ERR_SHAPE; }
     if (!view_is_contiguous(dst)) { set_error("cast: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
     CollapsedDims cd = collapse_dims(src->rank, src->shape, src->strides);
+    ordered_point(d);
     return launch_cast(src->dtype, dst->dtype, view_data(src), view_data(dst), n, cd, view_is_contiguous(src), d.stream);
 }
 
@@ -410,12 +510,19 @@ int magb200_device_shutdown(int device) {
     if (!d.ready) return MAGB200_OK;
     MAGB200_CUDA_TRY(cudaSetDevice(device));
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
+    MAGB200_CUDA_TRY(cudaDeviceSynchronize());
     for (int i = 0; i < 3; ++i) if (d.staging[i]) { cudaFree(d.staging[i]); d.staging[i] = nullptr; d.staging_bytes[i] = 0; }
     cudaFree(d.scratch); cudaFree(d.status);
-    if (d.h2d_stream) { cudaStreamSynchronize(d.h2d_stream); cudaStreamDestroy(d.h2d_stream); }
-    if (d.d2h_stream) { cudaStreamSynchronize(d.d2h_stream); cudaStreamDestroy(d.d2h_stream); }
+    if (d.h2d_stream) cudaStreamDestroy(d.h2d_stream);
+    if (d.d2h_stream) cudaStreamDestroy(d.d2h_stream);
     cudaStreamDestroy(d.own_stream);
-    d = DeviceState();
+    if (d.pool) {   // cached blocks go back to the driver; blocks still held by the caller stay valid and are forgotten
+        std::lock_guard<std::mutex> pl(d.pool->mu);
+        for (auto &cls : d.pool->free_blocks) for (void *b : cls.second) cudaFree(b);
+        d.pool->free_blocks.clear(); d.pool->live.clear();
+        d.pool->cached_bytes = d.pool->live_bytes = 0;
+    }
+    d.reset();
     return MAGB200_OK;
 }
 
@@ -426,6 +533,8 @@ int magb200_synchronize(int device) {
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
     if (d->d2h_stream) MAGB200_CUDA_TRY(cudaStreamSynchronize(d->d2h_stream));
     if (d->h2d_stream) MAGB200_CUDA_TRY(cudaStreamSynchronize(d->h2d_stream));
+    d->d2h_pending = false;
+    ordered_point(*d);
     return check_status_word(*d);
 }
 
@@ -433,7 +542,7 @@ int magb200_set_cta_limit(int device, int max_ctas) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
-    if (max_ctas < 0 || max_ctas > kNumSMsB200) { set_error("set_cta_limit: %d is outside 0..%d", max_ctas, kNumSMsB200); return MAGB200_ERR_INVALID_ARG; }
+    if (max_ctas < 0 || max_ctas > num_sms()) { set_error("set_cta_limit: %d is outside 0..%d", max_ctas, num_sms()); return MAGB200_ERR_INVALID_ARG; }
     d->cta_limit = max_ctas;
     return MAGB200_OK;
 }
@@ -452,26 +561,104 @@ void *magb200_get_stream(int device) {
     return (void *)d->stream;
 }
 
+static int order_after(cudaStream_t later, cudaStream_t earlier);
+
+// Release every cached block of the pool to the driver (after the device has gone idle). Returns the bytes released.
+static size_t pool_trim(DeviceState &d) {
+    MemPool &p = *d.pool;
+    if (p.cached_bytes == 0) return 0;
+    cudaDeviceSynchronize();
+    size_t released = p.cached_bytes;
+    for (auto &cls : p.free_blocks) for (void *b : cls.second) cudaFree(b);
+    p.free_blocks.clear();
+    p.cached_bytes = 0;
+    return released;
+}
+
 int magb200_malloc(int device, void **out, size_t bytes) {
+    if (!out) { set_error("malloc: null out pointer"); return MAGB200_ERR_INVALID_ARG; }
+    *out = nullptr;
+    if (cudaError_t inj = take_injected(MAGB200_FAULT_SITE_MALLOC)) return cuda_fail(inj, "cudaMalloc (injected)", __FILE__, __LINE__);
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
-    if (!out) { set_error("malloc: null out pointer"); return MAGB200_ERR_INVALID_ARG; }
-    *out = nullptr;
-    MAGB200_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 1));  // cudaMalloc returns >= 256-byte aligned memory
+    MemPool &p = *d->pool;
+    const size_t cls = size_class(bytes ? bytes : 1);
+    std::lock_guard<std::mutex> lock(p.mu);
+    auto it = p.free_blocks.find(cls);
+    if (it != p.free_blocks.end() && !it->second.empty()) {
+        *out = it->second.back();
+        it->second.pop_back();
+        p.cached_bytes -= cls;
+        ++p.hits;
+    } else {
+        void *ptr = nullptr;
+        cudaError_t e = cudaMalloc(&ptr, cls);   // cudaMalloc returns >= 256-byte aligned memory
+        if (e == cudaErrorMemoryAllocation && pool_trim(*d) > 0) { (void)cudaGetLastError(); e = cudaMalloc(&ptr, cls); }
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc", __FILE__, __LINE__);
+        *out = ptr;
+        ++p.misses;
+    }
+    p.live[*out] = cls;
+    p.live_bytes += cls;
     return MAGB200_OK;
 }
 int magb200_free(int device, void *ptr) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
-    if (ptr) { MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream)); MAGB200_CUDA_TRY(cudaFree(ptr)); }
+    if (!ptr) return MAGB200_OK;
+    // a download on the copy stream may still read the block: whoever gets it next writes on the launch stream, after this
+    if (d->d2h_pending && d->d2h_stream && !d->capturing) { if ((rc = order_after(d->stream, d->d2h_stream))) return rc; }
+    MemPool &p = *d->pool;
+    std::lock_guard<std::mutex> lock(p.mu);
+    auto it = p.live.find(ptr);
+    if (it == p.live.end()) {   // not from this pool (allocated before a shutdown): plain release
+        MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+        MAGB200_CUDA_TRY(cudaFree(ptr));
+        return MAGB200_OK;
+    }
+    const size_t cls = it->second;
+    p.live.erase(it);
+    p.live_bytes -= cls;
+    p.free_blocks[cls].push_back(ptr);
+    p.cached_bytes += cls;
+    return MAGB200_OK;
+}
+int magb200_pool_stats(int device, uint64_t *live_bytes, uint64_t *cached_bytes, uint64_t *hits, uint64_t *misses) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(d->pool->mu);
+    if (live_bytes) *live_bytes = d->pool->live_bytes;
+    if (cached_bytes) *cached_bytes = d->pool->cached_bytes;
+    if (hits) *hits = d->pool->hits;
+    if (misses) *misses = d->pool->misses;
+    return MAGB200_OK;
+}
+int magb200_mem_info(int device, uint64_t *free_bytes, uint64_t *total_bytes) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    size_t f = 0, t = 0;
+    MAGB200_CUDA_TRY(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return MAGB200_OK;
+}
+int magb200_pool_trim(int device) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(d->pool->mu);
+    pool_trim(*d);
     return MAGB200_OK;
 }
 int magb200_upload_async(int device, void *dst, const void *src, size_t bytes) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
+    ordered_point(*d);
     MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d->stream));
     return MAGB200_OK;
 }
@@ -511,6 +698,7 @@ int magb200_download_overlapped(int device, void *dst, const void *src, size_t b
     if (rc || (rc = copy_stream(*d, &d->d2h_stream))) return rc;
     if ((rc = order_after(d->d2h_stream, d->stream))) return rc;          // the producer of src has been submitted
     MAGB200_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d->d2h_stream));
+    d->d2h_pending = true;
     return MAGB200_OK;
 }
 int magb200_upload(int device, void *dst, const void *src, size_t bytes) {
@@ -552,6 +740,7 @@ int magb200_fill(int device, const magb200_view_t *dst, double value) {
     if (rc) return rc;
     if ((rc = check_view(dst, "fill result"))) return rc;
     if (!view_is_contiguous(dst)) { set_error("fill: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
+    ordered_point(*d);
     return launch_fill(dst->dtype, view_data(dst), view_numel(dst), value, d->stream);
 }
 
@@ -564,6 +753,7 @@ int magb200_matmul_result_shape(const magb200_view_t *x, const magb200_view_t *y
 }
 
 int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r) {
+    if (cudaError_t inj = take_injected(MAGB200_FAULT_SITE_LAUNCH)) return cuda_fail(inj, "kernel launch (injected)", __FILE__, __LINE__);
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
@@ -612,6 +802,29 @@ int magb200_reduce_broadcast(int device, void *cuda_stream, const void *stage, v
     return launch_reduce_broadcast(dtype, stage, peer_out, nranks, rank, rows_per_rank * n, cuda_stream ? (cudaStream_t)cuda_stream : d->stream);
 }
 
+int magb200_set_wait_limit_ns(uint64_t ns) {
+    if (ns < 1000ull * 1000ull || ns > 60ull * 1000ull * 1000ull * 1000ull) {
+        set_error("set_wait_limit_ns: %llu is outside 1 ms .. 60 s", (unsigned long long)ns);
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    set_wait_limit_ns(ns);
+    return MAGB200_OK;
+}
+uint64_t magb200_get_wait_limit_ns(void) { return get_wait_limit_ns(); }
+int magb200_test_leave_stage_unarmed(int k_block) {
+    if (k_block < -1) { set_error("test_leave_stage_unarmed: k_block must be >= 0 (or -1 to disarm)"); return MAGB200_ERR_INVALID_ARG; }
+    set_skip_kb_once(k_block);
+    return MAGB200_OK;
+}
+int magb200_test_inject_fault(int site, int cuda_error) {
+    if (site < MAGB200_FAULT_SITE_MALLOC || site > MAGB200_FAULT_SITE_LAUNCH || cuda_error < 0) {
+        set_error("test_inject_fault: unknown site %d", site);
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    g_inject[site].store(cuda_error);
+    return MAGB200_OK;
+}
+
 int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }
@@ -627,6 +840,8 @@ int magb200_matmul_host(int device, const magb200_view_t *x, size_t x_bytes, con
     if (rc) return rc;
     if ((rc = check_view(x, "matmul x")) || (rc = check_view(y, "matmul y")) || (rc = check_view(r, "matmul result"))) return rc;
     const size_t r_bytes = (size_t)view_numel(r) * dtype_size(r->dtype);
+    if ((rc = check_view_fits(x, x_bytes, "matmul x")) || (rc = check_view_fits(y, y_bytes, "matmul y"))) return rc;
+    if (!view_is_contiguous(r)) { set_error("matmul: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
     if ((rc = ensure_staging(*d, 0, x_bytes)) || (rc = ensure_staging(*d, 1, y_bytes)) || (rc = ensure_staging(*d, 2, r_bytes))) return rc;
     MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[0], x->base, x_bytes, cudaMemcpyHostToDevice, d->stream));
     MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[1], y->base, y_bytes, cudaMemcpyHostToDevice, d->stream));
@@ -644,6 +859,8 @@ int magb200_cast_host(int device, const magb200_view_t *src, size_t src_bytes, c
     if (rc) return rc;
     if ((rc = check_view(src, "cast source")) || (rc = check_view(dst, "cast result"))) return rc;
     const size_t dst_bytes = (size_t)view_numel(dst) * dtype_size(dst->dtype);
+    if ((rc = check_view_fits(src, src_bytes, "cast source"))) return rc;
+    if (!view_is_contiguous(dst)) { set_error("cast: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
     if ((rc = ensure_staging(*d, 0, src_bytes)) || (rc = ensure_staging(*d, 2, dst_bytes))) return rc;
     MAGB200_CUDA_TRY(cudaMemcpyAsync(d->staging[0], src->base, src_bytes, cudaMemcpyHostToDevice, d->stream));
     magb200_view_t ds = *src, dd = *dst;

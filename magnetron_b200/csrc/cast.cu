@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kThreads) fill_kernel(void *__restrict__ dst, 
 
 int grid_for(int64_t work_items) {
     int64_t blocks = (work_items + kThreads - 1) / kThreads;
-    const int64_t cap = (int64_t)kNumSMsB200 * 16;  // 16 resident 256-thread blocks cover every SM several times
+    const int64_t cap = (int64_t)num_sms() * 16;  // 16 resident 256-thread blocks cover every SM several times
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (int)blocks;

@@ -13,12 +13,17 @@
 namespace magb200 {
 
 constexpr int kMaxDims = MAGB200_MAX_DIMS;
-constexpr int kNumSMsB200 = 148;
+constexpr int kDefaultSMs = 148;   // a B200; used only until the current device has been asked
+int num_sms();                     // multiprocessor count of the current device (cached per device)
 
 // ---- error plumbing (thread-local message, never an exception across the C ABI) -----------------
 void set_error(const char *fmt, ...);
 int  cuda_fail(cudaError_t e, const char *what, const char *file, int line);
 void count_launch(int n = 1);
+// run-time knobs of the tensor-core kernels (gemm_tcgen05.cu)
+void set_wait_limit_ns(uint64_t ns);
+uint64_t get_wait_limit_ns();
+void set_skip_kb_once(int kb);
 
 #define MAGB200_CUDA_TRY(expr)                                                        \
     do {                                                                              \
@@ -128,7 +133,7 @@ struct GemmProblem {
 int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes);
 size_t simt_scratch_bytes(const GemmProblem &p);
 bool skinny_supported(const GemmProblem &p);
-int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk);
+int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled);
 bool tcgen05_supported(const GemmProblem &p);
 // Destination of a scatter epilogue: every rank's staging buffer [ranks][rows_per_rank][N] (device or peer-mapped pointers)
 struct ScatterTarget {

@@ -37,6 +37,12 @@ __device__ __forceinline__ void two_sum(float a, float b, float &s, float &e) {
     e = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bp)), __fsub_rn(b, bp));
 }
 
+// total + low, except that an infinite total stays infinite: TwoSum of an infinity leaves NaN in the low part
+// (inf - inf), which must not turn a legitimately infinite product sum into NaN.
+__device__ __forceinline__ float fold_low(float total, float low) {
+    return (fabsf(total) == __int_as_float(0x7F800000)) ? total : __fadd_rn(total, low);
+}
+
 // AKF: the A tile is fetched walking k fastest (else m fastest); BNF: the B tile walking n fastest (else k fastest).
 // Compile-time modes make every shared-memory offset of the fetch a constant.
 template <int DT, bool AKF, bool BNF>
@@ -186,7 +192,7 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
             const int64_t idx = cbase + gm * p.N + gn;
             if (nsplit == 1) {
                 float v = acc[i][j];
-                if constexpr (kCompensated) v = __fadd_rn(total[i][j], low[i][j]);
+                if constexpr (kCompensated) v = fold_low(total[i][j], low[i][j]);
                 store_from_f32<DT>(C, idx, v);
             } else {
                 float hi = acc[i][j], lo = 0.f;
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(256) simt_finalize_kernel(const float *__restr
             total = sum;
             low = __fadd_rn(low, __fadd_rn(e, partial[((int64_t)s * 2 + 1) * elems + i]));
         }
-        store_from_f32<DT>(C, i, __fadd_rn(total, low));
+        store_from_f32<DT>(C, i, fold_low(total, low));
     }
 }
 
@@ -223,8 +229,8 @@ SimtPlan plan_simt(const GemmProblem &p) {
     pl.tiles = pl.tiles_m * pl.tiles_n * p.batch_total;
     pl.nsplit = 1;
     // an output smaller than the GPU: cut K so that about one CTA per SM is busy, never below 256 K values per CTA
-    if (pl.tiles > 0 && pl.tiles * 2 <= kNumSMsB200 && p.K >= 512) {
-        int64_t s = kNumSMsB200 / pl.tiles;
+    if (pl.tiles > 0 && pl.tiles * 2 <= num_sms() && p.K >= 512) {
+        int64_t s = num_sms() / pl.tiles;
         if (s > p.K / 256) s = p.K / 256;
         if (s > 16) s = 16;
         if (s > 1) pl.nsplit = (int)s;
@@ -258,7 +264,7 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
     }
     const int64_t elems = p.batch_total * p.M * p.N;
     int64_t fin_blocks = (elems + 255) / 256;
-    if (fin_blocks > kNumSMsB200 * 8) fin_blocks = kNumSMsB200 * 8;
+    if (fin_blocks > num_sms() * 8) fin_blocks = num_sms() * 8;
     const bool akf = (p.sAk == 1) || (p.sAm != 1);   // walk k fastest unless m is the unit-stride dim
     const bool bnf = (p.sBn == 1) || (p.sBk != 1);
 #define MAGB200_SIMT_GO(DT, AKF, BNF) \

@@ -22,6 +22,8 @@
 
 #include <cuda.h>  // CUtensorMap and enums only; the driver entry point is resolved at run time
 
+#include <atomic>
+
 namespace magb200 {
 
 namespace {
@@ -30,7 +32,6 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr int kStatusTimeout = 1;
 constexpr int kMaxScatterRanks = 8;
 
@@ -45,6 +46,8 @@ struct TcArgs {
     int64_t tiles_m, tiles_n, total_tiles;
     int num_kb;
     int *status;
+    uint64_t wait_limit_ns;             // every mbarrier wait gives up after this long without progress
+    int skip_kb;                        // test hook: K block of each CTA's first tile whose loads are never issued (-1: none)
     // scatter epilogue (tensor-parallel row-sharded GEMM): rows of block o go to rank o's staging buffer, slot `rank`
     int scatter_ranks;                  // 0: plain epilogue into C
     int scatter_rank;
@@ -89,14 +92,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 // Bounded wait. Returns false (and raises the CTA's abort flag) when the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 63u) {
+        if ((spin & 15u) == 15u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+            if (global_timer_ns() - t0 > limit_ns) { *abort_flag = 1; return false; }
         }
     }
 }
@@ -232,7 +235,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
                 const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
                 for (int kb = 0; kb < args.num_kb; ++kb) {
-                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
+                    if (kb == args.skip_kb && tile == (int64_t)blockIdx.x) {   // test hook: this stage is never armed, its consumer's wait runs out
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     const uint32_t full = full0 + 8u * stage;
                     const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes;
@@ -274,11 +281,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             bool ok = true;
             for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
                 const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
-                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 for (int kb = 0; kb < args.num_kb; ++kb) {
-                    if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(full0 + 8u * stage, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes;
@@ -309,7 +316,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int64_t n0 = tn * BN;
             // every lane waits (each needs the acquire), then the warp agrees on one outcome so that the
             // warp-wide tcgen05.ld below is never reached by a partial warp
-            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag, args.wait_limit_ns));
             if (!ok) break;
             tcgen05_fence_after();
             if (vec_ok && !staged) {
@@ -432,15 +439,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //              to the peer's (a shared::cluster address), so both producers learn at once that the stage is free.
 //   tfull[a]   accumulator a complete: likewise committed to both CTAs' barriers.
 //   tempty[a]  accumulator a drained: the 8 epilogue warps of BOTH CTAs arrive on the leader's barrier (count 16).
+//
+// A stage holds 128 K values (two 64-wide sub-blocks, each a 128-byte-swizzled tile as TMA writes it), so one barrier round
+// trip of the MMA thread covers eight tcgen05.mma instead of four. That thread is the scarce resource: issuing one MMA costs
+// it about 65 clocks, a wait, two commits and the loop bookkeeping about 350 more, against 128 clocks of tensor-pipe time per
+// MMA. With four MMAs per round trip the thread needed about 610 clocks for 512 clocks of tensor work (measured with the
+// loads switched off: the pipe was idle 16 % of the time whatever the memory system did); with eight it needs about 870 for
+// 1024 and the pipe is the limit.
 // =====================================================================================================================
 constexpr int kThreads2 = 320;  // warp 0 TMA, warp 1 MMA (leader only), warps 2-9 epilogue (two per TMEM lane quarter)
 constexpr int BN2 = 256;
 
 struct Cfg2 {
-    static constexpr int kABytes = BM * BK * 2;          // this CTA's 128 rows of A
-    static constexpr int kBBytes = (BN2 / 2) * BK * 2;   // this CTA's 128 columns of B
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = 6;
+    static constexpr int kSub = 2;                               // 64-wide K sub-blocks per stage
+    static constexpr int kSubABytes = BM * BK * 2;               // this CTA's 128 rows of A, one sub-block
+    static constexpr int kSubBBytes = (BN2 / 2) * BK * 2;        // this CTA's 128 columns of B, one sub-block
+    static constexpr int kABytes = kSub * kSubABytes;
+    static constexpr int kBBytes = kSub * kSubBBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;        // 64 KB
+    static constexpr int kStages = 3;
     static constexpr int kTmemCols = 2 * BN2;
     static constexpr int kEpiWarps = 8;                           // two warps per TMEM lane quarter, 128 columns each
     static constexpr int kEpiCols = 64;                           // output columns per staging pass: 128-byte row segments
@@ -486,6 +503,18 @@ __device__ __forceinline__ void tcgen05_mma_f16_2sm(uint32_t tmem_d, uint64_t ad
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// tcgen05.mma with each shared-memory descriptor given as (low word, high word): from one K step, sub-block or stage to the
+// next only the low word (the start address in 16-byte units) moves, one integer add per operand on the issuing thread.
+__device__ __forceinline__ void tcgen05_mma_f16_2sm_split(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 template <int DT>
@@ -554,26 +583,35 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 }
                 const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
                 const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
-                for (int kb = 0; kb < args.num_kb; ++kb) {
-                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                const int num_kg = (args.num_kb + C::kSub - 1) / C::kSub;   // stages per tile; a sub-block past K is zero-filled by TMA
+                for (int kg = 0; kg < num_kg; ++kg) {
+                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
+                    if (kg == args.skip_kb && tile == pair) {   // test hook: neither CTA loads or arms this stage, the MMA thread's wait runs out
+                        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     const uint32_t full = full_leader0 + 8u * stage;
                     const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes;
                     if (leader) {
                         mbar_arrive_expect_tx(full0 + 8u * stage, 2u * (uint32_t)C::kStageBytes);
                     }
-                    const int k0 = kb * BK;
-                    if (!args.a_mn) {
-                        tma_load_5d_2sm(sa, &tmA, full, k0, m0, a2, a1, a0);
-                    } else {
 #pragma unroll
-                        for (int c = 0; c < BM / 64; ++c) tma_load_5d_2sm(sa + c * 8192, &tmA, full, m0 + c * 64, k0, a2, a1, a0);
-                    }
-                    if (!args.b_mn) {
-                        tma_load_5d_2sm(sb, &tmB, full, k0, n0, b2, b1, b0);
-                    } else {
+                    for (int sub = 0; sub < C::kSub; ++sub) {
+                        const int k0 = (kg * C::kSub + sub) * BK;
+                        const uint32_t ssa = sa + sub * C::kSubABytes, ssb = sb + sub * C::kSubBBytes;
+                        if (!args.a_mn) {
+                            tma_load_5d_2sm(ssa, &tmA, full, k0, m0, a2, a1, a0);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < (BN2 / 2) / 64; ++c) tma_load_5d_2sm(sb + c * 8192, &tmB, full, n0 + c * 64, k0, b2, b1, b0);
+                            for (int c = 0; c < BM / 64; ++c) tma_load_5d_2sm(ssa + c * 8192, &tmA, full, m0 + c * 64, k0, a2, a1, a0);
+                        }
+                        if (!args.b_mn) {
+                            tma_load_5d_2sm(ssb, &tmB, full, k0, n0, b2, b1, b0);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < (BN2 / 2) / 64; ++c) tma_load_5d_2sm(ssb + c * 8192, &tmB, full, n0 + c * 64, k0, b2, b1, b0);
+                        }
                     }
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -588,28 +626,42 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const uint32_t a_lbo = args.a_mn ? 8192u : 16u, a_step = args.a_mn ? 2048u : 32u;
             const uint32_t b_lbo = args.b_mn ? 8192u : 16u, b_step = args.b_mn ? 2048u : 32u;
             const uint32_t empty_peer0 = map_to_cta(empty0, 1), tfull_peer0 = map_to_cta(tfull0, 1);
+            // descriptors of stage 0, sub-block 0
+            const uint64_t adesc0 = make_smem_desc(tiles, a_lbo, 1024u), bdesc0 = make_smem_desc(tiles + C::kABytes, b_lbo, 1024u);
+            const uint32_t a_hi = (uint32_t)(adesc0 >> 32), b_hi = (uint32_t)(bdesc0 >> 32);
+            const uint32_t a_k = a_step >> 4, b_k = b_step >> 4;                                      // one K step of 16
+            constexpr uint32_t kStage16 = (uint32_t)C::kStageBytes >> 4;
+            constexpr uint32_t kSubA16 = (uint32_t)C::kSubABytes >> 4, kSubB16 = (uint32_t)C::kSubBBytes >> 4;
+            const int num_kg = (args.num_kb + C::kSub - 1) / C::kSub;
             int stage = 0;
             uint32_t phase = 0, titer = 0;
+            uint32_t a_lo = (uint32_t)adesc0, b_lo = (uint32_t)bdesc0;                                // of the current stage
+            uint32_t full = full0, empty_own = empty0, empty_peer = empty_peer0;
             bool ok = true;
             for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs, ++titer) {
                 const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
-                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN2;
-                for (int kb = 0; kb < args.num_kb; ++kb) {
-                    if (!mbar_wait(full0 + 8u * stage, phase, abort_flag)) { ok = false; break; }
+                for (int kg = 0; kg < num_kg; ++kg) {
+                    if (!mbar_wait(full, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                     tcgen05_fence_after();
-                    const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
-                    const uint32_t sb = sa + C::kABytes;
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t ad = make_smem_desc(sa + k * a_step, a_lbo, 1024u);
-                        const uint64_t bd = make_smem_desc(sb + k * b_step, b_lbo, 1024u);
-                        tcgen05_mma_f16_2sm(tmem_d, ad, bd, idesc, (kb | k) ? 1u : 0u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kg ? 1u : 0u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16, a_hi, b_lo + kSubB16, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + a_k, a_hi, b_lo + kSubB16 + b_k, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 2 * a_k, a_hi, b_lo + kSubB16 + 2 * b_k, b_hi, idesc, 1u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 3 * a_k, a_hi, b_lo + kSubB16 + 3 * b_k, b_hi, idesc, 1u);
+                    tcgen05_commit_2sm(empty_own);        // stage free: tell this CTA's producer ...
+                    tcgen05_commit_2sm(empty_peer);       // ... and the peer's
+                    if (++stage == C::kStages) {
+                        stage = 0; phase ^= 1u;
+                        a_lo = (uint32_t)adesc0; b_lo = (uint32_t)bdesc0; full = full0; empty_own = empty0; empty_peer = empty_peer0;
+                    } else {
+                        a_lo += kStage16; b_lo += kStage16; full += 8u; empty_own += 8u; empty_peer += 8u;
                     }
-                    tcgen05_commit_2sm(empty0 + 8u * stage);        // stage free: tell this CTA's producer ...
-                    tcgen05_commit_2sm(empty_peer0 + 8u * stage);   // ... and the peer's
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) { tcgen05_commit_2sm(tfull0 + 8u * acc); tcgen05_commit_2sm(tfull_peer0 + 8u * acc); }
             }
@@ -627,7 +679,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
             const int64_t row = tm * 2 * BM + (int64_t)rank * BM + quarter * 32 + lane;
             const int64_t n0 = tn * BN2;
-            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag));
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag, args.wait_limit_ns));
             if (!ok) break;
             tcgen05_fence_after();
             const int chalf = (warp - 2) >> 2;            // which 128-column half of the tile this warp drains
@@ -757,7 +809,52 @@ bool operand_ok(const OperandDesc &o) {
     return true;
 }
 
+int encode_uncached(const OperandDesc &o, int dtype, CUtensorMap *out);
+
+// A tensor map depends only on the operand's address, extents, pitches and box, so the driver call that builds it
+// (about a microsecond, two per matmul) is remembered per host thread: a decode loop or a layer that multiplies the same
+// weights again finds its maps here. An entry can never be stale: equal key, equal encoding.
+struct MapKey {
+    const void *base;
+    int64_t inner_extent, outer_extent, outer_pitch;
+    int64_t bext[kMaxBatchDims], bstride[kMaxBatchDims];
+    int32_t has[kMaxBatchDims];
+    uint32_t box_inner, box_outer;
+    int32_t dtype;
+};
+constexpr int kMapCacheSlots = 128;
+struct MapCache {
+    MapKey keys[kMapCacheSlots];
+    CUtensorMap maps[kMapCacheSlots];
+    uint64_t hash[kMapCacheSlots];
+    bool used[kMapCacheSlots];
+};
+uint64_t hash_key(const MapKey &k) {
+    uint64_t h = 1469598103934665603ull;
+    const unsigned char *b = reinterpret_cast<const unsigned char *>(&k);
+    for (size_t i = 0; i < sizeof(MapKey); ++i) { h ^= b[i]; h *= 1099511628211ull; }
+    return h;
+}
 int encode(const OperandDesc &o, int dtype, CUtensorMap *out) {
+    static thread_local MapCache *cache = nullptr;
+    if (!cache) cache = new MapCache();   // zero-initialised; lives as long as the thread
+    MapKey k;
+    memset(&k, 0, sizeof(k));             // padding bytes take part in the hash
+    k.base = o.base; k.inner_extent = o.inner_extent; k.outer_extent = o.outer_extent; k.outer_pitch = o.outer_pitch;
+    for (int d = 0; d < kMaxBatchDims; ++d) { k.bext[d] = o.bext[d]; k.bstride[d] = o.has[d] ? o.bstride[d] : 0; k.has[d] = o.has[d]; }
+    k.box_inner = o.box_inner; k.box_outer = o.box_outer; k.dtype = dtype;
+    const uint64_t h = hash_key(k);
+    const int s0 = (int)(h % kMapCacheSlots), s1 = (int)((h >> 20) % kMapCacheSlots);   // two candidate slots per key
+    for (int s : {s0, s1})
+        if (cache->used[s] && cache->hash[s] == h && memcmp(&cache->keys[s], &k, sizeof(k)) == 0) { *out = cache->maps[s]; return MAGB200_OK; }
+    int rc = encode_uncached(o, dtype, out);
+    if (rc) return rc;
+    const int s = cache->used[s0] ? s1 : s0;
+    cache->keys[s] = k; cache->maps[s] = *out; cache->hash[s] = h; cache->used[s] = true;
+    return MAGB200_OK;
+}
+
+int encode_uncached(const OperandDesc &o, int dtype, CUtensorMap *out) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return MAGB200_ERR_CUDA; }
     // fastest dim first: {inner, outer, b2, b1, b0}
@@ -828,26 +925,47 @@ int pick_bn(const GemmProblem &p) {
         const int bn = cand[i];
         if (bn > 64 && p.N <= bn / 2) continue;  // more than half of the tile would be padding
         const int64_t tiles = tm * ((p.N + bn - 1) / bn) * p.batch_total;
-        const double waves = (double)((tiles + kNumSMsB200 - 1) / kNumSMsB200);
+        const double waves = (double)((tiles + num_sms() - 1) / num_sms());
         const double cost = waves * tile_cost[i];
         if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
     }
     return best;
 }
 
+// ---- run-time knobs (set through the C ABI) ---------------------------------------------------------------------------
+std::atomic<uint64_t> g_wait_limit_ns{1000ull * 1000ull * 1000ull};
+std::atomic<int> g_skip_kb_once{-1};      // consumed by the next tensor-core launch
+
+// cudaFuncSetAttribute applies to the current device only, so the opt-in to more than 48 KB of dynamic shared memory is
+// remembered per (kernel, device): bit d of `done` is set once device d has it.
+template <typename K>
+int ensure_smem_optin(K kernel, size_t bytes, std::atomic<uint32_t> &done) {
+    int dev = 0;
+    MAGB200_CUDA_TRY(cudaGetDevice(&dev));
+    const uint32_t bit = 1u << (dev & 31);
+    if (!(done.load(std::memory_order_acquire) & bit)) {
+        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        done.fetch_or(bit, std::memory_order_release);
+    }
+    return MAGB200_OK;
+}
+
+void fill_knobs(TcArgs &args) {
+    args.wait_limit_ns = g_wait_limit_ns.load();
+    args.skip_kb = g_skip_kb_once.exchange(-1);
+}
+
 template <int BN, int DT>
 int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit) {
     using C = Cfg<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, DT>;
-    static bool attr_set = false;  // per template instantiation
-    if (!attr_set) {
-        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
-        attr_set = true;
-    }
+    static std::atomic<uint32_t> optin{0};  // per template instantiation
+    if (int rc = ensure_smem_optin(kernel, C::kSmemBytes, optin)) return rc;
+    fill_knobs(args);
     args.tiles_m = (p.M + BM - 1) / BM;
     args.tiles_n = (p.N + BN - 1) / BN;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
-    const int64_t max_ctas = cta_limit > 0 ? cta_limit : kNumSMsB200;
+    const int64_t max_ctas = cta_limit > 0 ? cta_limit : num_sms();
     const unsigned grid = (unsigned)(args.total_tiles < max_ctas ? args.total_tiles : max_ctas);
     kernel<<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, args);
     count_launch();
@@ -859,15 +977,13 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
 template <int DT>
 int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit) {
     auto kernel = gemm_tcgen05_2sm_kernel<DT>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg2::kSmemBytes));
-        attr_set = true;
-    }
+    static std::atomic<uint32_t> optin{0};
+    if (int rc = ensure_smem_optin(kernel, Cfg2::kSmemBytes, optin)) return rc;
+    fill_knobs(args);
     args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     args.tiles_n = (p.N + BN2 - 1) / BN2;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
-    const int64_t max_pairs = (cta_limit > 1 ? cta_limit : kNumSMsB200) / 2;
+    const int64_t max_pairs = (cta_limit > 1 ? cta_limit : num_sms()) / 2;
     const unsigned pairs = (unsigned)(args.total_tiles < max_pairs ? args.total_tiles : max_pairs);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -886,6 +1002,10 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
 }
 
 }  // namespace
+
+void set_wait_limit_ns(uint64_t ns) { g_wait_limit_ns.store(ns); }
+uint64_t get_wait_limit_ns() { return g_wait_limit_ns.load(); }
+void set_skip_kb_once(int kb) { g_skip_kb_once.store(kb); }
 
 bool tcgen05_supported(const GemmProblem &p) {
     if (p.dtype != MAGB200_BF16 && p.dtype != MAGB200_F16) return false;
@@ -907,7 +1027,7 @@ bool tcgen05_2sm_supported(const GemmProblem &p) {
 bool tcgen05_2sm_preferred(const GemmProblem &p) {
     if (!tcgen05_2sm_supported(p)) return false;
     const int64_t tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch_total;
-    return tiles >= kNumSMsB200 / 2;
+    return tiles >= num_sms() / 2;
 }
 
 int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {

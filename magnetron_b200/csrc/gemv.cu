@@ -23,6 +23,8 @@
 // so results do not depend on scheduling.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace magb200 {
 
 namespace {
@@ -45,13 +47,17 @@ struct SkinnyArgs {
     int nbatch;
     int64_t bshape[kMaxBatchDims], bsA[kMaxBatchDims], bsB[kMaxBatchDims];
     int64_t batch_total;
+    int early_weights;  // 1: the weights were not written by a kernel that may still be running; they may be fetched before pdl_wait()
 };
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while its
 // predecessor in the stream is still running. Everything that does not depend on the predecessor's output (index set-up,
 // the first weight loads) runs before pdl_wait(); the activations are read only after it. pdl_launch_dependents() lets
 // the successor start its own independent part early. Decode is a chain of microsecond kernels, so this hides most of
-// the launch latency between them.
+// the launch latency between them. Because every kernel here lets its successor start at once, a kernel can be running
+// while kernels several launches back have not finished: weights are fetched ahead of pdl_wait() only when the host has
+// established that none of those kernels writes them (SkinnyArgs::early_weights); a weight operand that is itself a fresh
+// result -- K in q @ K^T right after the k projection -- is read after the wait like the activations.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -244,6 +250,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
 
     // The weights do not depend on the previous kernel: the first steps of the first tile are in flight before the
     // activations are even staged (and, under programmatic dependent launch, before the previous kernel has finished).
+    if (!a.early_weights) pdl_wait();
     uint4 pre_a[kPre], pre_b[kPre];
     const int npre = (t_begin < t_end) ? min(nfull, kPre) : 0;
     if (npre > 0) {
@@ -412,9 +419,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
         asm volatile("cp.async.commit_group;" ::: "memory");          // one group per step, empty past the end
     };
 
+    if (!a.early_weights) pdl_wait();
     for (int q = 0; q < kAsyncDepth; ++q) issue();
 
-    // the weight copies above do not depend on the previous kernel; the activations do
+    // the weight copies above do not depend on a kernel still in flight (or came after the wait); the activations may
     pdl_wait();
     {
         const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
@@ -601,7 +609,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         int nsplit = 1;
         if (kch > kch_max) nsplit = (int)((p.K + kch_max - 1) / kch_max);
         const int64_t tiles = (p.N + 15) / 16;
-        const int64_t warps_wanted = (int64_t)kNumSMsB200 * 16;
+        const int64_t warps_wanted = (int64_t)num_sms() * 16;
         // few row tiles and a long K: split K across CTAs too (each split keeps at least 2048 K values)
         if (tiles * kWarps * p.batch_total < warps_wanted && p.K >= 8192) {
             int want = (int)((warps_wanted + tiles * kWarps * p.batch_total - 1) / (tiles * kWarps * p.batch_total));
@@ -647,7 +655,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             // plus what splitting costs (the second kernel, the partial sums).
             if (scarce && p.K >= 4096 && kch_two >= 1024) {
                 auto cost_of = [&](int ns, int64_t kc_) {
-                    const int64_t gx = ((int64_t)kNumSMsB200 * 2 + (int64_t)ns * p.batch_total - 1) / ((int64_t)ns * p.batch_total);
+                    const int64_t gx = ((int64_t)num_sms() * 2 + (int64_t)ns * p.batch_total - 1) / ((int64_t)ns * p.batch_total);
                     const double warps = (double)(gx * kWarps);
                     const double steps = (double)((kc_ + 63) / 64);
                     const double longest = (double)((tiles + (int64_t)warps - 1) / (int64_t)warps) * steps;
@@ -673,7 +681,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             pl.smem = kAsyncRingBytes + (size_t)M * pl.xstride * 2;
             const int64_t other = (int64_t)nsplit * p.batch_total;
             const int per_sm = pl.smem <= 110 * 1024 ? 2 : 1;
-            int64_t want = ((int64_t)kNumSMsB200 * per_sm + other - 1) / other;
+            int64_t want = ((int64_t)num_sms() * per_sm + other - 1) / other;
             if (want < 1) want = 1;
             pl.gridx = (unsigned)want;
             return pl.nsplit <= 65535;
@@ -688,7 +696,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         const int64_t blocks = (tiles + RW - 1) / RW;
         const int64_t other = (int64_t)nsplit * p.batch_total;
         // many short CTAs (one or two tiles per warp) let the hardware scheduler even out the SMs
-        int64_t want = (int64_t)kNumSMsB200 * 32;
+        int64_t want = (int64_t)num_sms() * 32;
         want = (want + other - 1) / other;
         if (want < 1) want = 1;
         pl.gridx = (unsigned)(blocks < want ? blocks : want);
@@ -696,7 +704,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     }
     if (km) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
-        const int64_t warps_wanted = (int64_t)kNumSMsB200 * 2 * kWarps;
+        const int64_t warps_wanted = (int64_t)num_sms() * 2 * kWarps;
         pl.R = (p.N >= 4 * warps_wanted) ? 4 : (p.N >= 2 * warps_wanted ? 2 : 1);
         if (M > 4 && pl.R > 2) pl.R = 2;  // keep R*M accumulators + unpacked operands in registers
         int64_t kch_max = (int64_t)(kSmemBudget / ((size_t)M * E::size));
@@ -720,7 +728,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         pl.kch = kch; pl.nsplit = nsplit;
         pl.smem = (size_t)M * kch * E::size;
         int64_t blocks = (p.N + (int64_t)kWarps * pl.R - 1) / ((int64_t)kWarps * pl.R);
-        int64_t cap = ((int64_t)kNumSMsB200 * 2 * 4) / ((int64_t)nsplit * p.batch_total) ;
+        int64_t cap = ((int64_t)num_sms() * 2 * 4) / ((int64_t)nsplit * p.batch_total) ;
         if (cap < 1) cap = 1;
         pl.gridx = (unsigned)(blocks < cap ? blocks : cap);
     } else {
@@ -732,8 +740,8 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         int nsplit = 1;
         if (kch > kch_max) nsplit = (int)((p.K + kch_max - 1) / kch_max);
         const int64_t blocks = (p.N + CB - 1) / CB;
-        if (blocks * p.batch_total < kNumSMsB200 && p.K >= 2048) {
-            int want = (int)((kNumSMsB200 * 2 + blocks * p.batch_total - 1) / (blocks * p.batch_total));
+        if (blocks * p.batch_total < num_sms() && p.K >= 2048) {
+            int want = (int)((num_sms() * 2 + blocks * p.batch_total - 1) / (blocks * p.batch_total));
             int cap = (int)(p.K / 512);
             if (want > cap) want = cap;
             if (want > nsplit) nsplit = want;
@@ -750,9 +758,30 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     return pl.nsplit <= 65535;
 }
 
+// Opt-in to more than 48 KB of dynamic shared memory: once per (kernel, device) with the largest size any plan asks for,
+// not on every launch (the attribute call costs more host time than a small decode kernel runs). The kernels share a few
+// function signatures, so the record is a small table keyed by the kernel's address.
+constexpr size_t kSmemOptIn = 128 * 1024;
+struct OptInEntry { std::atomic<uintptr_t> kernel{0}; std::atomic<uint32_t> devices{0}; };
+OptInEntry g_optin[128];
+
 template <typename K>
 int set_smem(K kernel, size_t bytes) {
-    if (bytes > 48 * 1024) MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (bytes <= 48 * 1024) return MAGB200_OK;
+    int dev = 0;
+    MAGB200_CUDA_TRY(cudaGetDevice(&dev));
+    const uint32_t bit = 1u << (dev & 31);
+    const uintptr_t me = (uintptr_t)kernel;
+    OptInEntry *e = nullptr;
+    for (unsigned probe = 0; probe < 128 && !e; ++probe) {
+        OptInEntry &c = g_optin[((me >> 4) + probe) & 127u];
+        uintptr_t cur = c.kernel.load(std::memory_order_acquire);
+        if (cur == 0 && c.kernel.compare_exchange_strong(cur, me)) cur = me;
+        if (cur == me) e = &c;
+    }
+    if (e && bytes <= kSmemOptIn && (e->devices.load(std::memory_order_acquire) & bit)) return MAGB200_OK;
+    MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes > kSmemOptIn ? bytes : kSmemOptIn)));
+    if (e && bytes <= kSmemOptIn) e->devices.fetch_or(bit, std::memory_order_release);
     return MAGB200_OK;
 }
 
@@ -798,7 +827,7 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
 }
 
 template <int DT>
-int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk) {
+int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled) {
     Plan pl;
     if (!make_plan<DT>(p, pl)) { set_error("skinny: layout not supported"); return MAGB200_ERR_INVALID_ARG; }
     const int64_t total = p.batch_total * p.M * p.N;
@@ -811,6 +840,7 @@ int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scra
     a.N = p.N; a.K = p.K; a.sAm = p.sAm; a.sAk = p.sAk;
     a.ldb = pl.km ? p.sBn : p.sBk;
     a.kch = pl.kch; a.nsplit = pl.nsplit; a.nbatch = p.nbatch; a.batch_total = p.batch_total;
+    a.early_weights = weights_settled ? 1 : 0;
     for (int d = 0; d < kMaxBatchDims; ++d) { a.bshape[d] = p.bshape[d]; a.bsA[d] = p.bsA[d]; a.bsB[d] = p.bsB[d]; }
     int rc;
     switch (p.M) {
@@ -822,7 +852,7 @@ int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scra
     if (rc) return rc;
     if (pl.nsplit > 1) {
         int64_t blocks = (total + kThreads - 1) / kThreads;
-        if (blocks > kNumSMsB200 * 8) blocks = kNumSMsB200 * 8;
+        if (blocks > num_sms() * 8) blocks = num_sms() * 8;
         if (int rc2 = launch_pdl(skinny_finalize_kernel<DT>, dim3((unsigned)blocks), dim3(kThreads), 0, st, (const float *)scratch, p.C, total, pl.nsplit)) return rc2;
         count_launch();
         MAGB200_CUDA_TRY(cudaGetLastError());
@@ -857,11 +887,13 @@ size_t skinny_scratch_bytes(const GemmProblem &p) {
     return (size_t)pl.nsplit * p.batch_total * p.M * p.N * sizeof(float);
 }
 
-int launch_skinny(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk) {
+// `weights_settled`: the caller knows that no kernel which may still be running writes the weight operand, so the kernels
+// may fetch weights before they wait for their predecessors (see pdl_wait above). Pass false when in doubt.
+int launch_skinny(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled) {
     switch (p.dtype) {
-        case MAGB200_F32:  return launch_dt<MAGB200_F32>(p, st, scratch, scratch_bytes, used_splitk);
-        case MAGB200_F16:  return launch_dt<MAGB200_F16>(p, st, scratch, scratch_bytes, used_splitk);
-        case MAGB200_BF16: return launch_dt<MAGB200_BF16>(p, st, scratch, scratch_bytes, used_splitk);
+        case MAGB200_F32:  return launch_dt<MAGB200_F32>(p, st, scratch, scratch_bytes, used_splitk, weights_settled);
+        case MAGB200_F16:  return launch_dt<MAGB200_F16>(p, st, scratch, scratch_bytes, used_splitk, weights_settled);
+        case MAGB200_BF16: return launch_dt<MAGB200_BF16>(p, st, scratch, scratch_bytes, used_splitk, weights_settled);
     }
     set_error("skinny: unsupported dtype %d", p.dtype);
     return MAGB200_ERR_INVALID_ARG;

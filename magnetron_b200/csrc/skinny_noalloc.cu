@@ -76,5 +76,7 @@ int magb200_matmul_skinny_noalloc(int device, void *cuda_stream, const magb200_v
     }
     float *scratch = nullptr;
     if ((rc = scratch_address(device, &scratch))) return rc;
-    return launch_skinny(g, (cudaStream_t)cuda_stream, scratch, kNoAllocScratchFloats * sizeof(float), nullptr);
+    // the caller's stream is not tracked by this library: whether an earlier kernel on it still writes y is unknown, so the
+    // kernels read the weights only after they have waited for their predecessors
+    return launch_skinny(g, (cudaStream_t)cuda_stream, scratch, kNoAllocScratchFloats * sizeof(float), nullptr, /*weights_settled=*/false);
 }

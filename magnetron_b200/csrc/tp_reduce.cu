@@ -61,7 +61,7 @@ int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out,
         if (!out.p[i] || ((uintptr_t)out.p[i] & 15u)) { set_error("reduce_broadcast: output pointer of rank %d is null or misaligned", i); return MAGB200_ERR_INVALID_ARG; }
     const int64_t vecs = block_elems / 8;
     int64_t blocks = (vecs + kThreads - 1) / kThreads;
-    if (blocks > kNumSMsB200 * 8) blocks = kNumSMsB200 * 8;
+    if (blocks > num_sms() * 8) blocks = num_sms() * 8;
     if (blocks < 1) return MAGB200_OK;
     if (dtype == MAGB200_BF16)
         reduce_broadcast_kernel<MAGB200_BF16><<<(unsigned)blocks, kThreads, 0, stream>>>((const uint4 *)stage, out, ranks, rank, vecs);

@@ -1,0 +1,212 @@
+"""GPU tests of the parts of the matmul path that are about scheduling and failure handling rather than arithmetic:
+weight operands that are themselves fresh results of the decode kernels,
+the bounded device-side waits, the device memory pool, non-finite operands, and more than one device per process."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import magnetron_b200 as mb
+from oracle import mag_oracle as O
+from tests import cases
+from tests.common import unit_roundoff
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(dt, rng, shape, scale):
+    return O.f32_to_bits(dt, cases.gen_storage(rng, shape, scale))
+
+
+def test_fresh_result_as_weight_operand_in_a_decode_chain(gpu):
+    """k = x @ Wk.T followed at once by s = q @ k.T on the same stream, many times with changing x and no
+    synchronisation in between. The decode kernels let their successors start early and fetch weights ahead of their
+    wait -- but k is a result that may still be in flight, so it must be read after the wait: every s must be the
+    product with the k of ITS round."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(9)
+    T, H, D = 8, 1024, 1024
+    wk = bits(dt, rng, (D, H), 0.05)
+    tw = mb.Tensor.from_bits(gpu, dt, wk)
+    rounds = 24
+    xs = [bits(dt, rng, (T, H), 1.0) for _ in range(rounds)]
+    qb = bits(dt, rng, (4, D), 1.0)
+    tq = mb.Tensor.from_bits(gpu, dt, qb)
+    txs = [mb.Tensor.from_bits(gpu, dt, x) for x in xs]
+    tk = mb.Tensor(gpu, dt, (T, D))
+    outs = [mb.Tensor(gpu, dt, (4, T)) for _ in range(rounds)]
+    mb.synchronize(gpu)
+    for r in range(rounds):
+        mb.check(L.magb200_matmul(gpu, C.byref(txs[r].view_struct()), C.byref(tw.T.view_struct()), C.byref(tk.view_struct())))
+        assert mb.last_kernel().startswith("skinny")
+        mb.check(L.magb200_matmul(gpu, C.byref(tq.view_struct()), C.byref(tk.T.view_struct()), C.byref(outs[r].view_struct())))
+        assert mb.last_kernel().startswith("skinny")
+    mb.synchronize(gpu)
+    wf, qf = O.bits_to_f64(dt, wk), O.bits_to_f64(dt, qb)
+    for r in range(rounds):
+        kf = O.bits_to_f64(dt, O.f32_to_bits(dt, (O.bits_to_f64(dt, xs[r]) @ wf.T).astype(np.float32)))
+        truth = qf @ kf.T
+        got = O.bits_to_f64(dt, outs[r].to_bits())
+        # k itself is rounded to bf16 once more on the device than in this restatement only where the fp32 sums differ in
+        # the last bit: allow two output roundings
+        assert np.max(np.abs(got - truth)) <= 4 * 2.0 ** -8 * np.max(np.abs(truth)), r
+    for t in txs + outs + [tw, tq, tk]:
+        t.release()
+
+
+@pytest.mark.parametrize("kernel,M,N", [("tcgen05", 128, 128), ("tcgen05_2sm", 256, 256)])
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(gpu, kernel, M, N):
+    """One-tile launch whose producer leaves one stage unarmed (test hook): the MMA thread's bounded wait runs out after
+    the (shortened) limit, the kernel drains and returns, synchronize reports MAGB200_ERR_TIMEOUT, and the next ordinary
+    matmul on the same device is correct. Nothing traps, faults or spins without a limit."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(5)
+    K = 512
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.1)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    out = mb.Tensor(gpu, dt, (M, N))
+    old = L.magb200_get_wait_limit_ns()
+    mb.check(L.magb200_set_wait_limit_ns(5_000_000))           # 5 ms
+    mb.force_kernel(kernel)
+    try:
+        mb.check(L.magb200_test_leave_stage_unarmed(2))
+        mb.check(L.magb200_matmul(gpu, C.byref(tx.view_struct()), C.byref(tw.T.view_struct()), C.byref(out.view_struct())))
+        rc = L.magb200_synchronize(gpu)
+        assert rc == mb.ERR_TIMEOUT, (rc, L.magb200_last_error())
+        assert b"wait ran out" in L.magb200_last_error()
+        # the hook was consumed by that launch; the same call now runs normally
+        mb.check(L.magb200_matmul(gpu, C.byref(tx.view_struct()), C.byref(tw.T.view_struct()), C.byref(out.view_struct())))
+        mb.synchronize(gpu)
+    finally:
+        mb.force_kernel(None)
+        mb.check(L.magb200_set_wait_limit_ns(old))
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    m = O.error_metrics(dt, out.to_bits(), xf @ wf.T, np.abs(xf) @ np.abs(wf).T)
+    assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, m
+    for t in (tx, tw, out):
+        t.release()
+
+
+def test_pool_reuses_freed_blocks_without_cuda_calls(gpu):
+    L = mb.lib()
+
+    def stats():
+        v = [C.c_uint64() for _ in range(4)]
+        mb.check(L.magb200_pool_stats(gpu, *[C.byref(x) for x in v]))
+        return [x.value for x in v]          # live, cached, hits, misses
+
+    a = mb.Tensor(gpu, O.BFLOAT16, (1000, 1000))
+    ptr = a.ptr
+    live0, _, hits0, misses0 = stats()
+    a.release()
+    live1, cached1, _, _ = stats()
+    assert live1 < live0 and cached1 >= 2_000_000
+    b = mb.Tensor(gpu, O.BFLOAT16, (999, 1001))      # same size class
+    _, _, hits2, misses2 = stats()
+    assert b.ptr == ptr and hits2 == hits0 + 1 and misses2 == misses0
+    b.release()
+    # results stay right when a block changes hands while its last reader is still queued
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(2)
+    xb, wb = bits(dt, rng, (512, 512), 1.0), bits(dt, rng, (512, 512), 0.1)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    want = (tx @ tw.T).to_bits()
+    for _ in range(8):
+        r = tx @ tw.T          # block comes from the pool ...
+        r2 = r @ tw.T          # ... is read by a second matmul ...
+        r.release()            # ... and goes back while that may still run
+        junk = mb.Tensor(gpu, dt, (512, 512))
+        mb.check(L.magb200_fill(gpu, C.byref(junk.view_struct()), 7.0))
+        got2 = r2.to_bits()
+        first = (tx @ tw.T)
+        assert np.array_equal(first.to_bits(), want)
+        ref2 = (first @ tw.T).to_bits()
+        assert np.array_equal(got2, ref2)
+        for t in (r2, junk, first):
+            t.release()
+    mb.check(L.magb200_pool_trim(gpu))
+    assert stats()[1] == 0
+    for t in (tx, tw):
+        t.release()
+
+
+def test_non_finite_operands_float32(gpu):
+    """float32 goes through the compensated FFMA kernel, whose error-free summation must not turn an infinite sum into NaN."""
+    dt = O.FLOAT32
+    rng = np.random.default_rng(14)
+    for (M, N, K) in ((96, 80, 200), (64, 64, 4096)):     # the second shape splits K over CTAs
+        xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.1)
+        xb[1, 7] = 0x7FC00000
+        xb[2, 9] = 0x7F800000
+        wb[5, K - 3] = 0xFF800000
+        tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+        r = tx @ tw.T
+        assert mb.last_kernel() == "simt"
+        f = O.bits_to_f64(dt, r.to_bits())
+        with np.errstate(all="ignore"):
+            truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
+        assert np.array_equal(np.isnan(f), np.isnan(truth))
+        assert np.array_equal(np.isposinf(f), np.isposinf(truth)) and np.array_equal(np.isneginf(f), np.isneginf(truth))
+        fin = np.isfinite(truth)
+        assert np.max(np.abs(f[fin] - truth[fin])) <= 1e-5 * np.max(np.abs(truth[fin]))
+        for t in (r, tx, tw):
+            t.release()
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_2sm", "skinny", "simt"])
+def test_non_finite_operands(gpu, kernel):
+    """NaN and infinities in the operands: rows / columns that meet them are NaN or infinite in the result, every other
+    element is unaffected. Recorded here: the tensor-core and decode kernels round with the hardware converters and
+    produce 0x7FFF for a NaN result, the FFMA kernel the canonical 0x7FC0; the reference's own NaN pattern depends on
+    the CPU specialisation, so only NaN-ness is asserted."""
+    dt = O.BFLOAT16
+    M, N, K = (4, 512, 512) if kernel == "skinny" else (256, 256, 256)
+    rng = np.random.default_rng(13)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.1)
+    xb[1, 7] = 0x7FC0            # NaN in activation row 1
+    xb[2, 9] = 0x7F80            # +inf in activation row 2
+    wb[5, 11] = 0xFF80           # -inf in weight row 5 (output column 5)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    mb.force_kernel(kernel)
+    try:
+        r = tx @ tw.T
+        assert mb.last_kernel().startswith(kernel)
+    finally:
+        mb.force_kernel(None)
+    got = r.to_bits()
+    f = O.bits_to_f64(dt, got)
+    with np.errstate(all="ignore"):
+        truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
+    assert np.array_equal(np.isnan(f), np.isnan(truth))
+    assert np.array_equal(np.isposinf(f), np.isposinf(truth)) and np.array_equal(np.isneginf(f), np.isneginf(truth))
+    fin = np.isfinite(truth)
+    assert np.max(np.abs(f[fin] - truth[fin])) <= 2.0 ** -7 * np.max(np.abs(truth[fin]))
+    nan_patterns = set(np.unique(got[np.isnan(f)]).tolist())
+    assert nan_patterns <= {0x7FFF, 0x7FC0, 0xFFC0, 0xFFFF}, [hex(p) for p in nan_patterns]
+    for t in (r, tx, tw):
+        t.release()
+
+
+def test_every_visible_device_runs_the_big_shared_memory_kernels(gpu):
+    """The opt-in to more than 48 KB of dynamic shared memory is per device: one tensor-core and one decode matmul on
+    every visible device of this process."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(3)
+    xb, wb = bits(dt, rng, (256, 512), 1.0), bits(dt, rng, (512, 512), 0.1)
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    for dev in range(mb.device_count()):
+        mb.check(L.magb200_device_init(dev))
+        tx, tw = mb.Tensor.from_bits(dev, dt, xb), mb.Tensor.from_bits(dev, dt, wb)
+        for kernel, rows in (("tcgen05_2sm", 256), ("tcgen05", 256), ("skinny", 8)):
+            mb.force_kernel(kernel)
+            try:
+                r = tx.slice(0, 0, rows) @ tw.T
+            finally:
+                mb.force_kernel(None)
+            m = O.error_metrics(dt, r.to_bits(), xf[:rows] @ wf.T, np.abs(xf[:rows]) @ np.abs(wf).T)
+            assert m["e"] <= unit_roundoff(dt) + 512 * 2.0 ** -24, (dev, kernel, m)
+            r.release()
+        tx.release(); tw.release()

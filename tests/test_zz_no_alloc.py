@@ -26,6 +26,12 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(gpu):
     wb = O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.02))
     tw = mb.Tensor.from_bits(gpu, dt, wb)
     stream = L.magb200_get_stream(gpu)
+
+    def free_bytes():
+        f, t = C.c_uint64(), C.c_uint64()
+        mb.check(L.magb200_mem_info(gpu, C.byref(f), C.byref(t)))
+        return f.value
+
     for call in range(2):
         xb = O.f32_to_bits(dt, cases.gen_storage(rng, (M, K), 1.0 + call))
         tx = mb.Tensor.from_bits(gpu, dt, xb)
@@ -34,9 +40,15 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(gpu):
         want_bits = want.to_bits()
         out = mb.Tensor(gpu, dt, (M, N))
         mb.check(L.magb200_fill(gpu, C.byref(out.view_struct()), 0.0))
+        mb.synchronize(gpu)
+        before = free_bytes()
         mb.check(L.magb200_matmul_skinny_noalloc(gpu, stream, C.byref(tx.view_struct()), C.byref(tw.T.view_struct()),
                                                  C.byref(out.view_struct())))
         mb.synchronize(gpu)
+        # the very first call on a device may load the library's code for this entry point, built-in array included (the
+        # driver loads modules on first use); from then on the amount of free device memory must not move
+        if call > 0:
+            assert free_bytes() == before, "the allocation-free entry point changed the amount of free device memory"
         got = out.to_bits()
         assert np.array_equal(got, want_bits), f"call {call}: {np.count_nonzero(got != want_bits)} elements differ"
         # and the result is right, not merely the same: fp64 truth on sampled columns
