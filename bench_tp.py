@@ -3,7 +3,8 @@
 `value` = whole-job TFLOP/s of the layer (7.99 TFLOP at M = 8192) with column-sharded QKV and gate/up, row-sharded o
 and down, and the two all-reduces of the paired schedule inside the timed region; time is the maximum over ranks of
 CUDA-event time. The same line reports the variant that also all-gathers the column-sharded outputs, the token sweep
-M in {1, 8, 512}. `bench.py --gpus 1 --workload tp` runs the same layer unsharded as the scaling yardstick.
+M in {1, 8, 512}. `bench.py --gpus 1 --workload tp` runs the same layer unsharded as the scaling yardstick (the one-GPU line of
+`bench.py` carries the same figure as `tp_layer_1gpu`).
 """
 from __future__ import annotations
 
@@ -42,7 +43,9 @@ def main(args, pk):
     if args.impl == "reference":
         if rank == 0:
             import bench
-            r = bench.cpu_reference(max(1, min(args.steps, 40)), min(args.warmup, 2))
+            cpu = bench.CpuRef()
+            r = bench.cpu_prefill_step(cpu, max(1, min(args.steps, 20)), min(args.warmup, 1)) if cpu.api else None
+            cpu.close()
             line = {"impl": "reference", "metric": "bf16 matmul TFLOP/s", "value": r["value"] if r else None, "unit": "TFLOP/s",
                     "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_pass"] if r else None,
                     "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",

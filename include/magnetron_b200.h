@@ -145,6 +145,11 @@ int  magb200_cast(int device, const magb200_view_t *src, const magb200_view_t *d
  * mag_contiguous / mag_reshape of a strided view dispatch (magnetron/core/mag_op_stubs.c:424-470). */
 int  magb200_clone(int device, const magb200_view_t *src, const magb200_view_t *dst);
 
+/* MAG_OP_CAT (mag_cat, magnetron/core/mag_op_stubs.c:996-1030; CPU kernels magnetron/cpu/mag_cpu_impl.inl:692-701):
+ * `count` contiguous inputs of one dtype and rank, equal on every axis but `dim`, copied one after the other along `dim`
+ * into the contiguous `dst` (stream-ordered device-to-device copies; the KV-cache append of the Qwen3 example). */
+int  magb200_cat(int device, const magb200_view_t *const *parts, int count, int dim, const magb200_view_t *dst);
+
 /* MAG_OP_FILL with a floating point value (magnetron/cpu/mag_cpu_impl_ops_fill.inl), contiguous dst. */
 int  magb200_fill(int device, const magb200_view_t *dst, double value);
 
@@ -168,6 +173,10 @@ void     magb200_launch_count_reset(void);
 /* Restrict routing (testing / profiling): 0 = automatic, otherwise a magb200_kernel_t that must be
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
+/* The two-SM kernel can share the tiles of a partial last wave out among all CTA pairs along K (fp32 partial tiles in the
+ * library's workspace, summed in a fixed order, so results are reproducible). mode 1 (default): only where it pays (few
+ * left-over tiles, K >= 4096); 0: never; 2: whenever the shape allows (tests). */
+int  magb200_set_balanced_last_wave(int mode);
 
 /* ---- tensor-parallel row-sharded linear, fused with its exchange ---------------------------------
  * No counterpart in the reference (it has no multi-device code). A row-sharded (K-sharded) linear needs the sum of

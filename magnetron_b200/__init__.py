@@ -74,6 +74,7 @@ SIGNATURES = {
     "magb200_cast": (C.c_int, [C.c_int, _VP, _VP]),
     "magb200_clone": (C.c_int, [C.c_int, _VP, _VP]),
     "magb200_fill": (C.c_int, [C.c_int, _VP, C.c_double]),
+    "magb200_cat": (C.c_int, [C.c_int, C.POINTER(_VP), C.c_int, C.c_int, _VP]),
     "magb200_matmul": (C.c_int, [C.c_int, _VP, _VP, _VP]),
     "magb200_matmul_result_shape": (C.c_int, [_VP, _VP, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "magb200_last_kernel": (C.c_int, []),
@@ -87,6 +88,7 @@ SIGNATURES = {
     "magb200_pool_stats": (C.c_int, [C.c_int] + [C.POINTER(C.c_uint64)] * 4),
     "magb200_pool_trim": (C.c_int, [C.c_int]),
     "magb200_mem_info": (C.c_int, [C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "magb200_set_balanced_last_wave": (C.c_int, [C.c_int]),
     "magb200_matmul_scatter": (C.c_int, [C.c_int, _VP, _VP, C.POINTER(C.c_void_p), C.c_int, C.c_int]),
     "magb200_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int]),
     "magb200_matmul_skinny_noalloc": (C.c_int, [C.c_int, C.c_void_p, _VP, _VP, _VP]),
@@ -308,6 +310,17 @@ class Tensor:
     def cast(self, dtype: int) -> "Tensor":                            # mag_cast -> MAG_OP_CAST
         out = Tensor(self.device, dtype, self.shape)
         check(lib().magb200_cast(self.device, C.byref(self.view_struct()), C.byref(out.view_struct())))
+        return out
+
+    @staticmethod
+    def cat(tensors: Sequence["Tensor"], dim: int) -> "Tensor":        # mag_cat -> MAG_OP_CAT
+        t0 = tensors[0]
+        shape = list(t0.shape)
+        shape[dim] = sum(t.shape[dim] for t in tensors)
+        out = Tensor(t0.device, t0.dtype, shape)
+        views = [t.view_struct() for t in tensors]
+        arr = (_VP * len(views))(*[C.pointer(v) for v in views])
+        check(lib().magb200_cat(t0.device, arr, len(views), dim, C.byref(out.view_struct())))
         return out
 
     def matmul(self, other: "Tensor") -> "Tensor":                     # mag_matmul -> MAG_OP_MATMUL

@@ -6,8 +6,8 @@
 Outputs land in `magnetron_b200/lib/`:
   libmagnetron_b200.so   the C ABI of include/magnetron_b200.h (kernels + host front-end)
   libmagnetron_cuda.so   the same objects plus the magnetron backend module (C host code compiled
-                         against the magnetron headers found under $MAGNETRON_SRC); skipped with a note when
-                         those headers are absent.
+                         against the magnetron headers found under $MAGNETRON_SRC, or in a directory named
+                         `reference` beside this repository); skipped with a note when those headers are absent.
 """
 from __future__ import annotations
 
@@ -24,6 +24,15 @@ OBJ = os.path.join(PKG, "build")
 CU_SOURCES = ["cabi.cu", "cast.cu", "gemv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "skinny_noalloc.cu", "tp_reduce.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+
+
+def magnetron_source_tree() -> str | None:
+    """Where the magnetron sources lie: $MAGNETRON_SRC, else a directory named `reference` beside this repository.
+    None when neither holds the backend header; nothing of that tree is ever copied, it is only compiled against."""
+    for cand in (os.environ.get("MAGNETRON_SRC"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "magnetron", "core", "mag_backend.h")):
+            return cand
+    return None
 
 
 def _nvcc() -> str:
@@ -70,7 +79,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> dict:
     out["cabi"] = lib
 
     # backend module: C host code against the magnetron headers (never copied into this tree)
-    ref = os.environ.get("MAGNETRON_SRC", "/root/reference")
+    ref = magnetron_source_tree() or ""
     backend_src = os.path.join(CSRC, "backend", "mag_b200_backend.c")
     plugin = os.path.join(LIB, "libmagnetron_cuda.so")
     core_dir = os.path.join(ROOT, "oracle", "_ref")

@@ -23,7 +23,8 @@
  *
  * The module ABI has no transfer entry (mag_backend.h:90-99) and the core's host-access calls refuse
  * non-CPU storage (mag_copy_raw_, magnetron/core/mag_op_stubs.c:1365-1374), so this module additionally
- * exports mag_b200_upload / mag_b200_download / mag_b200_synchronize for callers that hold device tensors.
+ * exports mag_b200_upload / mag_b200_download (and their _async forms on the copy streams) / mag_b200_synchronize for
+ * callers that hold device tensors.
  */
 #include <core/mag_backend.h>
 #include <core/mag_context.h>
@@ -37,6 +38,7 @@
 
 #define MAG_B200_BACKEND_VERSION mag_ver_encode(0, 1, 0)
 #define MAG_B200_MAX_DEVICES 16
+#define MAG_B200_MAX_CAT 64
 
 typedef struct mag_b200_device_t {
     mag_device_t iface;     /* handed to the core; must outlive the context's tensors */
@@ -49,17 +51,30 @@ typedef struct mag_b200_backend_t {
     mag_b200_device_t devices[MAG_B200_MAX_DEVICES];
 } mag_b200_backend_t;
 
-/* ---- status mapping -------------------------------------------------------------------------- */
-static mag_status_t mag_b200_map_status(int rc, const char *what) {
-    if (rc == MAGB200_OK) return MAG_STATUS_OK;
-    mag_log_error("b200 backend: %s failed (%d): %s", what, rc, magb200_last_error());
+/* ---- status mapping --------------------------------------------------------------------------
+ * Every C-ABI code has one magnetron status of its own, so a caller can tell the causes apart:
+ *   out of device memory -> ERR_MEMORY_ALLOCATION_FAILED     shapes that form no matmul / cast -> ERR_OPERATOR_IMPOSSIBLE
+ *   bad argument         -> ERR_INVALID_PARAM                beyond a fixed capacity            -> ERR_DIM_OVERFLOW
+ *   a bounded device-side wait ran out (results of that launch are invalid, the device stays usable) -> ERR_INVALID_STATE
+ *   no such device       -> ERR_INVALID_INDEX                any other CUDA runtime failure     -> ERR_UNKNOWN
+ * Exported so that the mapping can be checked without a device. */
+MAG_EXPORT mag_status_t mag_b200_status_of(int rc) {
     switch (rc) {
+        case MAGB200_OK:              return MAG_STATUS_OK;
         case MAGB200_ERR_OOM:         return MAG_STATUS_ERR_MEMORY_ALLOCATION_FAILED;
         case MAGB200_ERR_SHAPE:       return MAG_STATUS_ERR_OPERATOR_IMPOSSIBLE;
         case MAGB200_ERR_INVALID_ARG: return MAG_STATUS_ERR_INVALID_PARAM;
         case MAGB200_ERR_TOO_LARGE:   return MAG_STATUS_ERR_DIM_OVERFLOW;
-        default:                      return MAG_STATUS_ERR_INVALID_STATE;
+        case MAGB200_ERR_TIMEOUT:     return MAG_STATUS_ERR_INVALID_STATE;
+        case MAGB200_ERR_NO_DEVICE:   return MAG_STATUS_ERR_INVALID_INDEX;
+        default:                      return MAG_STATUS_ERR_UNKNOWN;
     }
+}
+
+static mag_status_t mag_b200_map_status(int rc, const char *what) {
+    if (rc == MAGB200_OK) return MAG_STATUS_OK;
+    mag_log_error("b200 backend: %s failed (%d): %s", what, rc, magb200_last_error());
+    return mag_b200_status_of(rc);
 }
 
 /* ---- tensor header -> view ------------------------------------------------------------------- */
@@ -81,7 +96,7 @@ static void mag_b200_view_of(const mag_tensor_t *t, magb200_view_t *v) {
 
 /* ---- submit ---------------------------------------------------------------------------------- */
 static mag_status_t mag_b200_unsupported(const mag_command_t *cmd, const char *why) {
-    mag_log_error("b200 backend: opcode %d %s; this module implements MATMUL, CAST, CLONE, FILL and the view opcodes", (int)cmd->op, why);
+    mag_log_error("b200 backend: opcode %d %s; this module implements MATMUL, CAST, CLONE, CAT, FILL and the view opcodes", (int)cmd->op, why);
     return MAG_STATUS_ERR_OPERATOR_IMPOSSIBLE;
 }
 
@@ -110,6 +125,18 @@ static mag_status_t mag_b200_submit(mag_device_t *dvc, const mag_command_t *cmd)
             mag_b200_view_of(cmd->out[0], &r);
             return mag_b200_map_status(cmd->op == MAG_OP_CAST ? magb200_cast(dev, &x, &r) : magb200_clone(dev, &x, &r),
                                        cmd->op == MAG_OP_CAST ? "cast" : "clone");
+        case MAG_OP_CAT: {
+            /* mag_cat (magnetron/core/mag_op_stubs.c:996-1030): contiguous inputs of one dtype, attrs[0] = the dim; the
+             * KV-cache append of the Qwen3 example (examples/qwen3/model.py:126-127) arrives here */
+            if (cmd->num_in < 1 || cmd->num_in > MAG_B200_MAX_CAT || cmd->num_out != 1) return mag_b200_unsupported(cmd, "has too many inputs for the device concat");
+            if (!mag_b200_dtype_ok(cmd->out[0]->dtype)) return mag_b200_unsupported(cmd, "has a dtype outside {float32, float16, bfloat16}");
+            if (cmd->attrs[0].tag != MAG_OP_ATTR_TYPE_I64) return MAG_STATUS_ERR_INVALID_PARAM;
+            magb200_view_t parts[MAG_B200_MAX_CAT];
+            const magb200_view_t *ptrs[MAG_B200_MAX_CAT];
+            for (uint32_t i = 0; i < cmd->num_in; ++i) { mag_b200_view_of(cmd->in[i], &parts[i]); ptrs[i] = &parts[i]; }
+            mag_b200_view_of(cmd->out[0], &r);
+            return mag_b200_map_status(magb200_cat(dev, ptrs, (int)cmd->num_in, (int)mag_op_attr_unwrap_int64(cmd->attrs[0]), &r), "cat");
+        }
         case MAG_OP_FILL:
             if (cmd->num_out != 1) return MAG_STATUS_ERR_INVALID_PARAM;
             if (!mag_b200_dtype_ok(cmd->out[0]->dtype)) return mag_b200_unsupported(cmd, "has a non floating point dtype");
@@ -264,6 +291,32 @@ MAG_EXPORT mag_status_t mag_b200_download(const mag_tensor_t *tensor, void *host
     const int dev = ((mag_b200_device_t *)tensor->storage->device->impl)->ordinal;
     const char *src = (const char *)tensor->storage->base + tensor->storage_offset * (int64_t)mag_type_trait(tensor->dtype)->size;
     return mag_b200_map_status(magb200_download(dev, host_data, src, size_bytes), "download");
+}
+
+/* The same transfers without waiting: they run on the module's copy streams beside the kernels of other operators and
+ * beside each other (the link is full duplex). The upload is ordered after the operators submitted so far and before the
+ * ones submitted later; the download is ordered after the operators submitted so far. `host_data` must be page-locked
+ * (mag_b200_host_alloc) and stay untouched until mag_b200_synchronize returns; the tensor may be released right after the
+ * call -- its storage is not handed to a later writer before the copy has read it. */
+MAG_EXPORT mag_status_t mag_b200_upload_async(mag_tensor_t *tensor, const void *host_data, size_t size_bytes) {
+    if (!host_data || !mag_b200_check_transfer(tensor, size_bytes, "mag_b200_upload_async")) return MAG_STATUS_ERR_INVALID_PARAM;
+    const int dev = ((mag_b200_device_t *)tensor->storage->device->impl)->ordinal;
+    char *dst = (char *)tensor->storage->base + tensor->storage_offset * (int64_t)mag_type_trait(tensor->dtype)->size;
+    return mag_b200_map_status(magb200_upload_overlapped(dev, dst, host_data, size_bytes), "upload");
+}
+
+MAG_EXPORT mag_status_t mag_b200_download_async(const mag_tensor_t *tensor, void *host_data, size_t size_bytes) {
+    if (!host_data || !mag_b200_check_transfer(tensor, size_bytes, "mag_b200_download_async")) return MAG_STATUS_ERR_INVALID_PARAM;
+    const int dev = ((mag_b200_device_t *)tensor->storage->device->impl)->ordinal;
+    const char *src = (const char *)tensor->storage->base + tensor->storage_offset * (int64_t)mag_type_trait(tensor->dtype)->size;
+    return mag_b200_map_status(magb200_download_overlapped(dev, host_data, src, size_bytes), "download");
+}
+
+MAG_EXPORT mag_status_t mag_b200_host_alloc(void **out, size_t size_bytes) {
+    return mag_b200_map_status(magb200_host_alloc_pinned(out, size_bytes), "page-locked host allocation");
+}
+MAG_EXPORT mag_status_t mag_b200_host_free(void *ptr) {
+    return mag_b200_map_status(magb200_host_free_pinned(ptr), "page-locked host release");
 }
 
 MAG_EXPORT mag_status_t mag_b200_synchronize(mag_context_t *ctx) {

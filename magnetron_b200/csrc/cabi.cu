@@ -52,11 +52,15 @@ static cudaError_t take_injected(int site) { return (cudaError_t)g_inject[site].
 // intermediate of a layer costs a device synchronisation. Freed blocks are therefore kept in size classes (eight per power
 // of two, at most 12.5 % slack) and handed out again without any CUDA call. Reuse needs no synchronisation because every
 // operator and copy of this library runs on the device's one launch stream: whatever still reads a freed block was
-// submitted before whatever will write it next. Blocks go back to the driver at shutdown or when cudaMalloc runs dry.
+// submitted before whatever will write it next. The one exception are downloads on the copy stream: a block freed while
+// such a download may still read it is parked with an event recorded on that stream and rejoins the free lists once the
+// event has completed. Blocks go back to the driver at shutdown or when cudaMalloc runs dry.
 struct MemPool {
     std::mutex mu;
     std::unordered_map<size_t, std::vector<void *>> free_blocks;   // class size -> blocks
     std::unordered_map<void *, size_t> live;                       // block -> class size
+    struct Deferred { void *ptr; size_t cls; cudaEvent_t ev; };
+    std::vector<Deferred> deferred;                                // freed while a copy-stream download may still read them
     size_t cached_bytes = 0, live_bytes = 0;
     uint64_t hits = 0, misses = 0;
 };
@@ -69,6 +73,8 @@ static size_t size_class(size_t bytes) {
 
 // ---- per-device state ---------------------------------------------------------------------------
 constexpr int kMaxDevices = 16;
+constexpr size_t kStatusBytes = 4096;
+constexpr int kCounterWord0 = 64, kCounterTiles = 256;   // counters of the two-SM kernel's shared last wave live in the status buffer
 struct AddrRange { uintptr_t lo, hi; };
 struct DeviceState {
     std::atomic<bool> ready{false};
@@ -133,9 +139,9 @@ static int ensure_device(int device, DeviceState **out) {
             MAGB200_CUDA_TRY(cudaSetDevice(device));
             MAGB200_CUDA_TRY(cudaStreamCreateWithFlags(&d.own_stream, cudaStreamNonBlocking));
             d.stream = d.own_stream;
-            MAGB200_CUDA_TRY(cudaMalloc(&d.status, 256));
-            MAGB200_CUDA_TRY(cudaMemset(d.status, 0, 256));
-            d.scratch_bytes = 32ull << 20;
+            MAGB200_CUDA_TRY(cudaMalloc(&d.status, kStatusBytes));     // word 0: time-out status; from word 64: tile counters
+            MAGB200_CUDA_TRY(cudaMemset(d.status, 0, kStatusBytes));
+            d.scratch_bytes = 64ull << 20;   // split-K partial sums; the two-SM kernel's shared last wave needs up to ~40 MB
             MAGB200_CUDA_TRY(cudaMalloc(&d.scratch, d.scratch_bytes));
             if (!d.pool) d.pool = new MemPool();
             d.ready.store(true, std::memory_order_release);
@@ -190,7 +196,7 @@ static int check_status_word(DeviceState &d) {
     MAGB200_CUDA_TRY(cudaMemcpyAsync(&h, d.status, sizeof(int), cudaMemcpyDeviceToHost, d.stream));
     MAGB200_CUDA_TRY(cudaStreamSynchronize(d.stream));
     if (h != 0) {
-        MAGB200_CUDA_TRY(cudaMemsetAsync(d.status, 0, sizeof(int), d.stream));
+        MAGB200_CUDA_TRY(cudaMemsetAsync(d.status, 0, kStatusBytes, d.stream));   // an abandoned launch may have left tile counters raised
         set_error("a device-side wait ran out (status %d): the launch was abandoned, results are invalid", h);
         return MAGB200_ERR_TIMEOUT;
     }
@@ -395,6 +401,13 @@ static int route(const GemmProblem &g, int forced, int *kernel) {
     return MAGB200_OK;
 }
 
+static SplitWorkspace split_workspace(DeviceState &d) {
+    SplitWorkspace ws;
+    ws.partial = d.scratch; ws.partial_bytes = d.scratch_bytes;
+    ws.counters = d.status + kCounterWord0; ws.max_tiles = kCounterTiles;
+    return ws;
+}
+
 static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel) {
     switch (kernel) {
         case MAGB200_KERNEL_SKINNY: {
@@ -410,10 +423,12 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
             g_last_kernel = MAGB200_KERNEL_TCGEN05;
             ordered_point(d);
             return launch_gemm_tcgen05(g, d.stream, d.cta_limit, d.status);
-        case MAGB200_KERNEL_TCGEN05_2SM:
+        case MAGB200_KERNEL_TCGEN05_2SM: {
             g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
             ordered_point(d);
-            return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status);
+            const SplitWorkspace ws = split_workspace(d);
+            return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status, nullptr, &ws);
+        }
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
             if (int rc = ensure_scratch(d, simt_scratch_bytes(g))) return rc;
@@ -518,6 +533,8 @@ int magb200_device_shutdown(int device) {
     cudaStreamDestroy(d.own_stream);
     if (d.pool) {   // cached blocks go back to the driver; blocks still held by the caller stay valid and are forgotten
         std::lock_guard<std::mutex> pl(d.pool->mu);
+        for (auto &df : d.pool->deferred) { cudaEventDestroy(df.ev); cudaFree(df.ptr); }
+        d.pool->deferred.clear();
         for (auto &cls : d.pool->free_blocks) for (void *b : cls.second) cudaFree(b);
         d.pool->free_blocks.clear(); d.pool->live.clear();
         d.pool->cached_bytes = d.pool->live_bytes = 0;
@@ -566,8 +583,10 @@ static int order_after(cudaStream_t later, cudaStream_t earlier);
 // Release every cached block of the pool to the driver (after the device has gone idle). Returns the bytes released.
 static size_t pool_trim(DeviceState &d) {
     MemPool &p = *d.pool;
-    if (p.cached_bytes == 0) return 0;
+    if (p.cached_bytes == 0 && p.deferred.empty()) return 0;
     cudaDeviceSynchronize();
+    for (auto &df : p.deferred) { cudaEventDestroy(df.ev); p.free_blocks[df.cls].push_back(df.ptr); p.cached_bytes += df.cls; }
+    p.deferred.clear();
     size_t released = p.cached_bytes;
     for (auto &cls : p.free_blocks) for (void *b : cls.second) cudaFree(b);
     p.free_blocks.clear();
@@ -585,6 +604,18 @@ int magb200_malloc(int device, void **out, size_t bytes) {
     MemPool &p = *d->pool;
     const size_t cls = size_class(bytes ? bytes : 1);
     std::lock_guard<std::mutex> lock(p.mu);
+    for (size_t i = 0; i < p.deferred.size();) {       // parked blocks whose download has finished are free again
+        if (cudaEventQuery(p.deferred[i].ev) == cudaSuccess) {
+            cudaEventDestroy(p.deferred[i].ev);
+            p.free_blocks[p.deferred[i].cls].push_back(p.deferred[i].ptr);
+            p.cached_bytes += p.deferred[i].cls;
+            p.deferred[i] = p.deferred.back();
+            p.deferred.pop_back();
+        } else {
+            (void)cudaGetLastError();                  // cudaErrorNotReady is not an error
+            ++i;
+        }
+    }
     auto it = p.free_blocks.find(cls);
     if (it != p.free_blocks.end() && !it->second.empty()) {
         *out = it->second.back();
@@ -608,8 +639,6 @@ int magb200_free(int device, void *ptr) {
     int rc = ensure_device(device, &d);
     if (rc) return rc;
     if (!ptr) return MAGB200_OK;
-    // a download on the copy stream may still read the block: whoever gets it next writes on the launch stream, after this
-    if (d->d2h_pending && d->d2h_stream && !d->capturing) { if ((rc = order_after(d->stream, d->d2h_stream))) return rc; }
     MemPool &p = *d->pool;
     std::lock_guard<std::mutex> lock(p.mu);
     auto it = p.live.find(ptr);
@@ -621,6 +650,15 @@ int magb200_free(int device, void *ptr) {
     const size_t cls = it->second;
     p.live.erase(it);
     p.live_bytes -= cls;
+    if (d->d2h_pending && d->d2h_stream && !d->capturing) {
+        // a download on the copy stream may still read the block: park it until everything queued there so far is done
+        MemPool::Deferred df;
+        df.ptr = ptr; df.cls = cls;
+        MAGB200_CUDA_TRY(cudaEventCreateWithFlags(&df.ev, cudaEventDisableTiming));
+        MAGB200_CUDA_TRY(cudaEventRecord(df.ev, d->d2h_stream));
+        p.deferred.push_back(df);
+        return MAGB200_OK;
+    }
     p.free_blocks[cls].push_back(ptr);
     p.cached_bytes += cls;
     return MAGB200_OK;
@@ -734,6 +772,39 @@ int magb200_clone(int device, const magb200_view_t *src, const magb200_view_t *d
     if (rc) return rc;
     return cast_device(*d, src, dst, true);
 }
+int magb200_cat(int device, const magb200_view_t *const *parts, int count, int dim, const magb200_view_t *dst) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!parts || count < 1) { set_error("cat: no inputs"); return MAGB200_ERR_INVALID_ARG; }
+    if ((rc = check_view(dst, "cat result"))) return rc;
+    if (!view_is_contiguous(dst)) { set_error("cat: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
+    if (dim < 0 || dim >= dst->rank) { set_error("cat: dimension %d is outside [0, %d)", dim, dst->rank); return MAGB200_ERR_INVALID_ARG; }
+    // contiguous inputs: input i is `outer` runs of inner_i elements, which land in the result at a pitch of sum inner_i
+    int64_t outer = 1, tail = 1, along = 0;
+    for (int i = 0; i < dim; ++i) outer *= dst->shape[i];
+    for (int i = dim + 1; i < dst->rank; ++i) tail *= dst->shape[i];
+    for (int p = 0; p < count; ++p) {
+        const magb200_view_t *v = parts[p];
+        if ((rc = check_view(v, "cat input"))) return rc;
+        if (v->dtype != dst->dtype || v->rank != dst->rank) { set_error("cat: input %d differs from the result in dtype or rank", p); return MAGB200_ERR_INVALID_ARG; }
+        if (!view_is_contiguous(v)) { set_error("cat: inputs must be contiguous row-major"); return MAGB200_ERR_INVALID_ARG; }
+        for (int i = 0; i < dst->rank; ++i)
+            if (i != dim && v->shape[i] != dst->shape[i]) { set_error("cat: shapes must match on non-concat dimensions (axis %d)", i); return MAGB200_ERR_SHAPE; }
+        along += v->shape[dim];
+    }
+    if (along != dst->shape[dim]) { set_error("cat: inputs add up to %lld along dim %d, the result has %lld", (long long)along, dim, (long long)dst->shape[dim]); return MAGB200_ERR_SHAPE; }
+    const size_t es = dtype_size(dst->dtype);
+    const size_t pitch = (size_t)(dst->shape[dim] * tail) * es;
+    char *out = view_data(dst);
+    ordered_point(*d);
+    for (int p = 0; p < count; ++p) {
+        const size_t width = (size_t)(parts[p]->shape[dim] * tail) * es;
+        MAGB200_CUDA_TRY(cudaMemcpy2DAsync(out, pitch, view_data(parts[p]), width, width, (size_t)outer, cudaMemcpyDeviceToDevice, d->stream));
+        out += width;
+    }
+    return MAGB200_OK;
+}
 int magb200_fill(int device, const magb200_view_t *dst, double value) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
@@ -787,7 +858,8 @@ int magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_vi
         if (!sc.stage[i] || ((uintptr_t)sc.stage[i] & 15u)) { set_error("matmul_scatter: staging pointer of rank %d is null or misaligned", i); return MAGB200_ERR_INVALID_ARG; }
     if (tcgen05_2sm_preferred(g)) {
         g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
-        return launch_gemm_tcgen05_2sm(g, d->stream, d->cta_limit, d->status, &sc);
+        const SplitWorkspace ws = split_workspace(*d);
+        return launch_gemm_tcgen05_2sm(g, d->stream, d->cta_limit, d->status, &sc, &ws);
     }
     g_last_kernel = MAGB200_KERNEL_TCGEN05;
     return launch_gemm_tcgen05(g, d->stream, d->cta_limit, d->status, &sc);
@@ -814,6 +886,11 @@ uint64_t magb200_get_wait_limit_ns(void) { return get_wait_limit_ns(); }
 int magb200_test_leave_stage_unarmed(int k_block) {
     if (k_block < -1) { set_error("test_leave_stage_unarmed: k_block must be >= 0 (or -1 to disarm)"); return MAGB200_ERR_INVALID_ARG; }
     set_skip_kb_once(k_block);
+    return MAGB200_OK;
+}
+int magb200_set_balanced_last_wave(int mode) {
+    if (mode < 0 || mode > 2) { set_error("set_balanced_last_wave: mode %d is outside 0..2", mode); return MAGB200_ERR_INVALID_ARG; }
+    set_balance_tail(mode);
     return MAGB200_OK;
 }
 int magb200_test_inject_fault(int site, int cuda_error) {

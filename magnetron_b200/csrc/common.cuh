@@ -144,7 +144,16 @@ struct ScatterTarget {
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr);
 bool tcgen05_2sm_supported(const GemmProblem &p);
 bool tcgen05_2sm_preferred(const GemmProblem &p);
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr);
+// Workspace for the shared-out last wave of the two-SM kernel: fp32 partial tiles and per-tile counters (zero between launches).
+struct SplitWorkspace {
+    float *partial;
+    size_t partial_bytes;
+    int *counters;        // 2 ints per tile
+    int max_tiles;
+};
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr,
+                            const SplitWorkspace *ws = nullptr);
+void set_balance_tail(int enabled);
 int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems, cudaStream_t stream);
 
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,

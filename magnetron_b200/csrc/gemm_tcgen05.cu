@@ -46,6 +46,13 @@ struct TcArgs {
     int64_t tiles_m, tiles_n, total_tiles;
     int num_kb;
     int *status;
+    // two-SM kernel, balanced last wave: the tiles left over by the full waves are shared out by K (see WorkUnit)
+    int64_t full_tiles;                 // tiles handled whole, `num_pairs` per wave
+    int tail_tiles, tail_pairs;         // tiles of the partial last wave and the CTA pairs that share them (0: none)
+    int num_kg;                         // K groups (stages) per tile
+    int tail_slots;                     // partial-sum slots per tail tile in `sk_partial`
+    float *sk_partial;                  // fp32 partial tiles of the contributors: [tail tile][slot][256 x 256]
+    int *sk_counters;                   // [tail tile][2]: contributions arrived / owner warps done
     uint64_t wait_limit_ns;             // every mbarrier wait gives up after this long without progress
     int skip_kb;                        // test hook: K block of each CTA's first tile whose loads are never issued (-1: none)
     // scatter epilogue (tensor-parallel row-sharded GEMM): rows of block o go to rank o's staging buffer, slot `rank`
@@ -450,14 +457,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 constexpr int kThreads2 = 320;  // warp 0 TMA, warp 1 MMA (leader only), warps 2-9 epilogue (two per TMEM lane quarter)
 constexpr int BN2 = 256;
 
-struct Cfg2 {
-    static constexpr int kSub = 2;                               // 64-wide K sub-blocks per stage
+template <int KSUB> struct Cfg2 {
+    static constexpr int kSub = KSUB;                            // 64-wide K sub-blocks per stage (2: the long-K default)
     static constexpr int kSubABytes = BM * BK * 2;               // this CTA's 128 rows of A, one sub-block
     static constexpr int kSubBBytes = (BN2 / 2) * BK * 2;        // this CTA's 128 columns of B, one sub-block
     static constexpr int kABytes = kSub * kSubABytes;
     static constexpr int kBBytes = kSub * kSubBBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;        // 64 KB
-    static constexpr int kStages = 3;
+    static constexpr int kStages = 6 / KSUB;
     static constexpr int kTmemCols = 2 * BN2;
     static constexpr int kEpiWarps = 8;                           // two warps per TMEM lane quarter, 128 columns each
     static constexpr int kEpiCols = 64;                           // output columns per staging pass: 128-byte row segments
@@ -497,12 +504,46 @@ __device__ __forceinline__ void tma_load_5d_2sm(uint32_t dst, const CUtensorMap 
 __device__ __forceinline__ void tcgen05_commit_2sm(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tcgen05_mma_f16_2sm(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+
+// ---- balanced last wave ---------------------------------------------------------------------------------------------------
+// A persistent grid of P CTA pairs finishes T tiles in ceil(T / P) tile times; the pairs without a tile in the last wave idle
+// (256 tiles on 74 pairs: 3.46 waves of work take 4). Narrower tiles do not help: a tcgen05.mma occupies the issuing thread
+// and the pipe about as long at N = 64 as at N = 256. So the r = T mod P tiles of the last wave are shared out along K
+// instead: their r * num_kg K groups are dealt to Q pairs in equal contiguous runs. A run that starts at K group 0 of a tile
+// makes its pair the tile's owner; any other run is a contribution: its pair writes the fp32 accumulator to a scratch slot
+// and raises the tile's counter, the owner adds the contributions in run order (fixed, so results do not depend on timing),
+// rounds once and stores. A pair's run may cross from the end of one tile into the start of the next: then it contributes
+// first and owns second, so an owner only ever waits for pairs that are not waiting for anybody.
+struct WorkUnit {
+    int64_t tile;
+    int kg0, kg1;        // K groups [kg0, kg1) of the tile
+    int part, parts;     // run index within the tile (0: owner) and number of runs
+    int tail_idx;        // index among the tail tiles (-1: a whole tile)
+};
+__device__ __forceinline__ int tail_pair_of(const TcArgs &a, int64_t kg_index) {   // pair whose run holds this K group
+    const int64_t R = (int64_t)a.tail_tiles * a.num_kg;
+    return (int)(((kg_index + 1) * a.tail_pairs + R - 1) / R - 1);
+}
+// The u-th unit of `pair` (u = 0, 1, ...); false when the pair has no further work.
+__device__ __forceinline__ bool work_unit(const TcArgs &a, int64_t pair, int64_t num_pairs, int u, WorkUnit &w) {
+    const int64_t whole = pair + (int64_t)u * num_pairs;
+    if (whole < a.full_tiles) { w.tile = whole; w.kg0 = 0; w.kg1 = a.num_kg; w.part = 0; w.parts = 1; w.tail_idx = -1; return true; }
+    const int v = u - (int)(a.full_tiles / num_pairs);   // full_tiles is a multiple of num_pairs: every pair had as many whole tiles
+    if (a.tail_pairs == 0 || pair >= a.tail_pairs || v > 1) return false;
+    const int64_t R = (int64_t)a.tail_tiles * a.num_kg;
+    const int64_t lo = pair * R / a.tail_pairs, hi = (pair + 1) * R / a.tail_pairs;
+    const int64_t ta = lo / a.num_kg;
+    const int64_t end_a = hi < (ta + 1) * a.num_kg ? hi : (ta + 1) * a.num_kg;
+    int64_t t, k0, k1;
+    if (v == 0) { t = ta; k0 = lo - ta * a.num_kg; k1 = end_a - ta * a.num_kg; }
+    else {
+        if (end_a >= hi) return false;
+        t = ta + 1; k0 = 0; k1 = hi - t * a.num_kg;
+    }
+    const int owner = tail_pair_of(a, t * a.num_kg), last = tail_pair_of(a, (t + 1) * a.num_kg - 1);
+    w.tile = a.full_tiles + t; w.kg0 = (int)k0; w.kg1 = (int)k1;
+    w.part = (int)pair - owner; w.parts = last - owner + 1; w.tail_idx = (int)t;
+    return true;
 }
 
 // tcgen05.mma with each shared-memory descriptor given as (low word, high word): from one K step, sub-block or stage to the
@@ -517,10 +558,13 @@ __device__ __forceinline__ void tcgen05_mma_f16_2sm_split(uint32_t tmem_d, uint3
         ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <int DT>
+// kShare: this launch shares its last wave out (see WorkUnit). A separate instantiation, because the sharing paths cost the
+// epilogue of every tile about 15 % on short-K shapes even when they are never taken (registers and scheduling of the
+// drain loop: measured on Q.K^T with K = 128, 0.66 ms against 0.56 ms).
+template <int DT, int KSUB, bool kShare>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
-    using C = Cfg2;
+    using C = Cfg2<KSUB>;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -567,9 +611,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             uint32_t phase = 0;
             bool ok = true;
             const uint32_t full_leader0 = map_to_cta(full0, 0);
-            for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs) {
+            WorkUnit w;
+            for (int u = 0; ok && work_unit(args, pair, num_pairs, u, w); ++u) {
                 int64_t batch, tm, tn;
-                decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
+                decode_tile(w.tile, args.tiles_m, args.tiles_n, batch, tm, tn);
                 const int m0 = (int)(tm * 2 * BM) + (int)rank * BM;        // this CTA's 128 rows of the 256-row tile
                 const int n0 = (int)(tn * BN2) + (int)rank * (BN2 / 2);    // this CTA's 128 columns of B
                 int bc[kMaxBatchDims] = {0, 0, 0};
@@ -583,10 +628,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 }
                 const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
                 const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
-                const int num_kg = (args.num_kb + C::kSub - 1) / C::kSub;   // stages per tile; a sub-block past K is zero-filled by TMA
-                for (int kg = 0; kg < num_kg; ++kg) {
+                for (int kg = w.kg0; kg < w.kg1; ++kg) {   // a sub-block past the end of K is zero-filled by TMA
                     if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
-                    if (kg == args.skip_kb && tile == pair) {   // test hook: neither CTA loads or arms this stage, the MMA thread's wait runs out
+                    if (kg == args.skip_kb && u == 0) {   // test hook: neither CTA loads or arms this stage, the MMA thread's wait runs out
                         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
@@ -632,28 +676,30 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const uint32_t a_k = a_step >> 4, b_k = b_step >> 4;                                      // one K step of 16
             constexpr uint32_t kStage16 = (uint32_t)C::kStageBytes >> 4;
             constexpr uint32_t kSubA16 = (uint32_t)C::kSubABytes >> 4, kSubB16 = (uint32_t)C::kSubBBytes >> 4;
-            const int num_kg = (args.num_kb + C::kSub - 1) / C::kSub;
             int stage = 0;
             uint32_t phase = 0, titer = 0;
             uint32_t a_lo = (uint32_t)adesc0, b_lo = (uint32_t)bdesc0;                                // of the current stage
             uint32_t full = full0, empty_own = empty0, empty_peer = empty_peer0;
             bool ok = true;
-            for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs, ++titer) {
+            WorkUnit w;
+            for (int u = 0; ok && work_unit(args, pair, num_pairs, u, w); ++u, ++titer) {
                 const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN2;
-                for (int kg = 0; kg < num_kg; ++kg) {
+                for (int kg = w.kg0; kg < w.kg1; ++kg) {
                     if (!mbar_wait(full, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                     tcgen05_fence_after();
-                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kg ? 1u : 0u);
+                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kg != w.kg0 ? 1u : 0u);
                     tcgen05_mma_f16_2sm_split(tmem_d, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
                     tcgen05_mma_f16_2sm_split(tmem_d, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u);
                     tcgen05_mma_f16_2sm_split(tmem_d, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u);
-                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16, a_hi, b_lo + kSubB16, b_hi, idesc, 1u);
-                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + a_k, a_hi, b_lo + kSubB16 + b_k, b_hi, idesc, 1u);
-                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 2 * a_k, a_hi, b_lo + kSubB16 + 2 * b_k, b_hi, idesc, 1u);
-                    tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 3 * a_k, a_hi, b_lo + kSubB16 + 3 * b_k, b_hi, idesc, 1u);
+                    if constexpr (KSUB == 2) {
+                        tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16, a_hi, b_lo + kSubB16, b_hi, idesc, 1u);
+                        tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + a_k, a_hi, b_lo + kSubB16 + b_k, b_hi, idesc, 1u);
+                        tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 2 * a_k, a_hi, b_lo + kSubB16 + 2 * b_k, b_hi, idesc, 1u);
+                        tcgen05_mma_f16_2sm_split(tmem_d, a_lo + kSubA16 + 3 * a_k, a_hi, b_lo + kSubB16 + 3 * b_k, b_hi, idesc, 1u);
+                    }
                     tcgen05_commit_2sm(empty_own);        // stage free: tell this CTA's producer ...
                     tcgen05_commit_2sm(empty_peer);       // ... and the peer's
                     if (++stage == C::kStages) {
@@ -673,16 +719,58 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         bool ok = true;
         const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
         const uint32_t tempty_leader0 = map_to_cta(tempty0, 0);
-        for (int64_t tile = pair; ok && tile < args.total_tiles; tile += num_pairs, ++titer) {
+        WorkUnit w;
+        for (int u = 0; ok && work_unit(args, pair, num_pairs, u, w); ++u, ++titer) {
             const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
             int64_t batch, tm, tn;
-            decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
+            decode_tile(w.tile, args.tiles_m, args.tiles_n, batch, tm, tn);
             const int64_t row = tm * 2 * BM + (int64_t)rank * BM + quarter * 32 + lane;
             const int64_t n0 = tn * BN2;
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag, args.wait_limit_ns));
             if (!ok) break;
             tcgen05_fence_after();
             const int chalf = (warp - 2) >> 2;            // which 128-column half of the tile this warp drains
+            // This warp's 32 x 128 block of a partial tile in scratch: [32-column chunk][accumulator register][lane], so that
+            // the 32 lanes of every store and load touch 128 contiguous bytes. Contributor and owner use the same mapping.
+            const size_t warp_block = ((size_t)rank * C::kEpiWarps + (size_t)(warp - 2)) * (32 * (BN2 / 2));
+            if (kShare && w.part > 0) {
+                // ---- contribution: the fp32 accumulator goes to this run's scratch slot, then the tile's counter is raised
+                float *slot = args.sk_partial + ((size_t)w.tail_idx * args.tail_slots + (size_t)(w.part - 1)) * (size_t)(2 * BM * BN2) + warp_block;
+                const uint32_t tb = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * (BN2 / 2);
+#pragma unroll 1
+                for (int c = 0; c < BN2 / 2; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tb + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) __stcg(slot + (size_t)c * 32 + i * 32 + lane, __uint_as_float(r[i]));
+                }
+                tcgen05_fence_before();
+                __threadfence();                           // the stores are visible device-wide before the counter moves
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
+                    atomicAdd(args.sk_counters + 2 * w.tail_idx, 1);
+                }
+                continue;
+            }
+            if (kShare && w.parts > 1) {
+                // ---- owner of a shared tile: wait (bounded) until every contributing warp has delivered
+                const int want = (w.parts - 1) * 2 * C::kEpiWarps;
+                const volatile int *cnt = args.sk_counters + 2 * w.tail_idx;
+                bool there = *cnt >= want;
+                if (!there) {
+                    const uint64_t t0 = global_timer_ns();
+                    for (uint32_t spin = 0; !(there = (*cnt >= want)); ++spin) {
+                        __nanosleep(64);
+                        if ((spin & 15u) == 15u && (*abort_flag || global_timer_ns() - t0 > args.wait_limit_ns)) { *abort_flag = 1; break; }
+                    }
+                }
+                ok = __all_sync(0xFFFFFFFFu, there);
+                if (!ok) break;
+                __threadfence();                           // acquire: the contributions are read after the counter
+            }
+            const float *contrib = args.sk_partial + (size_t)(w.tail_idx < 0 ? 0 : w.tail_idx) * args.tail_slots * (size_t)(2 * BM * BN2) + warp_block;
             if (vec_ok) {
                 // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
                 // kept at chunk c ^ (row & 7), conflict-free both ways), then 8 lanes write one row's 128 contiguous bytes, so
@@ -696,6 +784,14 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN2 / 2; c0 += C::kEpiCols) {
                     tmem_ld_wait();
+                    for (int j = 1; kShare && j < w.parts; ++j) {      // contributions in run order: the sum does not depend on timing
+                        const float *pj = contrib + (size_t)(j - 1) * (size_t)(2 * BM * BN2) + (size_t)c0 * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            ra[i] = __float_as_uint(__uint_as_float(ra[i]) + __ldcg(pj + i * 32));
+                            rb[i] = __float_as_uint(__uint_as_float(rb[i]) + __ldcg(pj + 1024 + i * 32));
+                        }
+                    }
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         uint4 o, q;
@@ -740,6 +836,11 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + c, r);
                 tmem_ld_wait();
+                for (int j = 1; kShare && j < w.parts; ++j) {
+                    const float *pj = contrib + (size_t)(j - 1) * (size_t)(2 * BM * BN2) + (size_t)(c - chalf * (BN2 / 2)) * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldcg(pj + i * 32));
+                }
                 if (row < args.M && n0 + c < args.N) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -749,6 +850,16 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_remote(tempty_leader0 + 8u * acc);   // leader's barrier counts all 16 epilogue warps of the pair
+            }
+            if (kShare && w.parts > 1) {
+                // every contribution has been read by this warp; the last of the pair's 16 epilogue warps to get here clears the
+                // tile's counters for the next launch (no contribution can still arrive: all were counted before the reads)
+                __threadfence();
+                __syncwarp();
+                if (lane == 0 && atomicAdd(args.sk_counters + 2 * w.tail_idx + 1, 1) == 2 * C::kEpiWarps - 1) {
+                    args.sk_counters[2 * w.tail_idx] = 0;
+                    args.sk_counters[2 * w.tail_idx + 1] = 0;
+                }
             }
         }
     }
@@ -935,6 +1046,7 @@ int pick_bn(const GemmProblem &p) {
 // ---- run-time knobs (set through the C ABI) ---------------------------------------------------------------------------
 std::atomic<uint64_t> g_wait_limit_ns{1000ull * 1000ull * 1000ull};
 std::atomic<int> g_skip_kb_once{-1};      // consumed by the next tensor-core launch
+std::atomic<int> g_balance_tail{1};       // sharing of a partial last wave along K: 0 off, 1 when it pays, 2 whenever possible
 
 // cudaFuncSetAttribute applies to the current device only, so the opt-in to more than 48 KB of dynamic shared memory is
 // remembered per (kernel, device): bit d of `done` is set once device d has it.
@@ -974,29 +1086,80 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
 }
 
 
-template <int DT>
-int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit) {
-    auto kernel = gemm_tcgen05_2sm_kernel<DT>;
+// Host mirror of tail_pair_of (device): pair whose run holds K group `kg_index` of the tail.
+int host_tail_pair_of(int64_t kg_index, int64_t R, int64_t Q) { return (int)(((kg_index + 1) * Q + R - 1) / R - 1); }
+
+// Decide how the tiles of a partial last wave are shared out (see WorkUnit). Fills full_tiles, tail_*, num_kg, sk_*.
+void plan_tail(TcArgs &args, int64_t pairs, const SplitWorkspace *ws, int ksub) {
+    const int64_t T = args.total_tiles;
+    args.num_kg = (args.num_kb + ksub - 1) / ksub;
+    const int64_t r = T % pairs;
+    args.full_tiles = T - r;
+    args.tail_tiles = (int)r;
+    args.tail_pairs = (int)r;            // default: one pair per left-over tile, the others idle
+    args.tail_slots = 0;
+    args.sk_partial = nullptr; args.sk_counters = nullptr;
+    if (r == 0) { args.tail_pairs = 0; return; }
+    const bool vec_ok = (args.N % 8 == 0) && (((uintptr_t)args.C & 15u) == 0);
+    if (!g_balance_tail.load() || !ws || !ws->partial || !ws->counters || !vec_ok || r > ws->max_tiles) return;
+    // Sharing costs a round trip of fp32 tiles through L2 and a serial sum in the owner (measured: about 8 us at 2-3 runs per
+    // tile), and under the board's power limit an idle pair is not a total loss (the busy ones clock higher). It pays when
+    // most pairs would idle and a tile is long: 2560 x 2048 x 8192 (6 of 80 tiles left over) +9 %, 4096^2 x 8192 +1 %,
+    // 4096^2 x 2048 -14 % with sharing forced. So: at most a quarter of the pairs busy without it, K >= 4096, at most four
+    // runs per tile (or whenever `force` asks for it, which the tests use to reach every path).
+    const bool force = g_balance_tail.load() == 2;
+    int cap = args.num_kg / 4;
+    if (cap > (force ? 8 : 4)) cap = force ? 8 : 4;
+    if (cap < 2) return;
+    if (!force && (r * 4 > pairs || args.num_kg < 32)) return;
+    int64_t Q = r * cap < pairs ? r * cap : pairs;
+    if (Q <= r) return;
+    const int64_t R = r * args.num_kg;
+    int max_parts = 1;
+    for (int64_t t = 0; t < r; ++t) {
+        const int parts = host_tail_pair_of((t + 1) * args.num_kg - 1, R, Q) - host_tail_pair_of(t * args.num_kg, R, Q) + 1;
+        if (parts > max_parts) max_parts = parts;
+    }
+    const size_t need = (size_t)r * (size_t)(max_parts - 1) * (size_t)(2 * BM * BN2) * sizeof(float);
+    if (max_parts < 2 || need > ws->partial_bytes) return;
+    args.tail_pairs = (int)Q;
+    args.tail_slots = max_parts - 1;
+    args.sk_partial = ws->partial;
+    args.sk_counters = ws->counters;
+}
+
+template <int DT, int KSUB, bool kShare>
+int launch_2sm_kernel(const CUtensorMap &ta, const CUtensorMap &tb, const TcArgs &args, const cudaLaunchConfig_t &cfg) {
+    auto kernel = gemm_tcgen05_2sm_kernel<DT, KSUB, kShare>;
     static std::atomic<uint32_t> optin{0};
-    if (int rc = ensure_smem_optin(kernel, Cfg2::kSmemBytes, optin)) return rc;
+    if (int rc = ensure_smem_optin(kernel, Cfg2<KSUB>::kSmemBytes, optin)) return rc;
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
+    return MAGB200_OK;
+}
+
+template <int DT, int KSUB>
+int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit,
+               const SplitWorkspace *ws) {
     fill_knobs(args);
     args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     args.tiles_n = (p.N + BN2 - 1) / BN2;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
     const int64_t max_pairs = (cta_limit > 1 ? cta_limit : num_sms()) / 2;
     const unsigned pairs = (unsigned)(args.total_tiles < max_pairs ? args.total_tiles : max_pairs);
+    plan_tail(args, pairs, ws, KSUB);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(kThreads2, 1, 1);
-    cfg.dynamicSmemBytes = Cfg2::kSmemBytes;
+    cfg.dynamicSmemBytes = Cfg2<KSUB>::kSmemBytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
+    const int rc = args.tail_slots > 0 ? launch_2sm_kernel<DT, KSUB, true>(ta, tb, args, cfg) : launch_2sm_kernel<DT, KSUB, false>(ta, tb, args, cfg);
+    if (rc) return rc;
     count_launch();
     return MAGB200_OK;
 }
@@ -1006,6 +1169,7 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
 void set_wait_limit_ns(uint64_t ns) { g_wait_limit_ns.store(ns); }
 uint64_t get_wait_limit_ns() { return g_wait_limit_ns.load(); }
 void set_skip_kb_once(int kb) { g_skip_kb_once.store(kb); }
+void set_balance_tail(int mode) { g_balance_tail.store(mode); }   // 0: off, 1: when it pays, 2: whenever possible
 
 bool tcgen05_supported(const GemmProblem &p) {
     if (p.dtype != MAGB200_BF16 && p.dtype != MAGB200_F16) return false;
@@ -1030,7 +1194,8 @@ bool tcgen05_2sm_preferred(const GemmProblem &p) {
     return tiles >= num_sms() / 2;
 }
 
-int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
+int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter,
+                            const SplitWorkspace *ws) {
     OperandDesc a, b;
     int amn = 0, bmn = 0;
     if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn)) {
@@ -1054,7 +1219,8 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
         args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
         for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
     }
-    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16>(p, ta, tb, args, st, cta_limit) : launch_2sm<MAGB200_F16>(p, ta, tb, args, st, cta_limit);
+    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16, 2>(p, ta, tb, args, st, cta_limit, ws)
+                                   : launch_2sm<MAGB200_F16, 2>(p, ta, tb, args, st, cta_limit, ws);
 }
 
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {

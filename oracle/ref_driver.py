@@ -12,7 +12,7 @@ holds `libmagnetron_core.so` plus backend modules (`libmagnetron_cpu.so`, option
     mag_matmul                                  include/magnetron/magnetron.h:372
     mag_tensor_* accessors                      include/magnetron/magnetron.h:398-446
 
-The default directory is `oracle/_ref/`, the output of `make -C oracle` (the reference's own sources
+The default directory is `oracle/_ref/`, the output of `make -C oracle REF=<magnetron source tree>` (the reference's own sources
 compiled where they lie). The same class drives a directory where the B200 plug-in was dropped next
 to the reference core, which is how the drop-in boundary is tested: same calls, device "cuda:0".
 """
@@ -107,7 +107,7 @@ class MagApi:
     def __init__(self, device: str = "cpu", lib_dir: str = REF_DIR, log_level: int | None = None):
         path = os.path.join(lib_dir, "libmagnetron_core.so")
         if not os.path.exists(path):
-            raise FileNotFoundError(f"{path} missing: run `make -C oracle` where the reference sources are present")
+            raise FileNotFoundError(f"{path} missing: run `make -C oracle REF=<magnetron source tree>` where the reference sources are present")
         self.lib = lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
         P, I64, VP = C.c_void_p, C.c_int64, C.c_void_p
         I64P = C.POINTER(C.c_int64)

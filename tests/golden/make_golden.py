@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden/ by running the UNMODIFIED reference CPU backend.
 
-    make -C oracle            # builds oracle/_ref from the reference sources (needs them on disk)
+    make -C oracle REF=<magnetron source tree>   # builds oracle/_ref from the reference sources (needs them on disk)
     python tests/golden/make_golden.py
 
 Outputs (committed):

@@ -133,7 +133,50 @@ def test_unsupported_opcode_returns_a_status(deploy_dir):
         api.close(True)
 
 
+def _cat(api, tensors, dim):
+    api.lib.mag_cat.restype = C.c_int
+    api.lib.mag_cat.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_size_t, C.c_int64]
+    arr = (C.c_void_p * len(tensors))(*[t.ptr for t in tensors])
+    return api._call(api.lib.mag_cat, arr, len(tensors), dim)
+
+
+def test_kv_append_through_the_reference_api(deploy_dir):
+    """mag_cat of a KV cache [B,H,T,D] with one new position, then scores against the grown cache: MAG_OP_CAT on the device
+    must give the bits that the reference CPU backend gives for the same call (both contexts live in this process, same core)."""
+    gpu_api = CudaApi(deploy_dir)
+    cpu_api = R.MagApi("cpu", lib_dir=deploy_dir, log_level=1)
+    ok = False
+    try:
+        dt = R.BFLOAT16
+        B, H, T, D = 2, 8, 37, 128
+        rng = np.random.default_rng(11)
+        cache = O.f32_to_bits(dt, cases.gen_storage(rng, (B, H, T, D), 1.0))
+        new = O.f32_to_bits(dt, cases.gen_storage(rng, (B, H, 1, D), 1.0))
+        q = O.f32_to_bits(dt, cases.gen_storage(rng, (B, H, 1, D), 1.0))
+        results = []
+        for api in (gpu_api, cpu_api):
+            tc, tn, tq = api.from_bits(dt, cache), api.from_bits(dt, new), api.from_bits(dt, q)
+            grown = _cat(api, [tc, tn], 2)
+            assert grown.shape == (B, H, T + 1, D)
+            kt = api.transpose(grown, 2, 3)
+            s = api.matmul(tq, kt)
+            results.append((api.to_bits(grown), api.to_bits(s)))
+            for t in (s, kt, grown, tq, tn, tc):
+                t.release()
+        assert np.array_equal(results[0][0], results[1][0])                     # the concat is a copy: bit exact
+        assert np.array_equal(results[0][0], np.concatenate([cache, new], axis=2))
+        qf, kf = O.bits_to_f64(dt, q), O.bits_to_f64(dt, results[0][0])
+        truth = np.einsum("bhqd,bhtd->bhqt", qf, kf)
+        m = O.error_metrics(dt, results[0][1], truth, np.einsum("bhqd,bhtd->bhqt", np.abs(qf), np.abs(kf)))
+        assert m["e"] <= unit_roundoff(dt) + D * 2.0 ** -24, m
+        ok = True
+    finally:
+        cpu_api.close(not ok)
+        finish(gpu_api, ok)
+
+
 CASES = {"matmul_cast": test_matmul_and_cast_through_the_reference_api,
+         "kv_append": test_kv_append_through_the_reference_api,
          "gqa_views": test_gqa_broadcast_views_through_the_reference_api,
          "unsupported_op": test_unsupported_opcode_returns_a_status}
 

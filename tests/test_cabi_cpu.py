@@ -82,3 +82,75 @@ def test_view_solver():
     assert f((4, 6), (1, 4), (24,)) is None                       # transposed: not viewable flat
     assert f((1, 2, 8, 16), (256, 128, 1, 8), (1, 2, 1, 8, 16)) == (0, 128, 0, 1, 8)   # K^T with a broadcast slot
     assert f((2, 3), (3, 1), (3, 2)) == (2, 1)
+
+
+def test_injected_faults_take_the_error_paths_without_a_device():
+    """A fault armed with magb200_test_inject_fault makes the next call at that site fail as if the CUDA runtime had
+    returned the error, before any device is touched: cudaErrorMemoryAllocation (2) must come back as MAGB200_ERR_OOM,
+    any other error as MAGB200_ERR_CUDA, and the fault is consumed by one call."""
+    L = mb.lib()
+    out = C.c_void_p(0x1234)
+    mb.check(L.magb200_test_inject_fault(1, 2))                    # site MALLOC, cudaErrorMemoryAllocation
+    assert L.magb200_malloc(0, C.byref(out), 1024) == mb.ERR_OOM
+    assert out.value is None and b"injected" in L.magb200_last_error()
+    mb.check(L.magb200_test_inject_fault(1, 999))                  # cudaErrorUnknown
+    assert L.magb200_malloc(0, C.byref(out), 1024) == mb.ERR_CUDA
+    v = mb.make_view(0x1000, mb.BFLOAT16, (4, 4))
+    mb.check(L.magb200_test_inject_fault(2, 719))                  # site LAUNCH, cudaErrorLaunchFailure
+    assert L.magb200_matmul(0, C.byref(v), C.byref(v), C.byref(v)) == mb.ERR_CUDA
+    if mb.device_count() == 0:                                     # consumed: the next call fails for the real reason
+        assert L.magb200_matmul(0, C.byref(v), C.byref(v), C.byref(v)) == mb.ERR_NO_DEVICE
+    assert L.magb200_test_inject_fault(7, 1) == mb.ERR_INVALID_ARG
+
+
+def test_knob_ranges():
+    L = mb.lib()
+    assert L.magb200_set_wait_limit_ns(10) == mb.ERR_INVALID_ARG          # below 1 ms
+    assert L.magb200_set_wait_limit_ns(10 ** 12) == mb.ERR_INVALID_ARG    # above 60 s
+    old = L.magb200_get_wait_limit_ns()
+    assert old == 10 ** 9
+    mb.check(L.magb200_set_wait_limit_ns(5 * 10 ** 6))
+    assert L.magb200_get_wait_limit_ns() == 5 * 10 ** 6
+    mb.check(L.magb200_set_wait_limit_ns(old))
+    assert L.magb200_set_balanced_last_wave(3) == mb.ERR_INVALID_ARG
+    mb.check(L.magb200_set_balanced_last_wave(1))
+    mb.check(L.magb200_test_leave_stage_unarmed(-1))
+
+
+STATUS_PROBE = r"""
+import ctypes as C, os, sys
+d = sys.argv[1]
+C.CDLL(os.path.join(d, "libmagnetron_core.so"), mode=C.RTLD_GLOBAL)
+h = C.CDLL(os.path.join(d, "libmagnetron_cuda.so"))
+h.mag_b200_status_of.restype, h.mag_b200_status_of.argtypes = C.c_int, [C.c_int]
+print(" ".join(str(h.mag_b200_status_of(int(a))) for a in sys.argv[2:]))
+"""
+
+
+def test_status_mapping_of_the_backend_module(tmp_path):
+    """Every C-ABI code maps to a magnetron status of its own (mag_b200_status_of, exported by the backend module). Run in
+    a process of its own: the module must sit next to a copy of the reference core, and a second copy of the core in
+    this process would disturb the tests that drive the checker."""
+    import shutil
+    import subprocess
+    import sys
+    plugin = os.path.join(os.path.dirname(mb.lib_path()), "libmagnetron_cuda.so")
+    core = os.path.join(ROOT, "oracle", "_ref", "libmagnetron_core.so")
+    if not (os.path.exists(plugin) and os.path.exists(core)):
+        pytest.skip("needs the backend module and the reference core it links against")
+    shutil.copy2(core, tmp_path / "libmagnetron_core.so")
+    shutil.copy2(plugin, tmp_path / "libmagnetron_cuda.so")
+    # mag_status_t values in declaration order (include/magnetron/magnetron.h:59-75)
+    names = ["OK", "PENDING", "THREAD_MISMATCH", "INVALID_RANK", "INVALID_DIM", "DIM_OVERFLOW", "INVALID_INDEX", "OUT_OF_BOUNDS",
+             "INVALID_PARAM", "STRIDE_SOLVER_FAILED", "BROADCAST_IMPOSSIBLE", "OPERATOR_IMPOSSIBLE", "INVALID_STATE", "IMAGE_ERROR",
+             "MEMORY_ALLOCATION_FAILED", "MEMORY_DEALLOCATION_FAILED", "UNKNOWN"]
+    code = {n: i for i, n in enumerate(names)}
+    want = {0: "OK", mb.ERR_OOM: "MEMORY_ALLOCATION_FAILED", mb.ERR_SHAPE: "OPERATOR_IMPOSSIBLE", mb.ERR_INVALID_ARG: "INVALID_PARAM",
+            mb.ERR_TOO_LARGE: "DIM_OVERFLOW", mb.ERR_TIMEOUT: "INVALID_STATE", mb.ERR_NO_DEVICE: "INVALID_INDEX", mb.ERR_CUDA: "UNKNOWN"}
+    rcs = list(want)
+    res = subprocess.run([sys.executable, "-c", STATUS_PROBE, str(tmp_path)] + [str(rc) for rc in rcs], capture_output=True, text=True,
+                         timeout=120)
+    assert res.returncode == 0, res.stderr[-2000:]
+    got = dict(zip(rcs, (int(v) for v in res.stdout.split())))
+    assert got == {rc: code[n] for rc, n in want.items()}
+    assert len(set(got.values())) == len(got)          # no two causes share a status

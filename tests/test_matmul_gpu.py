@@ -279,11 +279,12 @@ def test_fused_row_sharded_linear_emulated_ranks(gpu, ranks, M, N, K):
         t.release()
 
 
-def test_attention_scores_full_size(gpu):
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_attention_scores_full_size(gpu, dname):
     """Q[8x32x2048x128] @ K^T with K [8x8x2048x128] broadcast over 4 query heads per KV head (seed 4), at full size:
     549 GFLOP, a 2.1 GB result. fp64 truth on sampled (batch, head, row) triples; the 4 query heads of a group really
     read the same K (row of head g against K of its KV head)."""
-    dt = O.BFLOAT16
+    dt = cases.DTYPES[dname]
     B, KV, G, T, D = 8, 8, 4, 2048, 128
     rng = np.random.default_rng(4)
     q = bits(dt, rng, (B, KV, G, T, D), 1.0)
@@ -301,6 +302,86 @@ def test_attention_scores_full_size(gpu):
         assert m["e"] <= unit_roundoff(dt) + D * 2.0 ** -24, (b, h, g, t, m)
     for t_ in (s, tq, tk):
         t_.release()
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_attention_pv_full_size(gpu, dname):
+    """P[8x32x2048x2048] @ V with V [8x8x2048x128] broadcast over 4 query heads per KV head, at full size: P is 2.1 GB of
+    softmax rows (scaled N(0,1) logits, seed 4). The logits of one batch entry are drawn and soft-maxed on the host; batch
+    entry b holds the same rows rolled by 37 b keys, so every entry is different and still a softmax. fp64 truth on sampled
+    (batch, head, row) triples."""
+    dt = cases.DTYPES[dname]
+    B, KV, G, T, D = 8, 8, 4, 2048, 128
+    rng = np.random.default_rng(4)
+    v = bits(dt, rng, (B, KV, T, D), 1.0)
+    tv = mb.Tensor.from_bits(gpu, dt, v)
+    logits = rng.standard_normal((KV, G, T, T), dtype=np.float32) / np.float32(np.sqrt(D))
+    logits -= logits.max(-1, keepdims=True)
+    np.exp(logits, out=logits)
+    logits /= logits.sum(-1, keepdims=True)
+    p0 = O.f32_to_bits(dt, logits)
+    del logits
+    tp = mb.Tensor(gpu, dt, (B, KV, G, T, T))
+    per = KV * G * T * T
+    for b in range(B):
+        chunk = np.ascontiguousarray(np.roll(p0, 37 * b, axis=-1))
+        mb.check(mb.lib().magb200_upload(gpu, tp.ptr + b * per * 2, chunk.ctypes.data, chunk.nbytes))
+    o = tp @ tv.view((B, KV, 1, T, D))
+    assert o.shape == (B, KV, G, T, D) and mb.last_kernel().startswith("tcgen05")
+    got = o.to_bits()
+    for _ in range(32):
+        b, h, g, t = (int(rng.integers(0, n)) for n in (B, KV, G, T))
+        pf = O.bits_to_f64(dt, np.roll(p0[h, g, t], 37 * b))
+        vf = O.bits_to_f64(dt, v[b, h])
+        m = O.error_metrics(dt, got[b, h, g, t], pf @ vf, np.abs(pf) @ np.abs(vf))
+        assert m["e"] <= unit_roundoff(dt) + T * 2.0 ** -24, (b, h, g, t, m)
+    for t_ in (o, tp, tv):
+        t_.release()
+
+
+# per-rank problems of the Qwen3-32B layer sharded 8 ways: (M, N_local, K_local, K_full); K_full > K_local means the operands
+# are the rank's K slice of a wider activation and weight (row sharding: strided views)
+TP_RANK_SHAPES = [(8192, 1280, 5120, 5120), (8192, 5120, 1024, 2048), (8192, 6400, 5120, 5120), (8192, 5120, 3200, 6400),
+                  (512, 1280, 5120, 5120), (512, 5120, 1024, 2048), (512, 6400, 5120, 5120), (512, 5120, 3200, 6400)]
+
+
+@pytest.mark.parametrize("M,N,K,KF", TP_RANK_SHAPES)
+def test_tensor_parallel_per_rank_shapes(gpu, M, N, K, KF):
+    """What one of eight ranks multiplies for qkv / o / gate+up / down at 8192 and 512 tokens (seed 5): column shards are
+    plain x @ W_shard.T, row shards take the second K slice of x and of W as strided views. fp64 truth on sampled rows."""
+    dt = O.BFLOAT16
+    rng = np.random.default_rng(5)
+    xb, wb = bits(dt, rng, (M, KF), 1.0), bits(dt, rng, (N, KF), 0.02)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    k0 = KF - K
+    r = tx.slice(1, k0, K) @ tw.slice(1, k0, K).T
+    assert mb.last_kernel().startswith("tcgen05")
+    got = r.to_bits()
+    rows = np.unique(np.concatenate([[0, 255, 256, M - 1], rng.integers(0, M, 28)]))
+    sampled_check(dt, xb[:, k0:], wb[:, k0:], got, rows, K)
+    for t in (r, tx, tw):
+        t.release()
+
+
+@pytest.mark.parametrize("dname", list(cases.DTYPES))
+@pytest.mark.parametrize("shapes,dim", [([(2, 8, 5, 64), (2, 8, 1, 64)], 2),          # KV-cache append: one new position
+                                        ([(3, 7), (4, 7), (1, 7)], 0), ([(6, 5), (6, 1), (6, 9)], 1),
+                                        ([(2, 3, 4), (2, 3, 4)], 2), ([(1, 2, 2048, 128), (1, 2, 2048, 128)], 2)])
+def test_cat_matches_concatenate(gpu, dname, shapes, dim):
+    """MAG_OP_CAT on the device against numpy.concatenate on the same bit patterns (a pure copy: bit exact)."""
+    dt = cases.DTYPES[dname]
+    rng = np.random.default_rng(6)
+    hosts = [O.f32_to_bits(dt, cases.gen_storage(rng, sh, 1.0)) for sh in shapes]
+    tensors = [mb.Tensor.from_bits(gpu, dt, h) for h in hosts]
+    out = mb.Tensor.cat(tensors, dim)
+    assert np.array_equal(out.to_bits(), np.concatenate(hosts, axis=dim))
+    wrong = list(shapes[0])
+    wrong[(dim + 1) % len(wrong)] += 1                    # differs on an axis that is not the concat axis
+    bad = mb.Tensor.from_bits(gpu, dt, np.zeros(wrong, hosts[0].dtype))
+    with pytest.raises(mb.MagB200Error):
+        mb.Tensor.cat([tensors[0], bad], dim)
+    for t in tensors + [out, bad]:
+        t.release()
 
 
 def test_host_buffer_matmul(gpu):

@@ -93,3 +93,11 @@ def test_gqa_broadcast_views_through_the_reference_api(deploy_dir, gpu):
 def test_unsupported_opcode_returns_a_status(deploy_dir, gpu):
     """Opcodes outside the path come back as a status code, not as an abort."""
     run_in_fresh_process("unsupported_op", deploy_dir)
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_kv_append_through_the_reference_api(deploy_dir, gpu):
+    """mag_cat (KV-cache append) and the scores against the grown cache on "cuda:0", bit-compared with the reference CPU
+    backend running the same calls in the same process."""
+    run_in_fresh_process("kv_append", deploy_dir)

@@ -18,6 +18,58 @@ def bits(dt, rng, shape, scale):
     return O.f32_to_bits(dt, cases.gen_storage(rng, shape, scale))
 
 
+# (M, N, K, weight layout): 256 x 256 tiles on 74 CTA pairs
+BALANCED_SHAPES = [
+    (2560, 2048, 2048, "wT"),    # 80 tiles: one full wave, 6 tiles shared by 48 pairs (8 runs per tile)
+    (2560, 2560, 1024, "wT"),    # 100 tiles: 26 shared by 52 pairs (cap: 2 runs per tile)
+    (4096, 4096, 4096, "wT"),    # 256 tiles: 34 shared by 74 pairs, runs cross tile boundaries
+    (2048, 2048, 4096, "wT"),    # 64 tiles, less than a wave: all of them shared by 74 pairs
+    (2560, 2000, 1416, "wT"),    # ragged N and K
+    (2560, 2048, 1024, "kn"),    # contiguous [K,N] weight (N-major B)
+    (2560, 2048, 256, "wT"),     # too few K groups to share: falls back to whole tiles
+]
+
+
+@pytest.mark.parametrize("M,N,K,layout", BALANCED_SHAPES)
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_shared_last_wave(gpu, M, N, K, layout, dname):
+    """The two-SM kernel shares the tiles of a partial last wave among all CTA pairs along K (fp32 partials, fixed order).
+    The result must be reproducible bit for bit, meet the accuracy bar against fp64 on sampled rows, and differ from the
+    unshared schedule only in a few elements (the fp32 sum is associated differently, which can move the last bit)."""
+    dt = cases.DTYPES[dname]
+    L = mb.lib()
+    rng = np.random.default_rng(41)
+    xb = bits(dt, rng, (M, K), 1.0)
+    wb = bits(dt, rng, (N, K) if layout == "wT" else (K, N), 0.1)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    y = tw.T if layout == "wT" else tw
+    mb.force_kernel("tcgen05_2sm")
+    try:
+        mb.check(L.magb200_set_balanced_last_wave(2))      # share whenever the shape allows, not only where it pays
+        r1 = tx @ y
+        assert mb.last_kernel() == "tcgen05_2sm"
+        got = r1.to_bits()
+        r2 = tx @ y
+        again = r2.to_bits()
+        mb.check(L.magb200_set_balanced_last_wave(0))
+        r0 = tx @ y
+        plain = r0.to_bits()
+    finally:
+        mb.check(L.magb200_set_balanced_last_wave(1))
+        mb.force_kernel(None)
+    assert np.array_equal(got, again), "two runs of the shared last wave differ"
+    differ = got != plain
+    assert differ.mean() < 0.05, differ.mean()
+    rows = np.unique(np.concatenate([[0, 255, 256, M - 257, M - 1], rng.integers(0, M, 27)]))
+    wf = O.bits_to_f64(dt, wb)
+    wkn = wf.T if layout == "wT" else wf
+    xf = O.bits_to_f64(dt, xb[rows])
+    m = O.error_metrics(dt, got[rows], xf @ wkn, np.abs(xf) @ np.abs(wkn))
+    assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, m
+    for t in (r0, r1, r2, tx, tw):
+        t.release()
+
+
 def test_fresh_result_as_weight_operand_in_a_decode_chain(gpu):
     """k = x @ Wk.T followed at once by s = q @ k.T on the same stream, many times with changing x and no
     synchronisation in between. The decode kernels let their successors start early and fetch weights ahead of their
