@@ -444,8 +444,9 @@ def single_op_workload(dev: Dev, cpu: CpuRef, pk):
 
 
 def decode_workload(dev: Dev, cpu: CpuRef, steps: int, warmup: int, hbm_peak: float):
-    """One token pass of Qwen3-0.6B (28 layers x 7 projections + lm_head) per step; every launch reads a
-    different weight matrix and the 1.19 GB of weights exceed L2 many times over."""
+    """One token pass of Qwen3-0.6B (28 layers x 7 projections + lm_head) per step; every launch reads different weight
+    matrices and the 1.19 GB of weights exceed L2 many times over. Projections that share their activation (q,k,v and
+    gate,up) go out as one grouped call, so a layer is 4 launches."""
     mb = dev.mb
     rng = np.random.default_rng(2)
     layers = []
@@ -463,10 +464,25 @@ def decode_workload(dev: Dev, cpu: CpuRef, steps: int, warmup: int, hbm_peak: fl
                 calls.append((xs[K].view_struct(), w.T.view_struct(), outs[N].view_struct()))
         calls.append((xs[1024].view_struct(), lm_head.T.view_struct(), outs[VOCAB].view_struct()))
         act_bytes = sum((M * K + M * N) * 2 for _, N, K in DECODE_LAYER) * DECODE_LAYERS + (M * 1024 + M * VOCAB) * 2
+        # products that share their activation go out as one grouped call: (q,k,v), o, (gate,up), down -- 4 launches per layer
+        # (k and v get result buffers of their own here: a group's results must not alias)
+        outs_v, outs_up = mb.Tensor(dev.d, BF16, (M, 1024)), mb.Tensor(dev.d, BF16, (M, 3072))
+        keep, grouped = [], []
+        for li, layer in enumerate(layers):
+            vs = {nm: (xs[K].view_struct(), w.T.view_struct(), outs[N].view_struct()) for (nm, _, _), (w, N, K) in zip(DECODE_LAYER, layer)}
+            vs["v"] = (vs["v"][0], vs["v"][1], outs_v.view_struct())
+            vs["up"] = (vs["up"][0], vs["up"][1], outs_up.view_struct())
+            for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
+                yv, rv = [vs[n][1] for n in names], [vs[n][2] for n in names]
+                ya = (C.POINTER(mb.View) * len(names))(*[C.pointer(v) for v in yv])
+                ra = (C.POINTER(mb.View) * len(names))(*[C.pointer(v) for v in rv])
+                keep.append((yv, rv))
+                grouped.append((vs[names[0]][0], len(names), ya, ra))
 
         def step():
-            for xv, wv, rv in calls:
-                dev.matmul(xv, wv, rv)
+            for xv, n, ya, ra in grouped:
+                mb.check(dev.L.magb200_matmul_grouped(dev.d, C.byref(xv), n, ya, ra))
+            dev.matmul(*calls[-1])
 
         # the token pass is launch-bound when issued call by call (about 200 launches of a few microseconds);
         # it is recorded once and replayed as a CUDA graph, the way a serving loop would run it
@@ -488,7 +504,7 @@ def decode_workload(dev: Dev, cpu: CpuRef, steps: int, warmup: int, hbm_peak: fl
                            "frac_of_nominal_8000": gbs / 8000.0, "launches_per_step": launches // steps,
                            "lm_head_ms": ms_lm / max(steps, 10), "lm_head_gbs": gbs_lm, "lm_head_frac": gbs_lm / hbm_peak,
                            "lm_head_frac_of_nominal_8000": gbs_lm / 8000.0, "kernel": mb.last_kernel()}
-        for t in list(xs.values()) + list(outs.values()):
+        for t in list(xs.values()) + list(outs.values()) + [outs_v, outs_up]:
             t.release()
     for layer in layers:
         for w, _, _ in layer:

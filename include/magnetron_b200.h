@@ -161,6 +161,13 @@ int  magb200_fill(int device, const magb200_view_t *dst, double value);
  * one rounding to the result dtype. */
 int  magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r);
 
+/* `count` (1..4) matmuls that share their first operand: r_i = x @ y_i, e.g. the q, k and v projections or gate and up of a
+ * decode step, which magnetron dispatches as consecutive MAG_OP_MATMULs with the same in[0] (examples/qwen3/model.py:109-111,
+ * :48-49). Decode-shaped groups (M <= 8, 16-bit K-major weights, no K split) run as ONE launch whose 16-row weight tiles
+ * span all the y_i; anything else is executed product by product. Results are bit-identical to `count` magb200_matmul calls. */
+int  magb200_matmul_grouped(int device, const magb200_view_t *x, int count, const magb200_view_t *const *ys,
+                            const magb200_view_t *const *rs);
+
 /* Shape inference of the operator stub (magnetron/core/mag_op_stubs.c:1249-1310) for callers that
  * allocate `r` themselves. Returns MAGB200_ERR_SHAPE with the reference's message on a mismatch. */
 int  magb200_matmul_result_shape(const magb200_view_t *x, const magb200_view_t *y, int32_t *out_rank, int64_t *out_shape);
@@ -190,6 +197,38 @@ int  magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_v
 int  magb200_reduce_broadcast(int device, void *cuda_stream, const void *stage, void *const *peer_out, int nranks, int rank,
                               int64_t rows_per_rank, int64_t n, int dtype);   /* cuda_stream NULL = the device's stream; another
                               stream lets the exchange of one token chunk run beside the next chunk's GEMMs */
+
+/* Planner of a tensor-parallel linear y[M,N] = x[M,K] @ W[N,K]^T over `ranks` GPUs: how to shard it, which exchange to use,
+ * and whether sharding pays. `kind` says how the layer pairs the operator (column: shard N, no exchange; row: shard K, sum of
+ * partial results). The answer may be REPLICATE when the sharded form would be slower than one GPU alone (tiny operators,
+ * whose collective costs more than the work it saves); `pays` is set when the predicted speed-up is at least half of linear. */
+typedef enum magb200_tp_mode_t { MAGB200_TP_REPLICATE = 0, MAGB200_TP_COLUMN = 1, MAGB200_TP_ROW = 2 } magb200_tp_mode_t;
+typedef enum magb200_tp_exchange_t {
+    MAGB200_TP_EXCHANGE_NONE = 0,
+    MAGB200_TP_EXCHANGE_NCCL = 1,      /* local GEMM, then an NCCL all-reduce */
+    MAGB200_TP_EXCHANGE_SCATTER = 2,   /* magb200_matmul_scatter + magb200_reduce_broadcast over peer memory */
+    MAGB200_TP_EXCHANGE_SWITCH = 3     /* local GEMM + magb200_multimem_reduce_broadcast (in-switch reduction) */
+} magb200_tp_exchange_t;
+typedef struct magb200_tp_plan_t {
+    int32_t mode;          /* magb200_tp_mode_t */
+    int32_t exchange;      /* magb200_tp_exchange_t */
+    int32_t chunks;        /* token chunks to pipeline through the layer (1: none) */
+    int32_t pays;          /* predicted speed-up >= ranks / 2 */
+    double  single_us;     /* predicted time on one GPU */
+    double  sharded_us;    /* predicted time per rank, exchange included */
+    double  speedup;
+} magb200_tp_plan_t;
+int  magb200_tp_plan(int64_t M, int64_t N, int64_t K, int ranks, int kind, int dtype, int has_peer_access, int has_multicast,
+                     magb200_tp_plan_t *out);
+
+/* The exchange of a row-sharded linear through the NVSwitch (NVLS), for buffers that all ranks allocated symmetrically and bound
+ * to a multicast object: every rank's GEMM writes its partial [M,N] into its own `partial` buffer (plain magb200_matmul), the
+ * ranks meet at a barrier, then each rank calls this for its row block: multimem.ld_reduce on `mc_partial` (the multicast
+ * address of the partial buffers) makes the switch sum the block over all ranks, multimem.st on `mc_out` writes the sum into
+ * every rank's output. A rank then receives and sends each byte of the result once instead of once per peer. No counterpart
+ * in the reference. `max_ctas` bounds the grid (0 = default) so the kernel can run beside a GEMM on a side stream. */
+int  magb200_multimem_reduce_broadcast(int device, void *cuda_stream, const void *mc_partial, void *mc_out, int nranks, int rank,
+                                       int64_t rows_per_rank, int64_t n, int dtype, int max_ctas);
 
 /* Decode-shaped matmul (M <= 8) that allocates nothing, for callers that are not allowed to call
  * cudaMalloc (a plug-in inside another framework's stream-ordered region, a serving loop that must not touch

@@ -34,6 +34,16 @@ class View(C.Structure):
                 ("shape", C.c_int64 * MAX_DIMS), ("strides", C.c_int64 * MAX_DIMS)]
 
 
+class TpPlan(C.Structure):
+    """magb200_tp_plan_t"""
+    _fields_ = [("mode", C.c_int32), ("exchange", C.c_int32), ("chunks", C.c_int32), ("pays", C.c_int32),
+                ("single_us", C.c_double), ("sharded_us", C.c_double), ("speedup", C.c_double)]
+
+
+TP_REPLICATE, TP_COLUMN, TP_ROW = 0, 1, 2
+TP_EXCHANGE = {0: "none", 1: "nccl", 2: "scatter", 3: "switch"}
+
+
 class MagB200Error(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"magb200 error {code}: {message}")
@@ -51,6 +61,7 @@ _lib = None
 
 # name -> (restype, argtypes); one entry per declaration in include/magnetron_b200.h
 _VP = C.POINTER(View)
+
 SIGNATURES = {
     "magb200_last_error": (C.c_char_p, []),
     "magb200_device_count": (C.c_int, []),
@@ -76,6 +87,7 @@ SIGNATURES = {
     "magb200_fill": (C.c_int, [C.c_int, _VP, C.c_double]),
     "magb200_cat": (C.c_int, [C.c_int, C.POINTER(_VP), C.c_int, C.c_int, _VP]),
     "magb200_matmul": (C.c_int, [C.c_int, _VP, _VP, _VP]),
+    "magb200_matmul_grouped": (C.c_int, [C.c_int, _VP, C.c_int, C.POINTER(_VP), C.POINTER(_VP)]),
     "magb200_matmul_result_shape": (C.c_int, [_VP, _VP, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "magb200_last_kernel": (C.c_int, []),
     "magb200_launch_count": (C.c_uint64, []),
@@ -91,6 +103,8 @@ SIGNATURES = {
     "magb200_set_balanced_last_wave": (C.c_int, [C.c_int]),
     "magb200_matmul_scatter": (C.c_int, [C.c_int, _VP, _VP, C.POINTER(C.c_void_p), C.c_int, C.c_int]),
     "magb200_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int]),
+    "magb200_tp_plan": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(TpPlan)]),
+    "magb200_multimem_reduce_broadcast": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int]),
     "magb200_matmul_skinny_noalloc": (C.c_int, [C.c_int, C.c_void_p, _VP, _VP, _VP]),
     "magb200_matmul_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP, C.c_size_t, _VP]),
     "magb200_cast_host": (C.c_int, [C.c_int, _VP, C.c_size_t, _VP]),

@@ -171,8 +171,18 @@ static int ensure_scratch(DeviceState &d, size_t bytes) {
 // ---- which results may still be in flight under programmatic dependent launch -----------------------------------------
 static void ordered_point(DeviceState &d) { d.n_in_flight = 0; d.in_flight_overflow = false; }   // a fully ordered launch or copy
 static void note_early_result(DeviceState &d, const void *ptr, size_t bytes) {
-    if (d.n_in_flight < 32) { d.in_flight[d.n_in_flight].lo = (uintptr_t)ptr; d.in_flight[d.n_in_flight].hi = (uintptr_t)ptr + bytes; ++d.n_in_flight; }
-    else d.in_flight_overflow = true;
+    const uintptr_t lo = (uintptr_t)ptr, hi = lo + bytes;
+    for (int i = 0; i < d.n_in_flight; ++i)          // a decode loop writes the same few result buffers over and over
+        if (lo >= d.in_flight[i].lo && hi <= d.in_flight[i].hi) return;
+    if (d.n_in_flight < 32) { d.in_flight[d.n_in_flight].lo = lo; d.in_flight[d.n_in_flight].hi = hi; ++d.n_in_flight; return; }
+    // full: fold everything into one covering range (weights inside it are then read after the wait, which is always safe)
+    AddrRange all = {lo, hi};
+    for (int i = 0; i < d.n_in_flight; ++i) {
+        if (d.in_flight[i].lo < all.lo) all.lo = d.in_flight[i].lo;
+        if (d.in_flight[i].hi > all.hi) all.hi = d.in_flight[i].hi;
+    }
+    d.in_flight[0] = all;
+    d.n_in_flight = 1;
 }
 // Byte range an operand of the canonical problem can touch: base .. last addressed element.
 static AddrRange weight_range(const GemmProblem &g) {
@@ -831,6 +841,35 @@ int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y,
     return matmul_device(*d, device, x, y, r);
 }
 
+int magb200_matmul_grouped(int device, const magb200_view_t *x, int count, const magb200_view_t *const *ys, const magb200_view_t *const *rs) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!x || !ys || !rs || count < 1 || count > 4) { set_error("matmul_grouped: 1..4 products per call"); return MAGB200_ERR_INVALID_ARG; }
+    FullProblem fp[4];
+    GemmProblem gs[4];
+    bool one_launch = count > 1 && g_force.load() == 0;
+    bool settled = true;
+    for (int i = 0; i < count; ++i) {
+        if ((rc = build_problem(x, ys[i], rs[i], fp[i]))) return rc;
+        gs[i] = fp[i].g;
+        one_launch = one_launch && fp[i].n_outer == 0;
+        settled = settled && weights_settled(*d, gs[i]);
+    }
+    if (one_launch) {
+        rc = launch_skinny_grouped(gs, count, d->stream, settled);
+        if (rc == MAGB200_OK) {
+            g_last_kernel = MAGB200_KERNEL_SKINNY;
+            for (int i = 0; i < count; ++i) note_early_result(*d, gs[i].C, (size_t)(gs[i].M * gs[i].N) * dtype_size(gs[i].dtype));
+            return MAGB200_OK;
+        }
+        if (rc < 0) return rc;
+    }
+    for (int i = 0; i < count; ++i)
+        if ((rc = matmul_device(*d, device, x, ys[i], rs[i]))) return rc;
+    return MAGB200_OK;
+}
+
 int magb200_matmul_scatter(int device, const magb200_view_t *x, const magb200_view_t *y, void *const *peer_stage, int nranks, int rank) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
@@ -900,6 +939,65 @@ int magb200_test_inject_fault(int site, int cuda_error) {
     }
     g_inject[site].store(cuda_error);
     return MAGB200_OK;
+}
+
+// ---- tensor-parallel planner ---------------------------------------------------------------------------------------------
+// Cost model in microseconds, from figures measured on this part: tensor-core GEMMs 1400 TFLOP/s, weight streaming 6000 GB/s,
+// NVLink 650 GB/s per direction per GPU, 3 us per launch, an NCCL all-reduce 12 us before its first byte, the fused exchanges
+// two cross-rank barriers of 4 us and one kernel.
+int magb200_tp_plan(int64_t M, int64_t N, int64_t K, int ranks, int kind, int dtype, int has_peer_access, int has_multicast,
+                    magb200_tp_plan_t *out) {
+    if (!out || M < 1 || N < 1 || K < 1 || ranks < 1 || ranks > 8 || (kind != MAGB200_TP_COLUMN && kind != MAGB200_TP_ROW) || !dtype_ok(dtype)) {
+        set_error("tp_plan: bad argument");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    const double es = (double)dtype_size(dtype), p = (double)ranks;
+    const double kTensor = 1400e6 /*FLOP per us*/, kHbm = 6000e3 /*bytes per us*/, kLink = 650e3, kLaunch = 3.0, kNccl = 12.0, kBarrier = 4.0;
+    auto gemm_us = [&](double m, double n, double k) {
+        const double flops = 2.0 * m * n * k, bytes = es * (m * k + n * k + m * n);
+        const double t = flops / kTensor, b = bytes / kHbm;
+        return (t > b ? t : b) + kLaunch;
+    };
+    memset(out, 0, sizeof(*out));
+    out->single_us = gemm_us((double)M, (double)N, (double)K);
+    out->chunks = 1;
+    if (ranks == 1) { out->mode = kind; out->exchange = MAGB200_TP_EXCHANGE_NONE; out->sharded_us = out->single_us; out->pays = 0; return MAGB200_OK; }
+    if (kind == MAGB200_TP_COLUMN) {          // independent GEMMs on N / p columns, no exchange
+        out->mode = MAGB200_TP_COLUMN;
+        out->exchange = MAGB200_TP_EXCHANGE_NONE;
+        out->sharded_us = gemm_us((double)M, (double)N / p, (double)K);
+    } else {                                  // partial products over K / p, then the sum of p partial [M,N] results
+        const double result_bytes = es * (double)M * (double)N;
+        const double wire = result_bytes * (p - 1.0) / p;          // per rank and direction, reduce-scatter + all-gather halves
+        double ex;
+        const bool fused_ok = has_peer_access && M % ranks == 0 && M >= 256 && N % 8 == 0 && dtype != MAGB200_F32;
+        // the in-switch reduction moves fewer bytes per rank only from four ranks up ((p-1)/p + 1/p against 2 (p-1)/p), and at
+        // two ranks it ran at a third of the peer-store path's rate
+        if (fused_ok && has_multicast && ranks >= 8) { out->exchange = MAGB200_TP_EXCHANGE_SWITCH; ex = 2 * kBarrier + kLaunch + (wire + result_bytes / p) / kLink; }
+        else if (fused_ok) { out->exchange = MAGB200_TP_EXCHANGE_SCATTER; ex = 2 * kBarrier + kLaunch + 2.0 * wire / kLink; }
+        else { out->exchange = MAGB200_TP_EXCHANGE_NCCL; ex = kNccl + 2.0 * wire / kLink; }
+        out->mode = MAGB200_TP_ROW;
+        out->sharded_us = gemm_us((double)M, (double)N, (double)K / p) + ex;
+        // two token chunks through the layer let the exchange kernels of one chunk fill the gaps between the other chunk's
+        // GEMMs; measured on the Qwen3-32B layer at M = 8192: 8 ranks 7695 against 7440 TFLOP/s unchunked, 2 and 4 ranks no gain
+        out->chunks = (M >= 4096 && ranks >= 8) ? 2 : 1;
+    }
+    if (out->sharded_us > out->single_us) {   // sharding would slow this operator down: every rank keeps the whole weight
+        out->mode = MAGB200_TP_REPLICATE; out->exchange = MAGB200_TP_EXCHANGE_NONE; out->sharded_us = out->single_us; out->chunks = 1;
+    }
+    out->speedup = out->single_us / out->sharded_us;
+    out->pays = out->speedup >= 0.5 * p ? 1 : 0;   // at least half of linear scaling
+    return MAGB200_OK;
+}
+
+int magb200_multimem_reduce_broadcast(int device, void *cuda_stream, const void *mc_partial, void *mc_out, int nranks, int rank,
+                                      int64_t rows_per_rank, int64_t n, int dtype, int max_ctas) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (rows_per_rank < 1 || n < 1) { set_error("multimem_reduce_broadcast: empty block"); return MAGB200_ERR_INVALID_ARG; }
+    return launch_multimem_reduce_broadcast(dtype, mc_partial, mc_out, nranks, rank, rows_per_rank * n, max_ctas,
+                                            cuda_stream ? (cudaStream_t)cuda_stream : d->stream);
 }
 
 int magb200_last_kernel(void) { return g_last_kernel; }

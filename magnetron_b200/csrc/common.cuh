@@ -134,6 +134,7 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_sc
 size_t simt_scratch_bytes(const GemmProblem &p);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled);
+int launch_skinny_grouped(const GemmProblem *ps, int count, cudaStream_t stream, bool weights_settled);   // 1: not applicable
 bool tcgen05_supported(const GemmProblem &p);
 // Destination of a scatter epilogue: every rank's staging buffer [ranks][rows_per_rank][N] (device or peer-mapped pointers)
 struct ScatterTarget {
@@ -155,6 +156,9 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_l
                             const SplitWorkspace *ws = nullptr);
 void set_balance_tail(int enabled);
 int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems, cudaStream_t stream);
+
+int launch_multimem_reduce_broadcast(int dtype, const void *mc_partial, void *mc_out, int ranks, int rank, int64_t block_elems, int max_ctas,
+                                     cudaStream_t stream);
 
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
                 const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);

@@ -35,6 +35,7 @@ constexpr int kWarps = kThreads / 32;
 template <int DT> struct Elem { static constexpr int size = 2; static constexpr int vec = 8; using bits = uint16_t; };
 template <> struct Elem<MAGB200_F32> { static constexpr int size = 4; static constexpr int vec = 4; using bits = uint32_t; };
 
+constexpr int kMaxGroups = 4;
 struct SkinnyArgs {
     const void *A, *B;
     void *C;            // result [batch][M][N] in the operand dtype (used when nsplit == 1)
@@ -48,6 +49,13 @@ struct SkinnyArgs {
     int64_t bshape[kMaxBatchDims], bsA[kMaxBatchDims], bsB[kMaxBatchDims];
     int64_t batch_total;
     int early_weights;  // 1: the weights were not written by a kernel that may still be running; they may be fetched before pdl_wait()
+    // grouped launch (skinny_km_mma_kernel only): several weight matrices against the same activation rows, e.g. the q, k and
+    // v projections of a decode step. Group i owns the 16-row tiles [gtile0[i], gtile0[i+1]) of the launch.
+    int ngroups;        // 0: a single problem described by B, C, N, ldb above
+    const void *gB[kMaxGroups];
+    void *gC[kMaxGroups];
+    int64_t gN[kMaxGroups], gldb[kMaxGroups];
+    int64_t gtile0[kMaxGroups + 1];
 };
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while its
@@ -209,6 +217,34 @@ template <int DT> __device__ __forceinline__ void mma_16816(float (&c)[4], uint3
     }
 }
 
+// Stage the (up to 8) activation rows of this CTA's K range in shared memory. All rows are copied in one flattened loop
+// whose loads are issued four at a time before their stores: a row-by-row loop pays one L2 round trip per row, which made a
+// small projection take 8.3 us at M = 8 against 5.6 us at M = 1 for the same weight bytes.
+__device__ __forceinline__ void stage_activations(const SkinnyArgs &a, int M, int xstride, int64_t offA, int64_t k0, int kc, uint16_t *xs) {
+    const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
+    const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
+    if (vec) {
+        const int chunks = kc >> 3;                 // kc is a multiple of 8
+        const int total = M * chunks;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kThreads) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kThreads;
+                if (i < total) { const int m = i / chunks, c = i - m * chunks; v[u] = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm)[c]; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kThreads;
+                if (i < total) { const int m = i / chunks, c = i - m * chunks; reinterpret_cast<uint4 *>(xs + m * xstride)[c] = v[u]; }
+            }
+        }
+    } else {
+        for (int m = 0; m < M; ++m)
+            for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
+    }
+}
+
 // KW warps of the CTA split the CTA's K range, RW = 8 / KW warps take different 16-row tiles.
 // Fragment bookkeeping (g = lane / 4, t = lane % 4): the thread loads K values [k, k+8) of weight rows
 // r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
@@ -236,13 +272,27 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
     per = (per + 31) / 32 * 32;
     const int ks = min(kc, kw * per), ke = min(kc, ks + per);
     const int nfull = (ke - ks) >> 5;
-    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
     const uint16_t *xrow = xs + g * xstride;
     const bool has_x = g < M;
+    // which weight matrix a tile of the launch belongs to (one matrix unless the launch is grouped)
+    const uint16_t *Bbase;
+    uint16_t *Cg;
+    int64_t Ng, ldbg, tile_first;
+    auto select_group = [&](int64_t tile) {
+        int gi = 0;
+        if (a.ngroups > 1) {
+            while (gi + 1 < a.ngroups && tile >= a.gtile0[gi + 1]) ++gi;
+            Bbase = reinterpret_cast<const uint16_t *>(a.gB[gi]) + k0;
+            Cg = reinterpret_cast<uint16_t *>(a.gC[gi]); Ng = a.gN[gi]; ldbg = a.gldb[gi]; tile_first = a.gtile0[gi];
+        } else {
+            Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
+            Cg = reinterpret_cast<uint16_t *>(a.C); Ng = a.N; ldbg = a.ldb; tile_first = 0;
+        }
+    };
 
     // 16-row tiles are dealt out evenly: unit u (a row-warp slot of some CTA) takes tiles [u*T/U, (u+1)*T/U).
     // Every warp of a CTA runs the same number of rounds (the K-slice reduction below has CTA barriers).
-    const int64_t T = (a.N + 15) / 16;
+    const int64_t T = a.ngroups > 1 ? a.gtile0[a.ngroups] : (a.N + 15) / 16;
     const int64_t U = (int64_t)gridDim.x * RW;
     const int64_t u = (int64_t)blockIdx.x * RW + rw;
     const int64_t t_begin = u * T / U, t_end = (u + 1) * T / U;
@@ -253,41 +303,29 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
     if (!a.early_weights) pdl_wait();
     uint4 pre_a[kPre], pre_b[kPre];
     const int npre = (t_begin < t_end) ? min(nfull, kPre) : 0;
+    select_group(t_begin < T ? t_begin : 0);
     if (npre > 0) {
-        const uint4 *qa = reinterpret_cast<const uint4 *>(Bbase + min(t_begin * 16 + g, a.N - 1) * a.ldb + ks) + t;
-        const uint4 *qb = reinterpret_cast<const uint4 *>(Bbase + min(t_begin * 16 + g + 8, a.N - 1) * a.ldb + ks) + t;
+        const int64_t rp = (t_begin - tile_first) * 16;
+        const uint4 *qa = reinterpret_cast<const uint4 *>(Bbase + min(rp + g, Ng - 1) * ldbg + ks) + t;
+        const uint4 *qb = reinterpret_cast<const uint4 *>(Bbase + min(rp + g + 8, Ng - 1) * ldbg + ks) + t;
 #pragma unroll
         for (int i = 0; i < kPre; ++i)
             if (i < npre) { pre_a[i] = ldg_stream(qa + 4 * i); pre_b[i] = ldg_stream(qb + 4 * i); }
     }
 
     pdl_wait();
-    {
-        // stage the activation rows: 16-byte copies when the rows are unit-stride and aligned, else element-wise
-        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
-        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
-        if (vec) {
-            const int chunks = kc >> 3;  // kc is a multiple of 8
-            for (int m = 0; m < M; ++m) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
-                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
-                for (int c = threadIdx.x; c < chunks; c += kThreads) dst[c] = src[c];
-            }
-        } else {
-            for (int m = 0; m < M; ++m)
-                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
-        }
-    }
+    stage_activations(a, M, xstride, offA, k0, kc, xs);
     __syncthreads();
 
     for (int64_t round = 0; round < rounds; ++round) {
         const int64_t tile = t_begin + round;
         const bool active = tile < t_end;
-        const int64_t r0 = tile * 16;
+        if (active) select_group(tile);
+        const int64_t r0 = (tile - tile_first) * 16;
         float c[4] = {0.f, 0.f, 0.f, 0.f};
         if (active) {
-            const uint16_t *pa = Bbase + min(r0 + g, a.N - 1) * a.ldb;       // clamp: tail rows are loaded twice, stored once
-            const uint16_t *pb = Bbase + min(r0 + g + 8, a.N - 1) * a.ldb;
+            const uint16_t *pa = Bbase + min(r0 + g, Ng - 1) * ldbg;       // clamp: tail rows are loaded twice, stored once
+            const uint16_t *pb = Bbase + min(r0 + g + 8, Ng - 1) * ldbg;
             // The trip count is the same for all 32 lanes (mma.sync needs the whole warp). Full 32-wide K chunks run
             // without predicates so the compiler can keep eight 16-byte loads in flight per lane; the ragged last
             // chunk (K slice not a multiple of 32) is one predicated step in which out-of-range lanes feed zeros.
@@ -349,7 +387,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
             for (int i = 0; i < 4; ++i) {
                 const int64_t n = r0 + g + (i >> 1) * 8;
                 const int m = 2 * t + (i & 1);
-                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i]);
+                if (n < Ng && m < M) {
+                    if (a.ngroups > 1) store_from_f32<DT>(Cg, (int64_t)m * Ng + n, c[i]);
+                    else store_result<DT>(a, batch, split, m, M, n, c[i]);
+                }
             }
         }
     }
@@ -424,19 +465,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
 
     // the weight copies above do not depend on a kernel still in flight (or came after the wait); the activations may
     pdl_wait();
-    {
-        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
-        const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
-        for (int m = 0; m < M; ++m) {
-            if (vec) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm);
-                uint4 *dst = reinterpret_cast<uint4 *>(xs + m * xstride);
-                for (int c = threadIdx.x; c < (kc >> 3); c += kThreads) dst[c] = src[c];
-            } else {
-                for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
-            }
-        }
-    }
+    stage_activations(a, M, xstride, offA, k0, kc, xs);
     __syncthreads();
     float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains: consecutive mma do not wait on each other
     int c_ks = 0, c_slot = 0;
@@ -841,6 +870,7 @@ int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scra
     a.ldb = pl.km ? p.sBn : p.sBk;
     a.kch = pl.kch; a.nsplit = pl.nsplit; a.nbatch = p.nbatch; a.batch_total = p.batch_total;
     a.early_weights = weights_settled ? 1 : 0;
+    a.ngroups = 0;
     for (int d = 0; d < kMaxBatchDims; ++d) { a.bshape[d] = p.bshape[d]; a.bsA[d] = p.bsA[d]; a.bsB[d] = p.bsB[d]; }
     int rc;
     switch (p.M) {
@@ -862,6 +892,59 @@ int launch_dt(const GemmProblem &p, cudaStream_t st, float *scratch, size_t scra
 }
 
 }  // namespace
+
+namespace {
+template <int DT>
+int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool weights_settled) {
+    // plan for one problem with all the groups' 16-row tiles; only the register-load kernel without a K split is grouped
+    GemmProblem pc = ps[0];
+    SkinnyArgs a;
+    memset(&a, 0, sizeof(a));
+    int64_t tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        a.gB[i] = ps[i].B; a.gC[i] = ps[i].C; a.gN[i] = ps[i].N; a.gldb[i] = ps[i].sBn;
+        a.gtile0[i] = tiles;
+        tiles += (ps[i].N + 15) / 16;
+    }
+    a.gtile0[count] = tiles;
+    pc.N = tiles * 16;
+    Plan pl;
+    if (!make_plan<DT>(pc, pl) || !pl.mma || pl.async || pl.nsplit != 1) return 1;   // not applicable: the caller launches one by one
+    a.A = pc.A; a.B = nullptr; a.C = nullptr; a.partial = nullptr;
+    a.N = pc.N; a.K = pc.K; a.sAm = pc.sAm; a.sAk = pc.sAk; a.ldb = 0;
+    a.kch = pl.kch; a.nsplit = 1; a.nbatch = 0; a.batch_total = 1;
+    a.early_weights = weights_settled ? 1 : 0;
+    a.ngroups = count;
+    const int M = (int)pc.M;
+    dim3 grid(pl.gridx, 1, 1);
+    int rc = MAGB200_OK;
+#define LAUNCH_KW(KWV)                                                                                   \
+    case KWV:                                                                                            \
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
+        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
+        break;
+    switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
+#undef LAUNCH_KW
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+}  // namespace
+
+// Several decode-shaped products with the same activation rows in one launch: r_i = x . y_i. Returns 1 when the group cannot
+// run as one launch (mixed layouts, a K split, too many tiles: those shapes are better off alone anyway).
+int launch_skinny_grouped(const GemmProblem *ps, int count, cudaStream_t st, bool weights_settled) {
+    if (count < 2 || count > kMaxGroups) return 1;
+    const GemmProblem &p0 = ps[0];
+    if (p0.dtype == MAGB200_F32 || p0.M < 1 || p0.M > 8) return 1;
+    for (int i = 0; i < count; ++i) {
+        const GemmProblem &p = ps[i];
+        if (p.dtype != p0.dtype || p.M != p0.M || p.K != p0.K || p.A != p0.A || p.sAm != p0.sAm || p.sAk != p0.sAk) return 1;
+        if (p.batch_total != 1 || p.nbatch != 0 || p.sBk != 1 || p.K < 2 || p.K % 8 || p.sBn % 8 || ((uintptr_t)p.B & 15u)) return 1;
+    }
+    return p0.dtype == MAGB200_BF16 ? launch_grouped_dt<MAGB200_BF16>(ps, count, st, weights_settled)
+                                    : launch_grouped_dt<MAGB200_F16>(ps, count, st, weights_settled);
+}
 
 bool skinny_supported(const GemmProblem &p) {
     if (p.M < 1 || p.M > 8) return false;

@@ -49,7 +49,67 @@ __global__ void __launch_bounds__(kThreads) reduce_broadcast_kernel(const uint4 
     }
 }
 
+// The same exchange through the NVSwitch: `mc_partial` and `mc_out` are multicast addresses of buffers that every rank
+// allocated symmetrically (each rank's partial product [M,N] in its own memory, each rank's output [M,N]). One
+// multimem.ld_reduce makes the switch fetch the 16 bytes at that offset from every rank's partial and add them (fp32
+// accumulation), so a rank receives its row block once instead of once per peer; one multimem.st writes the finished 16
+// bytes into every rank's output, so it leaves the rank once. Per GEMM a rank moves (p-1)/p + 1/p of the tensor in each
+// direction instead of twice (p-1)/p, and the GEMM keeps its plain local epilogue.
+template <int DT>
+__global__ void __launch_bounds__(kThreads) multimem_reduce_broadcast_kernel(const uint4 *mc_partial, uint4 *mc_out, int64_t first_vec,
+                                                                            int64_t block_vecs) {
+    // A reduction through the switch takes microseconds to come back, so every thread keeps kInFlight of them in flight
+    // (issued back to back, stored afterwards): 16 bytes x 8 x 256 threads x the grid is what covers the link's latency.
+    constexpr int kInFlight = 8;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; i0 < block_vecs; i0 += stride * kInFlight) {
+        uint32_t v[kInFlight][4];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i < block_vecs) {
+                const uint4 *src = mc_partial + first_vec + i;
+                if constexpr (DT == MAGB200_BF16)
+                    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(src) : "memory");
+                else
+                    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3]) : "l"(src) : "memory");
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i < block_vecs)
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                             ::"l"(mc_out + first_vec + i), "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3]) : "memory");
+        }
+    }
+}
+
 }  // namespace
+
+int launch_multimem_reduce_broadcast(int dtype, const void *mc_partial, void *mc_out, int ranks, int rank, int64_t block_elems,
+                                     int max_ctas, cudaStream_t stream) {
+    if (ranks < 1 || ranks > kMaxRanks || rank < 0 || rank >= ranks) { set_error("multimem_reduce_broadcast: bad rank %d of %d", rank, ranks); return MAGB200_ERR_INVALID_ARG; }
+    if (!mc_partial || !mc_out || block_elems % 8 || (((uintptr_t)mc_partial | (uintptr_t)mc_out) & 15u)) {
+        set_error("multimem_reduce_broadcast: multicast addresses must be non-null and 16-byte aligned, the row block a multiple of 8 elements");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    const int64_t vecs = block_elems / 8;
+    int64_t blocks = (vecs + kThreads * 8 - 1) / (kThreads * 8);
+    const int64_t cap = max_ctas > 0 ? max_ctas : num_sms() * 2;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) return MAGB200_OK;
+    if (dtype == MAGB200_BF16)
+        multimem_reduce_broadcast_kernel<MAGB200_BF16><<<(unsigned)blocks, kThreads, 0, stream>>>((const uint4 *)mc_partial, (uint4 *)mc_out, (int64_t)rank * vecs, vecs);
+    else if (dtype == MAGB200_F16)
+        multimem_reduce_broadcast_kernel<MAGB200_F16><<<(unsigned)blocks, kThreads, 0, stream>>>((const uint4 *)mc_partial, (uint4 *)mc_out, (int64_t)rank * vecs, vecs);
+    else { set_error("multimem_reduce_broadcast: 16-bit dtypes only"); return MAGB200_ERR_INVALID_ARG; }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
 
 int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems,
                             cudaStream_t stream) {

@@ -72,6 +72,12 @@ def layer_flops(specs: Sequence[ShardedLinear], m: int) -> float:
     return sum(2.0 * m * s.n * s.k for s in specs)
 
 
+def activation_block(m: int, width: int, seed: int, name: str, index: int) -> torch.Tensor:
+    """Columns [index*width, (index+1)*width) of the seeded activation of linear `name`: fp32 ~ N(0,1)."""
+    g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + 17 + 7919 * sum(map(ord, name)) + index)
+    return torch.randn((m, width), generator=g, dtype=torch.float32)
+
+
 def cabi_matmul(device: int, reserve_sms: int = 0) -> Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]:
     """out[M,N] = x[M,K] @ w[N,K].T on `device` through magb200_matmul, on torch's current stream. `reserve_sms` SMs are
     left free by the tensor-core GEMMs for a collective that runs at the same time."""
@@ -146,13 +152,83 @@ class FusedRowLinear:
         return self.finish()
 
 
+class SwitchRowLinear:
+    """Row-sharded linear whose exchange goes through the NVSwitch: the GEMM writes this rank's partial product into its own
+    symmetric buffer (plain epilogue, nothing crosses NVLink during the GEMM), a barrier orders the ranks, then
+    `magb200_multimem_reduce_broadcast` lets the switch sum this rank's row block over all ranks (multimem.ld_reduce) and write
+    the sum into every rank's output (multimem.st). Same two-step interface as FusedRowLinear. Needs a multicast binding of
+    the symmetric buffers (NVLS); `available()` says whether this group has one."""
+
+    def __init__(self, m: int, n: int, dtype, device: torch.device, matmul: Callable, group=None, max_ctas: int = 0):
+        import torch.distributed._symmetric_memory as symm_mem
+        import magnetron_b200 as mb
+        self.mb, self.L, self.matmul, self.max_ctas = mb, mb.lib(), matmul, max_ctas
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if m % self.world:
+            raise ValueError(f"token count {m} must be divisible by the {self.world} ranks")
+        self.m, self.n, self.dev = m, n, device.index or 0
+        self.partial = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self.out = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self.h_partial = symm_mem.rendezvous(self.partial, self.group)
+        self.h_out = symm_mem.rendezvous(self.out, self.group)
+        self.mc_partial, self.mc_out = int(self.h_partial.multicast_ptr or 0), int(self.h_out.multicast_ptr or 0)
+        if not self.mc_partial or not self.mc_out:
+            raise RuntimeError("the symmetric buffers have no multicast binding on this system")
+        self.dt = {torch.bfloat16: mb.BFLOAT16, torch.float16: mb.FLOAT16}[dtype]
+
+    @staticmethod
+    def available(device: torch.device, group=None) -> bool:
+        """True when a symmetric allocation of this group comes with a multicast address (probed once with a small buffer)."""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            t = symm_mem.empty((4096,), dtype=torch.bfloat16, device=device)
+            h = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+            return bool(h.multicast_ptr)
+        except Exception:   # noqa: BLE001 - no symmetric memory, no NVLS: the caller picks another exchange
+            return False
+
+    def scatter(self, x: torch.Tensor, w: torch.Tensor) -> None:
+        """First half on the current stream: the local GEMM into the symmetric partial buffer, then the barrier after which
+        every rank's partial is complete."""
+        self.matmul(x, w, self.partial)
+        self.h_partial.barrier(channel=0)
+
+    def finish(self) -> torch.Tensor:
+        stream = torch.cuda.current_stream(self.out.device).cuda_stream
+        self.mb.check(self.L.magb200_multimem_reduce_broadcast(self.dev, C.c_void_p(stream) if stream else None, C.c_void_p(self.mc_partial),
+                                                               C.c_void_p(self.mc_out), self.world, self.rank, self.m // self.world, self.n,
+                                                               self.dt, self.max_ctas))
+        self.h_out.barrier(channel=1)
+        return self.out
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        self.scatter(x, w)
+        return self.finish()
+
+
+def plan_linear(spec: ShardedLinear, m: int, world: int, *, peer_access: bool, multicast: bool, dtype_code: int = 2):
+    """The library's decision for one linear (magb200_tp_plan): sharding mode, exchange, token chunks, and whether it pays."""
+    import magnetron_b200 as mb
+    pl = mb.TpPlan()
+    mb.check(mb.lib().magb200_tp_plan(m, spec.n, spec.k, world, mb.TP_COLUMN if spec.kind == "col" else mb.TP_ROW, dtype_code,
+                                      int(peer_access), int(multicast), C.byref(pl)))
+    return {"mode": ["replicate", "column", "row"][pl.mode], "exchange": mb.TP_EXCHANGE[pl.exchange], "chunks": pl.chunks, "pays": bool(pl.pays),
+            "single_us": pl.single_us, "sharded_us": pl.sharded_us, "speedup": pl.speedup}
+
+
 class TPLayer:
     """The sharded linears of one layer on this rank, with resident weight shards and preallocated outputs."""
 
     def __init__(self, specs: Sequence[ShardedLinear], m: int, *, device: torch.device, dtype=torch.bfloat16,
                  matmul: Callable | None = None, group=None, seed: int = 5, chunks: int = 4, reserve_sms: int = 0,
-                 fused: bool = False):
+                 fused: bool = False, exchange: str = "scatter", side_ctas: int = 0, keep_full: Sequence[str] = ()):
+        """`fused`: row-sharded linears use a fused exchange of this package instead of NCCL; `exchange` picks it
+        ("scatter": scatter epilogue + reduce-broadcast over peer memory, "switch": in-switch reduction, "auto": what
+        magb200_tp_plan says, which also sets the chunk count)."""
         self.specs, self.m, self.group = tuple(specs), m, group
+        self.plan = None
+        self.full_w = {}
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if matmul is None:
@@ -160,19 +236,37 @@ class TPLayer:
                 raise RuntimeError("TPLayer runs on CUDA devices only: there is no CPU path")
             matmul = cabi_matmul(device.index or 0, reserve_sms)
         self.matmul = matmul
+        if fused and exchange == "auto" and self.world > 1:
+            multicast = SwitchRowLinear.available(device, group)
+            self.plan = {s.name: plan_linear(s, m, self.world, peer_access=True, multicast=multicast) for s in self.specs}
+            rows = [self.plan[s.name] for s in self.specs if s.kind == "row"]
+            chunks = max([r["chunks"] for r in rows] or [1])
+            kinds = {r["exchange"] for r in rows}
+            exchange = "switch" if "switch" in kinds else ("scatter" if "scatter" in kinds else "nccl")
+            if exchange == "nccl":
+                fused = False
+        self.exchange = exchange
         self.chunks = max(1, min(chunks, m // 512)) if m >= 1024 else 1
         self.fused = {}
         self.fused_chunks = {}
+        # linears the plan keeps whole on every rank (their exchange would cost more than sharding saves)
+        self.replicated = {n for n, pl in (self.plan or {}).items() if pl["mode"] == "replicate"}
         self.side_stream = None
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.w, self.x, self.y = {}, {}, {}
         for s in self.specs:
             n_loc, k_loc = local_shape(s, self.world, self.rank)
+            if s.name in self.replicated and s.n * s.k <= (1 << 27):
+                n_loc, k_loc = s.n, s.k
+            else:
+                self.replicated.discard(s.name)
             # the full weight is drawn from one seeded stream and sliced, so every world size multiplies the
             # same matrix; only the local shard is kept on the device
             full = torch.randn((s.n, s.k), generator=gen, dtype=torch.float32) * 0.02 if s.n * s.k <= (1 << 27) else None
             if full is not None:
-                if s.kind == "col":
+                if s.name in self.replicated:
+                    shard = full
+                elif s.kind == "col":
                     lo, hi = shard_range(s.n, self.world, self.rank, s.granule)
                     shard = full[lo:hi]
                 else:
@@ -182,15 +276,24 @@ class TPLayer:
             else:  # too large to materialise on the host in one piece: seeded per shard
                 g2 = torch.Generator(device="cpu").manual_seed(seed * 1000 + self.rank)
                 self.w[s.name] = (torch.randn((n_loc, k_loc), generator=g2, dtype=torch.float32) * 0.02).to(dtype).to(device)
-            xin = torch.randn((m, k_loc), generator=torch.Generator(device="cpu").manual_seed(seed + 17), dtype=torch.float32)
-            self.x[s.name] = xin.to(dtype).to(device)
-            if fused and s.kind == "row" and self.world > 1 and m % self.world == 0 and m >= 256:
-                self.fused[s.name] = FusedRowLinear(m, s.n, dtype, device, group)
+            # the activation is one [m, K] matrix for every world size, drawn in blocks of `granule` columns with a seed per
+            # block; a rank materialises only the blocks of its K range (all of them for a column-sharded linear)
+            k_lo = shard_range(s.k, self.world, self.rank, s.granule)[0] if (s.kind == "row" and s.name not in self.replicated) else 0
+            blocks = [activation_block(m, s.granule, seed, s.name, (k_lo + j) // s.granule) for j in range(0, k_loc, s.granule)]
+            self.x[s.name] = torch.cat(blocks, dim=1).to(dtype).to(device)
+            if s.name in keep_full and full is not None:
+                self.full_w[s.name] = full.to(dtype)
+            if fused and s.kind == "row" and s.name not in self.replicated and self.world > 1 and m % self.world == 0 and m >= 256:
+                def make(rows):
+                    if exchange == "switch":
+                        return SwitchRowLinear(rows, s.n, dtype, device, self.matmul, group, side_ctas)
+                    return FusedRowLinear(rows, s.n, dtype, device, group)
+                self.fused[s.name] = make(m)
                 self.y[s.name] = self.fused[s.name].out
                 mc = m // self.chunks
                 if self.chunks > 1 and m % self.chunks == 0 and mc % self.world == 0:
                     # one exchange object per token chunk, so chunks can be in flight at the same time
-                    self.fused_chunks[s.name] = [FusedRowLinear(mc, s.n, dtype, device, group) for _ in range(self.chunks)]
+                    self.fused_chunks[s.name] = [make(mc) for _ in range(self.chunks)]
             else:
                 self.y[s.name] = torch.empty((m, n_loc), dtype=dtype, device=device)
 
@@ -207,7 +310,7 @@ class TPLayer:
         """Partial product over this rank's K range, then a sum all-reduce; cut into chunks of M so that the
         all-reduce of chunk i runs while chunk i+1 multiplies."""
         x, w, y = self.x[name], self.w[name], self.y[name]
-        if self.world == 1:
+        if self.world == 1 or name in self.replicated:
             self.matmul(x, w, y)
             return y
         works = []
@@ -226,6 +329,15 @@ class TPLayer:
                 self.column(s.name, gather=gather_outputs)
             else:
                 self.row(s.name)
+
+    def step_auto(self) -> None:
+        """The schedule the library picks for this layer: fused exchange with token chunks in flight when the plan asks for
+        chunks, the fused exchange op by op otherwise, NCCL for shapes no fused exchange takes (few tokens)."""
+        if self.fused_chunks:
+            return self.step_fused_pipelined()
+        if self.fused:
+            return self.step_fused()
+        return self.step(False)
 
     def step_fused(self) -> None:
         """Op by op, the row-sharded linears through the fused GEMM + exchange kernels."""

@@ -70,6 +70,52 @@ def test_shared_last_wave(gpu, M, N, K, layout, dname):
         t.release()
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_grouped_decode_matches_separate_calls(gpu, M, dname):
+    """q/k/v and gate/up of a decode step as one grouped launch each: bit-identical to the separate matmuls, also when a
+    weight's row count is not a multiple of the 16-row tile, and a group that cannot be one launch (a prefill-shaped x)
+    still gives the separate calls' results."""
+    dt = cases.DTYPES[dname]
+    L = mb.lib()
+    rng = np.random.default_rng(19)
+    K = 1024
+    xb = bits(dt, rng, (M, K), 1.0)
+    tx = mb.Tensor.from_bits(gpu, dt, xb)
+    for Ns in ((2048, 1024, 1024), (3072, 3072), (1000, 24, 520, 8)):
+        ws = [mb.Tensor.from_bits(gpu, dt, bits(dt, rng, (N, K), 0.05)) for N in Ns]
+        want = [(tx @ w.T).to_bits() for w in ws]
+        outs = [mb.Tensor(gpu, dt, (M, N)) for N in Ns]
+        for o in outs:
+            mb.check(L.magb200_fill(gpu, C.byref(o.view_struct()), 0.0))
+        yv = [w.T.view_struct() for w in ws]
+        rv = [o.view_struct() for o in outs]
+        ys = (C.POINTER(mb.View) * len(Ns))(*[C.pointer(v) for v in yv])
+        rs = (C.POINTER(mb.View) * len(Ns))(*[C.pointer(v) for v in rv])
+        L.magb200_launch_count_reset()
+        mb.check(L.magb200_matmul_grouped(gpu, C.byref(tx.view_struct()), len(Ns), ys, rs))
+        assert L.magb200_launch_count() == 1, "the group did not run as one launch"
+        mb.synchronize(gpu)
+        for o, wnt in zip(outs, want):
+            assert np.array_equal(o.to_bits(), wnt)
+        for t in ws + outs:
+            t.release()
+    # prefill-shaped: falls back to one matmul per product
+    xb2 = bits(dt, rng, (64, 256), 1.0)
+    tx2 = mb.Tensor.from_bits(gpu, dt, xb2)
+    ws = [mb.Tensor.from_bits(gpu, dt, bits(dt, rng, (N, 256), 0.05)) for N in (128, 64)]
+    want = [(tx2 @ w.T).to_bits() for w in ws]
+    outs = [mb.Tensor(gpu, dt, (64, N)) for N in (128, 64)]
+    yv = [w.T.view_struct() for w in ws]
+    rv = [o.view_struct() for o in outs]
+    mb.check(L.magb200_matmul_grouped(gpu, C.byref(tx2.view_struct()), 2, (C.POINTER(mb.View) * 2)(*[C.pointer(v) for v in yv]),
+                                      (C.POINTER(mb.View) * 2)(*[C.pointer(v) for v in rv])))
+    for o, wnt in zip(outs, want):
+        assert np.array_equal(o.to_bits(), wnt)
+    for t in ws + outs + [tx, tx2]:
+        t.release()
+
+
 def test_fresh_result_as_weight_operand_in_a_decode_chain(gpu):
     """k = x @ Wk.T followed at once by s = q @ k.T on the same stream, many times with changing x and no
     synchronisation in between. The decode kernels let their successors start early and fetch weights ahead of their

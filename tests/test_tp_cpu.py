@@ -64,15 +64,11 @@ def _rank_main(rank, world, port, ret):
                 out[s.name] = torch.cat(parts, dim=1)
             else:
                 out[s.name] = layer.y[s.name].clone()
-        # gather every rank's input slice so rank 0 can form the unsharded product
-        xs = {}
+        # the unsharded activation, rebuilt on its own from the block seeds: every rank must have taken ITS K slice of it
+        xs = {s.name: torch.cat([tp.activation_block(m, s.granule, 5, s.name, j) for j in range(s.k // s.granule)], dim=1) for s in SMALL}
         for s in SMALL:
-            if s.kind == "row":
-                parts = [torch.empty_like(layer.x[s.name]) for _ in range(world)]
-                dist.all_gather(parts, layer.x[s.name])
-                xs[s.name] = torch.cat(parts, dim=1)
-            else:
-                xs[s.name] = layer.x[s.name]
+            lo, hi = tp.shard_range(s.k, world, rank, s.granule) if s.kind == "row" else (0, s.k)
+            assert torch.equal(layer.x[s.name], xs[s.name][:, lo:hi]), s.name
         if rank == 0:
             gen = torch.Generator(device="cpu").manual_seed(5)
             ok = True
@@ -98,3 +94,25 @@ def test_two_gloo_ranks_reproduce_the_unsharded_layer():
         p.join(120)
         assert p.exitcode == 0
     assert ret.get(timeout=5) is True
+
+
+def test_planner_decisions():
+    """magb200_tp_plan: column shards never exchange; a row-sharded linear at prefill size takes a fused exchange (through the
+    switch when the buffers have a multicast binding) and pays; at one token its all-reduce eats the gain, so it is marked as
+    not paying, and an operator that sharding would slow down is kept whole."""
+    qkv, o, gate_up, down = tp.QWEN3_32B_LAYER
+    big = tp.plan_linear(down, 8192, 8, peer_access=True, multicast=True)
+    assert big["mode"] == "row" and big["exchange"] == "switch" and big["pays"] and big["chunks"] == 2
+    assert tp.plan_linear(down, 8192, 8, peer_access=True, multicast=False)["exchange"] == "scatter"
+    assert tp.plan_linear(down, 8192, 2, peer_access=True, multicast=True)["exchange"] == "scatter"
+    assert tp.plan_linear(down, 8192, 8, peer_access=False, multicast=False)["exchange"] == "nccl"
+    col = tp.plan_linear(gate_up, 1, 8, peer_access=True, multicast=True)
+    assert col["mode"] == "column" and col["exchange"] == "none" and col["pays"]
+    tiny = tp.plan_linear(o, 1, 8, peer_access=True, multicast=True)
+    assert tiny["exchange"] in ("nccl", "none") and not tiny["pays"]
+    assert tp.plan_linear(o, 1, 2, peer_access=True, multicast=True)["mode"] == "replicate"
+    for m in (1, 8, 512, 8192):
+        for p in (2, 4, 8):
+            for spec in tp.QWEN3_32B_LAYER:
+                pl = tp.plan_linear(spec, m, p, peer_access=True, multicast=True)
+                assert pl["sharded_us"] <= pl["single_us"] * 1.0001 and 1 <= pl["chunks"] <= 4
