@@ -238,7 +238,8 @@ int  magb200_multimem_reduce_broadcast(int device, void *cuda_stream, const void
  * to a 4 MiB array built into the library (held by every GPU that loads it): problems whose partials
  * (splits x batch x M x N floats) exceed it fail with MAGB200_ERR_TOO_LARGE. The first call on a device
  * resolves the array's address and should be made before any stream capture. All calls share the array;
- * calls whose kernels overlap on the GPU race, so keep them on one stream. */
+ * calls whose kernels overlap on the GPU race, so keep them on one stream. The call leaves `device` as the
+ * calling thread's current CUDA device; a device that is absent or not sm_100 gives MAGB200_ERR_NO_DEVICE. */
 int  magb200_matmul_skinny_noalloc(int device, void *cuda_stream, const magb200_view_t *x, const magb200_view_t *y,
                                    const magb200_view_t *r);
 

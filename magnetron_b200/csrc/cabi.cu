@@ -447,13 +447,46 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
     }
 }
 
+extern "C" int magb200_malloc(int device, void **out, size_t bytes);
+extern "C" int magb200_free(int device, void *ptr);
+
+// A 16-bit problem that fell to the FFMA kernel only because TMA cannot describe an operand (a row pitch that is not a
+// multiple of 16 bytes -- any odd K --, an inner stride of 2, a misaligned slice): copy the offending operand(s) into pooled
+// scratch with a legal pitch and run the tensor-core kernel on the copy. The reference packs every operand on every call
+// (magnetron/cpu/mag_cpu_impl_ops_matmul.inl:1257-2308); here it is the exception. Returns 1 when the detour does not apply.
+static int run_packed(DeviceState &d, int device, const GemmProblem &g) {
+    if (g.dtype == MAGB200_F32 || g.M <= 8 || (double)g.M * (double)g.N * (double)g.K * (double)g.batch_total < (double)(1 << 24)) return 1;
+    const bool pack_a = !tcgen05_operand_ok(g, true), pack_b = !tcgen05_operand_ok(g, false);
+    if (!pack_a && !pack_b) return 1;
+    if (d.capturing) return 1;                     // the scratch comes from the pool: not while a graph is being recorded
+    GemmProblem gp = g;
+    void *ta = nullptr, *tb = nullptr;
+    int rc = MAGB200_OK;
+    if (pack_a && !(rc = magb200_malloc(device, &ta, packed_operand_bytes(g, true)))) rc = launch_pack_operand(gp, true, ta, d.stream);
+    if (!rc && pack_b && !(rc = magb200_malloc(device, &tb, packed_operand_bytes(g, false)))) rc = launch_pack_operand(gp, false, tb, d.stream);
+    if (!rc) {
+        if (!tcgen05_supported(gp)) rc = 1;        // something else is in the way (e.g. a misaligned result): the FFMA kernel takes it
+        else rc = run_one(d, device, gp, tcgen05_2sm_preferred(gp) ? MAGB200_KERNEL_TCGEN05_2SM : MAGB200_KERNEL_TCGEN05);
+    }
+    // back to the pool at once: the next owner of the blocks is ordered after this launch on the same stream
+    if (ta) magb200_free(device, ta);
+    if (tb) magb200_free(device, tb);
+    return rc;
+}
+
 static int matmul_device(DeviceState &d, int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r) {
     FullProblem fp;
     int rc = build_problem(x, y, r, fp);
     if (rc) return rc;
     int kernel = 0;
     if ((rc = route(fp.g, g_force.load(), &kernel))) return rc;
-    if (fp.n_outer == 0) return run_one(d, device, fp.g, kernel);
+    if (fp.n_outer == 0) {
+        if (kernel == MAGB200_KERNEL_SIMT && g_force.load() == 0) {
+            rc = run_packed(d, device, fp.g);
+            if (rc <= 0) return rc;
+        }
+        return run_one(d, device, fp.g, kernel);
+    }
     // more than three independent batch dims survive merging: walk the outer ones on the host
     int64_t outer_total = 1;
     for (int i = 0; i < fp.n_outer; ++i) outer_total *= fp.oshape[i];

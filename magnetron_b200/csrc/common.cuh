@@ -163,5 +163,9 @@ int launch_multimem_reduce_broadcast(int dtype, const void *mc_partial, void *mc
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
                 const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);
 int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream);
+// device-side repack of a 16-bit operand that TMA cannot describe (see cast.cu)
+bool tcgen05_operand_ok(const GemmProblem &p, bool is_a);
+size_t packed_operand_bytes(const GemmProblem &p, bool is_a);
+int launch_pack_operand(GemmProblem &p, bool is_a, void *dst, cudaStream_t stream);
 
 }  // namespace magb200

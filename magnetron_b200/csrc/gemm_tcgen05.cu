@@ -1181,6 +1181,12 @@ bool tcgen05_supported(const GemmProblem &p) {
 }
 
 
+bool tcgen05_operand_ok(const GemmProblem &p, bool is_a) {
+    OperandDesc o;
+    int mn;
+    return describe(p, is_a, 128, o, mn);
+}
+
 // The two-SM kernel pays when the output has at least one full wave of 256 x 256 tiles for the 74 CTA pairs; smaller
 // problems keep the one-CTA kernel with its narrower tiles (measured: 4096 x 1024 x 4096, 64 tiles, is 12 % faster there).
 bool tcgen05_2sm_supported(const GemmProblem &p) {

@@ -16,9 +16,12 @@
 //   * all calls share the one array and it keeps whatever the previous call left. Nothing in it has to start
 //     at zero: each call's first kernel writes every partial sum that its second kernel reads. Two calls
 //     whose kernels overlap on the GPU (different streams, or different host threads) race on the array;
-//     keep calls on one stream or order them yourself.
+//     keep calls on one stream or order them yourself;
+//   * the call makes `device` the calling thread's current CUDA device and leaves it so; a NULL stream means the legacy
+//     default stream here (the library's own per-device stream is used only by the entry points that own one).
 #include "common.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace magb200 {
@@ -35,20 +38,33 @@ constexpr size_t kNoAllocScratchFloats = 1u << 20;  // 4 MiB of fp32 partial sum
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 
 constexpr int kMaxDev = 16;
-float *g_scratch_ptr[kMaxDev] = {nullptr};
+std::atomic<float *> g_scratch_ptr[kMaxDev];
 std::mutex g_setup_mu;
 
+// Makes `device` current (the launch below needs that anyway) and returns the array's address there. Only the first call on
+// a device takes the lock and asks the runtime; later calls read the cached address.
 int scratch_address(int device, float **out) {
     if (device < 0 || device >= kMaxDev) { set_error("device %d out of range", device); return MAGB200_ERR_INVALID_ARG; }
-    std::lock_guard<std::mutex> lock(g_setup_mu);
-    MAGB200_CUDA_TRY(cudaSetDevice(device));  // the symbol has one instance per device; ask for this device's
-    if (!g_scratch_ptr[device]) {
-        float *ptr = nullptr;
-        MAGB200_CUDA_TRY(cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch));
-        if (!ptr) { set_error("cudaGetSymbolAddress returned a null address for the built-in scratch array"); return MAGB200_ERR_CUDA; }
-        g_scratch_ptr[device] = ptr;
+    if (cudaSetDevice(device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error("no CUDA device %d: this library has no CPU fallback", device);
+        return MAGB200_ERR_NO_DEVICE;
     }
-    *out = g_scratch_ptr[device];
+    float *ptr = g_scratch_ptr[device].load(std::memory_order_acquire);
+    if (!ptr) {
+        std::lock_guard<std::mutex> lock(g_setup_mu);
+        ptr = g_scratch_ptr[device].load(std::memory_order_relaxed);
+        if (!ptr) {
+            cudaDeviceProp prop;
+            MAGB200_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+            if (prop.major != 10) { set_error("device %d (%s) is sm_%d%d; the kernels are built for sm_100a only", device, prop.name, prop.major, prop.minor); return MAGB200_ERR_NO_DEVICE; }
+            // the symbol has one instance per device; with `device` current this is that device's
+            MAGB200_CUDA_TRY(cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch));
+            if (!ptr) { set_error("cudaGetSymbolAddress returned a null address for the built-in scratch array"); return MAGB200_ERR_CUDA; }
+            g_scratch_ptr[device].store(ptr, std::memory_order_release);
+        }
+    }
+    *out = ptr;
     return MAGB200_OK;
 }
 

@@ -116,6 +116,36 @@ def test_grouped_decode_matches_separate_calls(gpu, M, dname):
         t.release()
 
 
+PACK_CASES = [
+    # name, x storage, x view recipe, w storage, w view recipe (applied before .T)
+    ("odd_k", (640, 1001), [], (512, 1001), []),                                        # row pitch 2002 bytes: both operands are packed
+    ("inner_stride_2", (640, 2048), [("slice", 1, 0, 1024, 2)], (512, 1024), []),       # x[:, ::2]: only x is packed
+    ("misaligned_slice", (640, 1032), [("slice", 1, 3, 1024, 1)], (512, 1024), []),     # x[:, 3:1027]: base 6 bytes off a 16-byte boundary
+    ("batched_broadcast_w", (3, 300, 1001), [], (520, 1001), []),                       # batch folds into M = 900
+]
+
+
+@pytest.mark.parametrize("name,xs,xops,ws,wops", PACK_CASES)
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_operands_tma_cannot_describe_are_packed_on_the_device(gpu, name, xs, xops, ws, wops, dname):
+    """16-bit operands with an odd row pitch, an inner stride of 2 or a misaligned base cannot be read by TMA. Large enough
+    problems are repacked on the device and still run on the tensor cores instead of the FFMA kernel."""
+    dt = cases.DTYPES[dname]
+    rng = np.random.default_rng(29)
+    xb, wb = bits(dt, rng, xs, 1.0), bits(dt, rng, ws, 0.1)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    vx, vw = cases.apply_ops(tx, xops), cases.apply_ops(tw, wops)
+    r = vx @ vw.T
+    assert mb.last_kernel().startswith("tcgen05"), mb.last_kernel()
+    xf = cases.apply_ops(cases.NpView(O.bits_to_f64(dt, xb)), xops).a
+    wf = cases.apply_ops(cases.NpView(O.bits_to_f64(dt, wb)), wops).a
+    truth = xf @ wf.T
+    m = O.error_metrics(dt, r.to_bits(), truth, np.abs(xf) @ np.abs(wf).T)
+    assert m["e"] <= unit_roundoff(dt) + xf.shape[-1] * 2.0 ** -24, m
+    for t in (r, tx, tw):
+        t.release()
+
+
 def test_fresh_result_as_weight_operand_in_a_decode_chain(gpu):
     """k = x @ Wk.T followed at once by s = q @ k.T on the same stream, many times with changing x and no
     synchronisation in between. The decode kernels let their successors start early and fetch weights ahead of their
