@@ -117,6 +117,15 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
+// Bulk tensor store shared -> global (the epilogue's write-out): the box is clipped at the tensor's edges, so tails in M and N
+// need no predicates. Completion is tracked by the issuing thread's bulk async-groups.
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -561,15 +570,20 @@ __device__ __forceinline__ void tcgen05_mma_f16_2sm_split(uint32_t tmem_d, uint3
 // kShare: this launch shares its last wave out (see WorkUnit). A separate instantiation, because the sharing paths cost the
 // epilogue of every tile about 15 % on short-K shapes even when they are never taken (registers and scheduling of the
 // drain loop: measured on Q.K^T with K = 128, 0.66 ms against 0.56 ms).
-template <int DT, int KSUB, bool kShare>
+// kTmaStore: the staged 32 x 64 patches leave through cp.async.bulk.tensor stores (one instruction per patch instead of
+// eight shared loads and eight predicated 16-byte global stores per lane); used whenever the result is a plain local
+// tensor TMA can describe. The scatter epilogue (peer stores) and the shared last wave keep the per-lane write-out.
+template <int DT, int KSUB, bool kShare, bool kTmaStore>
 __global__ void __launch_bounds__(kThreads2, 1)
-gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
+gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, const TcArgs args) {
     using C = Cfg2<KSUB>;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
     unsigned char *tiles_ptr = smem_raw + (tiles - raw);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles_ptr + (size_t)C::kStages * C::kStageBytes);
+    // layout: [stages][epilogue patches, 4 KB per warp, 1024-byte aligned as the 128-byte swizzle wants][barriers]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles_ptr + (size_t)C::kStages * C::kStageBytes + (size_t)C::kEpiWarps * C::kEpiWarpBytes);
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * C::kStages;
     const uint32_t tfull0 = empty0 + 8u * C::kStages;
@@ -775,7 +789,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
                 // kept at chunk c ^ (row & 7), conflict-free both ways), then 8 lanes write one row's 128 contiguous bytes, so
                 // global and peer stores are whole 128-byte segments. The next TMEM loads are issued before the write-out.
-                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + 256 + (size_t)(warp - 2) * C::kEpiWarpBytes;
+                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + (size_t)(warp - 2) * C::kEpiWarpBytes;
                 const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
                 const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * (BN2 / 2);
                 uint32_t ra[32], rb[32];
@@ -784,6 +798,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN2 / 2; c0 += C::kEpiCols) {
                     tmem_ld_wait();
+                    if constexpr (kTmaStore) {          // the previous bulk store has read the patch before it is overwritten
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    }
                     for (int j = 1; kShare && j < w.parts; ++j) {      // contributions in run order: the sum does not depend on timing
                         const float *pj = contrib + (size_t)(j - 1) * (size_t)(2 * BM * BN2) + (size_t)c0 * 32 + lane;
 #pragma unroll
@@ -816,6 +834,14 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         __syncwarp();
                         if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
                     }
+                    if constexpr (kTmaStore) {
+                        // the patch is laid out exactly as a 128-byte-swizzled 64 x 32 box: make the writes visible to the async
+                        // proxy, then one lane stores the whole patch; rows beyond M and columns beyond N are clipped by TMA
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0 && row0 < args.M && n0 + chalf * (BN2 / 2) + c0 < args.N)
+                            tma_store_5d(&tmC, smem_u32(stg), (int)(n0 + chalf * (BN2 / 2) + c0), (int)row0, (int)batch, 0, 0);
+                    } else {
                     __syncwarp();
                     const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 7) * 8;
 #pragma unroll
@@ -828,6 +854,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         }
                     }
                     __syncwarp();
+                    }
                 }
             } else {
             uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0;
@@ -861,6 +888,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     args.sk_counters[2 * w.tail_idx + 1] = 0;
                 }
             }
+        }
+        if constexpr (kTmaStore) {      // the shared-memory patches must outlive the bulk stores that read them
+            if (lane == 0) tma_store_wait_all();
         }
     }
 
@@ -1128,18 +1158,19 @@ void plan_tail(TcArgs &args, int64_t pairs, const SplitWorkspace *ws, int ksub) 
     args.sk_counters = ws->counters;
 }
 
-template <int DT, int KSUB, bool kShare>
-int launch_2sm_kernel(const CUtensorMap &ta, const CUtensorMap &tb, const TcArgs &args, const cudaLaunchConfig_t &cfg) {
-    auto kernel = gemm_tcgen05_2sm_kernel<DT, KSUB, kShare>;
+template <int DT, int KSUB, bool kShare, bool kTmaStore>
+int launch_2sm_kernel(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcArgs &args, const cudaLaunchConfig_t &cfg) {
+    auto kernel = gemm_tcgen05_2sm_kernel<DT, KSUB, kShare, kTmaStore>;
     static std::atomic<uint32_t> optin{0};
     if (int rc = ensure_smem_optin(kernel, Cfg2<KSUB>::kSmemBytes, optin)) return rc;
-    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, args));
     return MAGB200_OK;
 }
 
+// `tc`: tensor map of the result for the bulk-store epilogue, or null when the result cannot leave that way
 template <int DT, int KSUB>
-int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st, int cta_limit,
-               const SplitWorkspace *ws) {
+int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap *tc, TcArgs &args, cudaStream_t st,
+               int cta_limit, const SplitWorkspace *ws) {
     fill_knobs(args);
     args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
     args.tiles_n = (p.N + BN2 - 1) / BN2;
@@ -1158,7 +1189,10 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const int rc = args.tail_slots > 0 ? launch_2sm_kernel<DT, KSUB, true>(ta, tb, args, cfg) : launch_2sm_kernel<DT, KSUB, false>(ta, tb, args, cfg);
+    int rc;
+    if (args.tail_slots > 0) rc = launch_2sm_kernel<DT, KSUB, true, false>(ta, tb, ta, args, cfg);
+    else if (tc) rc = launch_2sm_kernel<DT, KSUB, false, true>(ta, tb, *tc, args, cfg);
+    else rc = launch_2sm_kernel<DT, KSUB, false, false>(ta, tb, ta, args, cfg);
     if (rc) return rc;
     count_launch();
     return MAGB200_OK;
@@ -1225,8 +1259,20 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
         args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
         for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
     }
-    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16, 2>(p, ta, tb, args, st, cta_limit, ws)
-                                   : launch_2sm<MAGB200_F16, 2>(p, ta, tb, args, st, cta_limit, ws);
+    // the result as TMA sees it: [batch][M][N] contiguous -> boxes of 64 columns x 32 rows for the epilogue's bulk stores
+    CUtensorMap tcm;
+    const CUtensorMap *tc = nullptr;
+    if (!scatter && p.N % 8 == 0) {
+        OperandDesc c;
+        memset(&c, 0, sizeof(c));
+        c.base = p.C; c.inner_extent = p.N; c.outer_extent = p.M; c.outer_pitch = p.N;
+        c.box_inner = 64; c.box_outer = 32;
+        for (int d = 0; d < kMaxBatchDims; ++d) { c.bext[d] = 1; c.bstride[d] = 0; c.has[d] = 0; }
+        if (p.batch_total > 1) { c.bext[kMaxBatchDims - 1] = p.batch_total; c.bstride[kMaxBatchDims - 1] = p.M * p.N; c.has[kMaxBatchDims - 1] = 1; }
+        if (operand_ok(c) && encode(c, p.dtype, &tcm) == MAGB200_OK) tc = &tcm;
+    }
+    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16, 2>(p, ta, tb, tc, args, st, cta_limit, ws)
+                                   : launch_2sm<MAGB200_F16, 2>(p, ta, tb, tc, args, st, cta_limit, ws);
 }
 
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
