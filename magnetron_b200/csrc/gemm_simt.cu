@@ -7,34 +7,44 @@
 // multiple of 16 bytes, a misaligned base). Operands are gathered through their strides straight into
 // shared memory as fp32, so no packed copy of a strided view is ever made in HBM.
 //
-// Tile: 128x128x16 per 512-thread CTA, 8x4 accumulators per thread. A warp covers 4 row groups x 8
-// column groups, so its shared-memory reads are three 128-bit wavefronts per K step. The next K tile
-// is fetched from global memory into registers while the current one is multiplied, and shared memory
-// is double buffered: one barrier per K tile.
+// Tile: 128x128x16 per 256-thread CTA, 8x8 accumulators per thread (two 4-wide groups of rows and of
+// columns, 64 apart): four 128-bit shared-memory reads feed 64 FMAs. A warp covers 4 row groups x 8
+// column groups, so its reads are broadcasts or one contiguous 128-byte line. The next K tile is fetched
+// from global memory into registers while the current one is multiplied, and shared memory is double
+// buffered: one barrier per K tile. One CTA per SM owns the whole register file (up to 255 per thread).
 //
 // fp32 accuracy: a single fp32 accumulator that walks the whole K loses several units in the last place
 // at K in the thousands, more than the reference's blocked CPU kernel does. For float32 the kernel
-// therefore sums 32 products at a time in a fresh accumulator and folds it into the running total with an
-// error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 32-term
-// group. The 16-bit dtypes skip this: their error is set by the final rounding of the result.
+// therefore sums 64 products at a time in a fresh accumulator and folds it into the running total with an
+// error-free TwoSum, carrying the lost low part along; what remains is the rounding inside one 64-term
+// group. The running totals stay in registers; the low parts, touched only once per fold, live in shared
+// memory (64 KB), which is what keeps the kernel free of register spills. The 16-bit dtypes skip all of
+// this: their error is set by the final rounding of the result.
 //
 // Few tiles (an output smaller than the GPU): K is split over several CTAs per tile; each writes its
 // (total, low) pair as fp32 and a second kernel adds the pairs in split order, again with TwoSum, and
 // rounds once.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace magb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 16, THREADS = 512, PAD = 4;
-constexpr int kLoads = (BM * BK) / THREADS;   // elements of each operand tile a thread fetches: 4
+constexpr int BM = 128, BN = 128, BK = 16, THREADS = 256, PAD = 4;
+constexpr int kLoads = (BM * BK) / THREADS;   // elements of each operand tile a thread fetches: 8
+constexpr int kFoldTiles = 4;                 // float32: K tiles summed in one fresh accumulator between folds (64 products)
+constexpr size_t kTileBytes = 2 * (size_t)BK * (BM + PAD) * sizeof(float);   // one operand, both buffers
+constexpr size_t kLowBytes = (size_t)64 * THREADS * sizeof(float);           // low parts of the compensated totals
+template <int DT> constexpr size_t simt_smem_bytes() { return 2 * kTileBytes + (DT == MAGB200_F32 ? kLowBytes : 0); }
 
-// s + e == a + b exactly
+// s + e == a + b exactly (s may alias a)
 __device__ __forceinline__ void two_sum(float a, float b, float &s, float &e) {
-    s = __fadd_rn(a, b);
-    const float bp = __fsub_rn(s, a);
-    e = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bp)), __fsub_rn(b, bp));
+    const float sum = __fadd_rn(a, b);
+    const float bp = __fsub_rn(sum, a);
+    e = __fadd_rn(__fsub_rn(a, __fsub_rn(sum, bp)), __fsub_rn(b, bp));
+    s = sum;
 }
 
 // total + low, except that an infinite total stays infinite: TwoSum of an infinity leaves NaN in the low part
@@ -48,8 +58,11 @@ __device__ __forceinline__ float fold_low(float total, float low) {
 template <int DT, bool AKF, bool BNF>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial) {
-    __shared__ __align__(16) float As[2][BK][BM + PAD];
-    __shared__ __align__(16) float Bs[2][BK][BN + PAD];
+    extern __shared__ __align__(16) unsigned char simt_smem[];
+    typedef float Tile[BK][BM + PAD];
+    Tile *As = reinterpret_cast<Tile *>(simt_smem);                   // As[2][BK][BM + PAD]
+    Tile *Bs = reinterpret_cast<Tile *>(simt_smem + kTileBytes);      // Bs[2][BK][BN + PAD]
+    float4 *low_s = reinterpret_cast<float4 *>(simt_smem + 2 * kTileBytes) + threadIdx.x;   // slot g of this thread: low_s[g * THREADS]
 
     const int64_t tiles_per_batch = tiles_m * tiles_n;
     const int64_t tiles_total = tiles_per_batch * p.batch_total;
@@ -76,8 +89,8 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
     }
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
-    const int tx = (warp & 3) * 8 + (lane & 7);    // column group: columns tx*4 .. tx*4+3
-    const int ty = (warp >> 2) * 4 + (lane >> 3);  // row group: rows ty*4 .. +3 and 64 + ty*4 .. +3
+    const int tx = (warp & 1) * 8 + (lane & 7);    // column group: columns tx*4 .. +3 and 64 + tx*4 .. +3
+    const int ty = (warp >> 1) * 4 + (lane >> 3);  // row group: rows ty*4 .. +3 and 64 + ty*4 .. +3
 
     // ---- what this thread fetches of every K tile: kLoads elements of A and of B. One coordinate is fixed per thread,
     // the other advances by a constant, so the elements sit at pointer + i * step, a K tile later adds BK * stride, and
@@ -128,18 +141,22 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
     };
 
     constexpr bool kCompensated = (DT == MAGB200_F32);
-    float acc[8][4];                                   // sum of the current K tile (fp32) or of all of K (16-bit)
-    float total[kCompensated ? 8 : 1][4], low[kCompensated ? 8 : 1][4];  // running total and its lost low part
+    float acc[8][8];                                   // sum of the current group of K tiles (fp32) or of all of K (16-bit)
+    float total[kCompensated ? 8 : 1][8];              // fp32: running totals; their lost low parts sit in low_s
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
             acc[i][j] = 0.f;
-            if constexpr (kCompensated) { total[i][j] = 0.f; low[i][j] = 0.f; }
+            if constexpr (kCompensated) total[i][j] = 0.f;
         }
+    if constexpr (kCompensated) {
+#pragma unroll
+        for (int g = 0; g < 16; ++g) low_s[g * THREADS] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 
     int buf = 0;
-    bool fold = false;                                 // fp32: fold after every second K tile (32 products per fresh accumulator)
+    int since_fold = 0;
     if (kbeg < kend) {
         fetch(kbeg, true);
         stash(0);
@@ -150,31 +167,41 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
         if (more) fetch(k0 + BK, k0 + 2 * BK > kend);   // global loads in flight under the multiply below
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
-            float a[8], b[4];
+            float a[8], b[8];
             *reinterpret_cast<float4 *>(&a[0]) = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4]);
             *reinterpret_cast<float4 *>(&a[4]) = *reinterpret_cast<const float4 *>(&As[buf][kk][64 + ty * 4]);
             *reinterpret_cast<float4 *>(&b[0]) = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]);
+            *reinterpret_cast<float4 *>(&b[4]) = *reinterpret_cast<const float4 *>(&Bs[buf][kk][64 + tx * 4]);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
-        if (kCompensated && (fold || !more)) {
+        if constexpr (kCompensated) {
+            if (++since_fold == kFoldTiles || !more) {
+                since_fold = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float s, e;
-                    two_sum(total[i][j], acc[i][j], s, e);
-                    total[i][j] = s;
-                    low[i][j] = __fadd_rn(low[i][j], e);
-                    acc[i][j] = 0.f;
-                }
+                    for (int h = 0; h < 2; ++h) {
+                        float4 lo = low_s[(i * 2 + h) * THREADS];
+                        float e0, e1, e2, e3;
+                        two_sum(total[i][h * 4 + 0], acc[i][h * 4 + 0], total[i][h * 4 + 0], e0);
+                        two_sum(total[i][h * 4 + 1], acc[i][h * 4 + 1], total[i][h * 4 + 1], e1);
+                        two_sum(total[i][h * 4 + 2], acc[i][h * 4 + 2], total[i][h * 4 + 2], e2);
+                        two_sum(total[i][h * 4 + 3], acc[i][h * 4 + 3], total[i][h * 4 + 3], e3);
+                        lo.x = __fadd_rn(lo.x, e0);
+                        lo.y = __fadd_rn(lo.y, e1);
+                        lo.z = __fadd_rn(lo.z, e2);
+                        lo.w = __fadd_rn(lo.w, e3);
+                        low_s[(i * 2 + h) * THREADS] = lo;
+                        acc[i][h * 4 + 0] = acc[i][h * 4 + 1] = acc[i][h * 4 + 2] = acc[i][h * 4 + 3] = 0.f;
+                    }
+            }
         }
         if (more) stash(buf ^ 1);                      // the other buffer: nobody reads it during this tile
         __syncthreads();
         buf ^= 1;
-        fold = !fold;
     }
 
     // ---- epilogue: row-major C with ldc = N; one rounding to the result dtype, or the (total, low) pair of this K split
@@ -186,19 +213,23 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
         const int64_t gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
         if (gm >= p.M) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t gn = n0 + tx * 4 + j;
-            if (gn >= p.N) continue;
-            const int64_t idx = cbase + gm * p.N + gn;
-            if (nsplit == 1) {
-                float v = acc[i][j];
-                if constexpr (kCompensated) v = fold_low(total[i][j], low[i][j]);
-                store_from_f32<DT>(C, idx, v);
-            } else {
-                float hi = acc[i][j], lo = 0.f;
-                if constexpr (kCompensated) { hi = total[i][j]; lo = low[i][j]; }
-                partial[((int64_t)split * 2 + 0) * elems + idx] = hi;
-                partial[((int64_t)split * 2 + 1) * elems + idx] = lo;
+        for (int h = 0; h < 2; ++h) {
+            float lo4[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (kCompensated) *reinterpret_cast<float4 *>(lo4) = low_s[(i * 2 + h) * THREADS];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int j = h * 4 + jj;
+                const int64_t gn = n0 + h * 64 + tx * 4 + jj;
+                if (gn >= p.N) continue;
+                const int64_t idx = cbase + gm * p.N + gn;
+                float hi = acc[i][j];
+                if constexpr (kCompensated) hi = total[i][j];
+                if (nsplit == 1) {
+                    store_from_f32<DT>(C, idx, kCompensated ? fold_low(hi, lo4[jj]) : hi);
+                } else {
+                    partial[((int64_t)split * 2 + 0) * elems + idx] = hi;
+                    partial[((int64_t)split * 2 + 1) * elems + idx] = lo4[jj];
+                }
             }
         }
     }
@@ -218,6 +249,20 @@ __global__ void __launch_bounds__(256) simt_finalize_kernel(const float *__restr
         }
         store_from_f32<DT>(C, i, fold_low(total, low));
     }
+}
+
+// More than 48 KB of dynamic shared memory needs an opt-in per (kernel, device): bit d of `done` is set once device d has it.
+template <typename K>
+int simt_smem_optin(K kernel, size_t bytes, std::atomic<uint32_t> &done) {
+    if (bytes <= 48 * 1024) return MAGB200_OK;
+    int dev = 0;
+    MAGB200_CUDA_TRY(cudaGetDevice(&dev));
+    const uint32_t bit = 1u << (dev & 31);
+    if (!(done.load(std::memory_order_acquire) & bit)) {
+        MAGB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        done.fetch_or(bit, std::memory_order_release);
+    }
+    return MAGB200_OK;
 }
 
 struct SimtPlan { int64_t tiles_m, tiles_n, tiles; int nsplit; int64_t kchunk; };
@@ -267,8 +312,13 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
     if (fin_blocks > num_sms() * 8) fin_blocks = num_sms() * 8;
     const bool akf = (p.sAk == 1) || (p.sAm != 1);   // walk k fastest unless m is the unit-stride dim
     const bool bnf = (p.sBn == 1) || (p.sBk != 1);
-#define MAGB200_SIMT_GO(DT, AKF, BNF) \
-    gemm_simt_kernel<DT, AKF, BNF><<<(unsigned)grid, THREADS, 0, stream>>>(p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch)
+#define MAGB200_SIMT_GO(DT, AKF, BNF)                                                                        \
+    do {                                                                                                     \
+        static std::atomic<uint32_t> optin{0};                                                               \
+        if (int rc = simt_smem_optin(gemm_simt_kernel<DT, AKF, BNF>, simt_smem_bytes<DT>(), optin)) return rc; \
+        gemm_simt_kernel<DT, AKF, BNF><<<(unsigned)grid, THREADS, simt_smem_bytes<DT>(), stream>>>(          \
+            p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch);                                       \
+    } while (0)
 #define MAGB200_SIMT_LAUNCH(DT)                                                                              \
     if (akf) { if (bnf) MAGB200_SIMT_GO(DT, true, true); else MAGB200_SIMT_GO(DT, true, false); }            \
     else     { if (bnf) MAGB200_SIMT_GO(DT, false, true); else MAGB200_SIMT_GO(DT, false, false); }          \
