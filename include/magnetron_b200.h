@@ -63,7 +63,9 @@ typedef enum magb200_kernel_t {
     MAGB200_KERNEL_SKINNY   = 2,  /* M <= 8 weight-streaming kernel (HBM bound)                          */
     MAGB200_KERNEL_SIMT     = 3,  /* exact-fp32 / arbitrary-stride tiled FFMA kernel                     */
     MAGB200_KERNEL_SKINNY_SPLITK = 4, /* M <= 8, K split across CTAs with an fp32 scratch reduction      */
-    MAGB200_KERNEL_TCGEN05_2SM = 5   /* 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2)           */
+    MAGB200_KERNEL_TCGEN05_2SM = 5,  /* 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2)           */
+    MAGB200_KERNEL_TCGEN05_F32X3 = 6 /* float32 as three bf16 planes per operand: six tcgen05 MMAs per product,
+                                        per-K-block accumulators folded with compensated fp32 sums        */
 } magb200_kernel_t;
 
 /* ---- library / device ------------------------------------------------------------------------ */

@@ -22,7 +22,7 @@ FLOAT32, FLOAT16, BFLOAT16 = 0, 1, 2          # mag_dtype_t values (include/magn
 DTYPE_SIZE = {FLOAT32: 4, FLOAT16: 2, BFLOAT16: 2}
 BITS_DTYPE = {FLOAT32: np.uint32, FLOAT16: np.uint16, BFLOAT16: np.uint16}
 MAX_DIMS = 16
-KERNEL_NAMES = {0: "none", 1: "tcgen05", 2: "skinny", 3: "simt", 4: "skinny_splitk", 5: "tcgen05_2sm"}
+KERNEL_NAMES = {0: "none", 1: "tcgen05", 2: "skinny", 3: "simt", 4: "skinny_splitk", 5: "tcgen05_2sm", 6: "tcgen05_f32x3"}
 KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items()}
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
@@ -149,7 +149,7 @@ def synchronize(device: int = 0) -> None:
 
 
 def force_kernel(name: str | None) -> None:
-    """Pin matmul routing to one kernel ("tcgen05", "skinny", "simt") or restore automatic routing."""
+    """Pin matmul routing to one kernel ("tcgen05", "tcgen05_2sm", "tcgen05_f32x3", "skinny", "simt") or restore automatic routing."""
     check(lib().magb200_force_kernel(KERNEL_IDS[name] if name else 0))
 
 

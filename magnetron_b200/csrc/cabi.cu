@@ -74,6 +74,7 @@ static size_t size_class(size_t bytes) {
 // ---- per-device state ---------------------------------------------------------------------------
 constexpr int kMaxDevices = 16;
 constexpr size_t kStatusBytes = 4096;
+constexpr int kSplitFlagWord = 8;                          // "operands cannot be split" word of the float32 tensor-core path
 constexpr int kCounterWord0 = 64, kCounterTiles = 256;   // counters of the two-SM kernel's shared last wave live in the status buffer
 struct AddrRange { uintptr_t lo, hi; };
 struct DeviceState {
@@ -397,10 +398,17 @@ static int route(const GemmProblem &g, int forced, int *kernel) {
     const bool tc = tcgen05_supported(g);
     int k = sk ? MAGB200_KERNEL_SKINNY
                : (tc ? (tcgen05_2sm_preferred(g) ? MAGB200_KERNEL_TCGEN05_2SM : MAGB200_KERNEL_TCGEN05) : MAGB200_KERNEL_SIMT);
+    // float32: the split-operand tensor-core kernel once the product is large enough to carry its fixed cost (one pass that
+    // splits the operands, a stand-by launch of the FFMA kernel behind it)
+    const bool f3 = g.dtype == MAGB200_F32 && f32x3_supported(g);
+    if (k == MAGB200_KERNEL_SIMT && f3 && g.K >= 64 &&
+        (double)g.M * (double)g.N * (double)g.K * (double)g.batch_total >= (double)(1ll << 28))
+        k = MAGB200_KERNEL_TCGEN05_F32X3;
     if (forced) {
         if (forced == MAGB200_KERNEL_SKINNY_SPLITK) forced = MAGB200_KERNEL_SKINNY;
         const bool can = (forced == MAGB200_KERNEL_SKINNY && sk) || (forced == MAGB200_KERNEL_TCGEN05 && tc) ||
-                         (forced == MAGB200_KERNEL_TCGEN05_2SM && tcgen05_2sm_supported(g)) || forced == MAGB200_KERNEL_SIMT;
+                         (forced == MAGB200_KERNEL_TCGEN05_2SM && tcgen05_2sm_supported(g)) || forced == MAGB200_KERNEL_SIMT ||
+                         (forced == MAGB200_KERNEL_TCGEN05_F32X3 && f3);
         if (!can) {
             set_error("matmul: forced kernel %d cannot run this problem (M=%lld N=%lld K=%lld)", forced, (long long)g.M, (long long)g.N, (long long)g.K);
             return MAGB200_ERR_INVALID_ARG;
@@ -439,6 +447,26 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
             const SplitWorkspace ws = split_workspace(d);
             return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status, nullptr, &ws);
         }
+        case MAGB200_KERNEL_TCGEN05_F32X3: {
+            // planes of both operands in the workspace; the FFMA kernel stands by behind the tensor-core launch and runs
+            // instead of it when the split pass meets an element it cannot split (not finite, or out of bf16's normal range)
+            const size_t bytes_a = (plane_bytes(plane_layout(g, true)) + 255) & ~(size_t)255;
+            const size_t bytes_b = plane_bytes(plane_layout(g, false));
+            const bool fits = bytes_a + bytes_b <= ((size_t)8 << 30) && !(d.capturing && bytes_a + bytes_b > d.scratch_bytes);
+            if (fits && ensure_scratch(d, bytes_a + bytes_b) == MAGB200_OK) {
+                g_last_kernel = MAGB200_KERNEL_TCGEN05_F32X3;
+                ordered_point(d);
+                int *unsafe = d.status + kSplitFlagWord;
+                char *planes = reinterpret_cast<char *>(d.scratch);
+                MAGB200_CUDA_TRY(cudaMemsetAsync(unsafe, 0, sizeof(int), d.stream));
+                int rc = launch_split3(g, planes, planes + bytes_a, unsafe, d.stream);
+                if (!rc) rc = launch_gemm_f32x3(g, planes, planes + bytes_a, unsafe, d.status, d.stream);
+                if (!rc) rc = launch_gemm_simt(g, d.stream, nullptr, 0, unsafe);
+                return rc;
+            }
+            (void)cudaGetLastError();
+        }   // no room for the planes: the FFMA kernel takes the product
+        // fallthrough
         default:
             g_last_kernel = MAGB200_KERNEL_SIMT;
             if (int rc = ensure_scratch(d, simt_scratch_bytes(g))) return rc;
@@ -1037,7 +1065,7 @@ int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }
 int magb200_force_kernel(int kernel) {
-    if (kernel < 0 || kernel > MAGB200_KERNEL_TCGEN05_2SM) { set_error("force_kernel: unknown kernel %d", kernel); return MAGB200_ERR_INVALID_ARG; }
+    if (kernel < 0 || kernel > MAGB200_KERNEL_TCGEN05_F32X3) { set_error("force_kernel: unknown kernel %d", kernel); return MAGB200_ERR_INVALID_ARG; }
     g_force.store(kernel);
     return MAGB200_OK;
 }

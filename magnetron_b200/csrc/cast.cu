@@ -157,6 +157,98 @@ __global__ void __launch_bounds__(kThreads) pack_operand_kernel(const PackArgs a
     }
 }
 
+// ---- fp32 operand -> three bf16 planes (hi, mid, lo with hi + mid + lo == value to 24 bits) -------------------------------
+// Tiles of 32 rows x 64 K values go through shared memory, so the reads walk whichever source dim has the unit stride and
+// the writes always walk K (two values, four bytes, per lane). Both operands of a product are split by one launch.
+struct SplitOperand {
+    const float *src;
+    uint16_t *dst;
+    int64_t rows, K, kpad;
+    int64_t s_row, s_k;                  // source strides (elements)
+    int nbatch;
+    int64_t bshape[kMaxBatchDims], bsrc[kMaxBatchDims], bdst[kMaxBatchDims];   // packed batch extents (1 where broadcast) and strides
+    int64_t row_tiles, k_tiles, tiles;
+    int k_fast;                          // 1: read with threads along K, 0: along rows
+};
+struct SplitArgs {
+    SplitOperand op[2];
+    int *unsafe;
+};
+__device__ __forceinline__ void split3(float v, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
+    hi = f32_bits_to_bf16_bits(__float_as_uint(v));
+    const float r1 = __fsub_rn(v, __uint_as_float(hi << 16));          // exact: the difference fits in 24 bits
+    mid = f32_bits_to_bf16_bits(__float_as_uint(r1));
+    const float r2 = __fsub_rn(r1, __uint_as_float(mid << 16));
+    lo = f32_bits_to_bf16_bits(__float_as_uint(r2));
+}
+__device__ __forceinline__ bool unsafe_to_split(float v) {
+    const uint32_t a = __float_as_uint(v) & 0x7FFFFFFFu;
+    // not finite or rounds to a bf16 infinity; or non-zero below 2^-100, where the lower planes leave the normal range
+    return a >= 0x7F7F8000u || (a != 0u && a < (27u << 23));
+}
+__global__ void __launch_bounds__(kThreads) split3_kernel(const SplitArgs a) {
+    __shared__ float tile[32][65];
+    const int t = threadIdx.x;
+    bool bad = false;
+    const int64_t total = a.op[0].tiles + a.op[1].tiles;
+    for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
+        const SplitOperand &o = a.op[id >= a.op[0].tiles ? 1 : 0];
+        const int64_t local = id >= a.op[0].tiles ? id - a.op[0].tiles : id;
+        const int64_t kt = local % o.k_tiles;
+        int64_t rem = local / o.k_tiles;
+        const int64_t rt = rem % o.row_tiles;
+        rem /= o.row_tiles;
+        int64_t so = 0, dof = 0;
+        for (int d = o.nbatch - 1; d >= 0; --d) {
+            const int64_t q = rem / o.bshape[d], idx = rem - q * o.bshape[d];
+            so += idx * o.bsrc[d];
+            dof += idx * o.bdst[d];
+            rem = q;
+        }
+        const int64_t r0 = rt * 32, k0 = kt * 64;
+        if (o.k_fast) {
+            const int kx = t & 63, ry = t >> 6;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = ry + 4 * i;
+                float v = 0.f;
+                if (r0 + r < o.rows && k0 + kx < o.K) v = o.src[so + (r0 + r) * o.s_row + (k0 + kx) * o.s_k];
+                bad = bad || unsafe_to_split(v);
+                tile[r][kx] = v;
+            }
+        } else {
+            const int rx = t & 31, ky = t >> 5;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int k = ky + 8 * i;
+                float v = 0.f;
+                if (r0 + rx < o.rows && k0 + k < o.K) v = o.src[so + (r0 + rx) * o.s_row + (k0 + k) * o.s_k];
+                bad = bad || unsafe_to_split(v);
+                tile[rx][k] = v;
+            }
+        }
+        __syncthreads();
+        const int kp = (t & 31) * 2, ry = t >> 5;
+        if (k0 + kp < o.kpad) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = ry + 8 * i;
+                if (r0 + r >= o.rows) continue;
+                uint32_t h0, m0, l0, h1, m1, l1;
+                split3(tile[r][kp], h0, m0, l0);
+                split3(tile[r][kp + 1], h1, m1, l1);
+                uint16_t *q = o.dst + dof + (r0 + r) * o.kpad + k0 + kp;
+                const int64_t plane = o.rows * o.kpad;
+                *reinterpret_cast<uint32_t *>(q) = h0 | (h1 << 16);
+                *reinterpret_cast<uint32_t *>(q + plane) = m0 | (m1 << 16);
+                *reinterpret_cast<uint32_t *>(q + 2 * plane) = l0 | (l1 << 16);
+            }
+        }
+        __syncthreads();
+    }
+    if (bad) *a.unsafe = 1;
+}
+
 int grid_for(int64_t work_items) {
     int64_t blocks = (work_items + kThreads - 1) / kThreads;
     const int64_t cap = (int64_t)num_sms() * 16;  // 16 resident 256-thread blocks cover every SM several times
@@ -228,6 +320,40 @@ int launch_pack_operand(GemmProblem &p, bool is_a, void *dst, cudaStream_t strea
     MAGB200_CUDA_TRY(cudaGetLastError());
     if (is_a) { p.A = dst; p.sAm = a.kpad; p.sAk = 1; for (int d = 0; d < p.nbatch; ++d) p.bsA[d] = new_stride[d]; }
     else { p.B = dst; p.sBn = a.kpad; p.sBk = 1; for (int d = 0; d < p.nbatch; ++d) p.bsB[d] = new_stride[d]; }
+    return MAGB200_OK;
+}
+
+int launch_split3(const GemmProblem &p, void *planes_a, void *planes_b, int *unsafe, cudaStream_t stream) {
+    SplitArgs a;
+    memset(&a, 0, sizeof(a));
+    a.unsafe = unsafe;
+    for (int which = 0; which < 2; ++which) {
+        const bool is_a = which == 0;
+        SplitOperand &o = a.op[which];
+        const PlaneLayout l = plane_layout(p, is_a);
+        o.src = reinterpret_cast<const float *>(is_a ? p.A : p.B);
+        o.dst = reinterpret_cast<uint16_t *>(is_a ? planes_a : planes_b);
+        o.rows = l.rows; o.K = p.K; o.kpad = l.kpad;
+        o.s_row = is_a ? p.sAm : p.sBn; o.s_k = is_a ? p.sAk : p.sBk;
+        o.nbatch = p.nbatch;
+        for (int d = 0; d < p.nbatch; ++d) {
+            const int64_t st = is_a ? p.bsA[d] : p.bsB[d];
+            const bool kept = st != 0 && p.bshape[d] > 1;
+            o.bshape[d] = kept ? p.bshape[d] : 1;
+            o.bsrc[d] = st;
+            o.bdst[d] = l.bstride[d];
+        }
+        o.row_tiles = (o.rows + 31) / 32;
+        o.k_tiles = (o.kpad + 63) / 64;
+        o.tiles = o.row_tiles * o.k_tiles * l.batches;
+        o.k_fast = (o.s_k == 1 || o.s_row != 1) ? 1 : 0;
+    }
+    int64_t blocks = a.op[0].tiles + a.op[1].tiles;
+    if (blocks < 1) return MAGB200_OK;
+    if (blocks > (int64_t)num_sms() * 16) blocks = (int64_t)num_sms() * 16;
+    split3_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(a);
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
     return MAGB200_OK;
 }
 

@@ -130,7 +130,8 @@ struct GemmProblem {
 };
 
 // kernel launchers (each returns a magb200_status_t); `stream` is the device's launch stream
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes);
+// `run_if_set` (optional): a device word read at kernel start; the launch does nothing when it is zero.
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, const int *run_if_set = nullptr);
 size_t simt_scratch_bytes(const GemmProblem &p);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled);
@@ -167,5 +168,35 @@ int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream)
 bool tcgen05_operand_ok(const GemmProblem &p, bool is_a);
 size_t packed_operand_bytes(const GemmProblem &p, bool is_a);
 int launch_pack_operand(GemmProblem &p, bool is_a, void *dst, cudaStream_t stream);
+
+// ---- float32 on the tensor cores: every fp32 operand element is written as the sum of three bf16 values (8 + 8 + 8
+// significant bits) and the product is assembled from six bf16 MMAs; see gemm_tcgen05.cu. The three planes of one operand
+// batch are stacked along the row dim: element (plane, row, k) sits at [plane * rows + row][k] of a [3 * rows][kpad] matrix
+// with unit K stride, so one tensor map with the usual batch dims describes all of it. Broadcast batch dims are not replicated.
+struct PlaneLayout {
+    int64_t rows, kpad;                    // rows of one plane (M or N); row pitch in elements (K rounded up to 8)
+    int64_t bstride[kMaxBatchDims];        // element stride of each batch dim in the packed operand (0: broadcast)
+    int64_t batches;                       // product of the non-broadcast batch extents
+};
+inline PlaneLayout plane_layout(const GemmProblem &p, bool is_a) {
+    PlaneLayout l;
+    l.rows = is_a ? p.M : p.N;
+    l.kpad = (p.K + 7) / 8 * 8;
+    l.batches = 1;
+    int64_t pitch = 3 * l.rows * l.kpad;
+    for (int d = 0; d < kMaxBatchDims; ++d) l.bstride[d] = 0;
+    for (int d = p.nbatch - 1; d >= 0; --d) {
+        const int64_t st = is_a ? p.bsA[d] : p.bsB[d];
+        if (st != 0 && p.bshape[d] > 1) { l.bstride[d] = pitch; pitch *= p.bshape[d]; l.batches *= p.bshape[d]; }
+    }
+    return l;
+}
+inline size_t plane_bytes(const PlaneLayout &l) { return (size_t)(l.batches * 3 * l.rows * l.kpad) * 2; }
+// Splits both fp32 operands of `p` into their planes (one launch). `*unsafe` is raised when an element is not finite, would
+// overflow bf16, or is so small that its lower planes would be subnormal: the split product is then not to be used.
+int launch_split3(const GemmProblem &p, void *planes_a, void *planes_b, int *unsafe, cudaStream_t stream);
+bool f32x3_supported(const GemmProblem &p);
+// C = A @ B from the planes; the launch does nothing when `*skip_if_set` is non-zero.
+int launch_gemm_f32x3(const GemmProblem &p, const void *planes_a, const void *planes_b, const int *skip_if_set, int *status_word_dev, cudaStream_t stream);
 
 }  // namespace magb200

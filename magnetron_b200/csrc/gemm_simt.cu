@@ -57,7 +57,9 @@ __device__ __forceinline__ float fold_low(float total, float low) {
 // Compile-time modes make every shared-memory offset of the fetch a constant.
 template <int DT, bool AKF, bool BNF>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial) {
+gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial,
+                 const int *__restrict__ run_if_set) {
+    if (run_if_set && *run_if_set == 0) return;        // stand-by launch behind the split-operand tensor-core kernel
     extern __shared__ __align__(16) unsigned char simt_smem[];
     typedef float Tile[BK][BM + PAD];
     Tile *As = reinterpret_cast<Tile *>(simt_smem);                   // As[2][BK][BM + PAD]
@@ -294,9 +296,10 @@ size_t simt_scratch_bytes(const GemmProblem &p) {
     return pl.nsplit > 1 ? (size_t)pl.nsplit * 2 * (size_t)(p.batch_total * p.M * p.N) * sizeof(float) : 0;
 }
 
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, size_t scratch_bytes) {
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, size_t scratch_bytes, const int *run_if_set) {
     SimtPlan pl = plan_simt(p);
     if (pl.tiles <= 0) return MAGB200_OK;
+    if (run_if_set) scratch = nullptr;                // the stand-by form never splits K: its finalize pass would be unconditional
     if (pl.nsplit > 1 && (!scratch || scratch_bytes < simt_scratch_bytes(p))) {   // no workspace: one CTA walks all of K
         pl.nsplit = 1;
         pl.kchunk = ((p.K + BK - 1) / BK) * BK;
@@ -317,7 +320,7 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
         static std::atomic<uint32_t> optin{0};                                                               \
         if (int rc = simt_smem_optin(gemm_simt_kernel<DT, AKF, BNF>, simt_smem_bytes<DT>(), optin)) return rc; \
         gemm_simt_kernel<DT, AKF, BNF><<<(unsigned)grid, THREADS, simt_smem_bytes<DT>(), stream>>>(          \
-            p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch);                                       \
+            p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch, run_if_set);                                     \
     } while (0)
 #define MAGB200_SIMT_LAUNCH(DT)                                                                              \
     if (akf) { if (bnf) MAGB200_SIMT_GO(DT, true, true); else MAGB200_SIMT_GO(DT, true, false); }            \

@@ -911,6 +911,269 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
 }
 
+// =====================================================================================================================
+// float32 on the tensor cores: split operands.
+//
+// Every fp32 operand element is the sum of three bf16 values, a = a0 + a1 + a2 with 8 significant bits each (cast.cu writes
+// the three planes), so a * b = a0 b0 + (a0 b1 + a1 b0) + (a0 b2 + a1 b1 + a2 b0) + terms below 2^-26 |a b|: six bf16 MMAs
+// whose products are exact in the fp32 accumulator. What decides the accuracy is the accumulation, and a tensor-core
+// accumulator that walked all of K would do no better than a plain fp32 chain (which misses the reference's accuracy by a
+// factor of five). So the leading products a0 b0 of one 64-wide K block go to a FRESH accumulator (four MMAs), which the
+// eight drain warps then fold into per-thread running totals with an error-free TwoSum while the tensor core is already
+// filling the other of two such accumulators; the five small products (2^-8 and 2^-16 of the leading one) collect in a third
+// accumulator over all of K, where their own rounding is far below the result's last place, and are added once at the end.
+//
+// One 128 x 128 tile per CTA. A stage holds one K block of all six planes (96 KB), two stages. Warp 0 lane 0: TMA producer;
+// warp 1 lane 0: MMA issue (24 per K block); warps 2-9: drain (warp w owns TMEM lanes 32 (w % 4) .. +31 and 64 columns).
+// A drain thread keeps its 64 running totals in registers; their 64 low parts, touched once per K block, live in the
+// fourth quarter of TMEM (tcgen05.ld / tcgen05.st of the thread's own lane and columns), because ten warps leave a thread
+// 168 registers (three warps share one scheduler's 16 K).
+// TMEM columns: [0,128) and [128,256) the two leading-product accumulators, [256,384) the small products, [384,512) low parts.
+//
+// What bounds it: a 128 x 128 x 16 MMA reads 8 KB of shared memory for 64 clocks of tensor work, which is the whole 128 bytes
+// per clock a shared memory delivers, and the TMA writes of the next stage come on top; a wider tile would need more than the
+// 512 TMEM columns (two fresh accumulators, the small products and the low parts for every column).
+// =====================================================================================================================
+constexpr int kF3Threads = 320;
+constexpr int kF3BN = 128;
+constexpr int kF3PlaneBytes = BM * BK * 2;                 // one plane of one operand: 128 rows x 64 K values
+constexpr int kF3StageBytes = 6 * kF3PlaneBytes;
+constexpr int kF3Stages = 2;
+constexpr uint32_t kF3TmemCols = 512;
+constexpr size_t kF3SmemBytes = (size_t)kF3Stages * kF3StageBytes + 1024 + 256;
+
+struct F3Args {
+    float *C;
+    int64_t M, N, K;
+    int nbatch;
+    int64_t bshape[kMaxBatchDims];
+    int a_has[kMaxBatchDims], b_has[kMaxBatchDims];
+    int64_t tiles_m, tiles_n;
+    int num_kb;
+    int *status;
+    const int *skip_if_set;
+    uint64_t wait_limit_ns;
+};
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// s + e == a + b exactly
+__device__ __forceinline__ void two_sum_f3(float a, float b, float &s, float &e) {
+    const float sum = __fadd_rn(a, b);
+    const float bp = __fsub_rn(sum, a);
+    e = __fadd_rn(__fsub_rn(a, __fsub_rn(sum, bp)), __fsub_rn(b, bp));
+    s = sum;
+}
+
+__global__ void __launch_bounds__(kF3Threads, 1)
+gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const F3Args args) {
+    if (args.skip_if_set && *args.skip_if_set != 0) return;   // the operands cannot be split: the FFMA kernel behind this launch runs
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    unsigned char *tiles_ptr = smem_raw + (tiles - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles_ptr + (size_t)kF3Stages * kF3StageBytes);
+    // barrier slots: full[2], empty[2], mfull[2] (leading accumulator complete), mfree[2] (drained), cfull (small products complete)
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 16u, mfull0 = full0 + 32u, mfree0 = full0 + 48u, cfull = full0 + 64u;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 9);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 10);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(full0 + 8u * i, 1); mbar_init(empty0 + 8u * i, 1);
+            mbar_init(mfull0 + 8u * i, 1); mbar_init(mfree0 + 8u * i, 8);
+        }
+        mbar_init(cfull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"(kF3TmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int64_t batch, tm, tn;
+    decode_tile((int64_t)blockIdx.x, args.tiles_m, args.tiles_n, batch, tm, tn);
+    const int m0 = (int)(tm * BM), n0 = (int)(tn * kF3BN);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int bc[kMaxBatchDims] = {0, 0, 0};
+            {
+                int64_t rem = batch;
+                for (int d = args.nbatch - 1; d >= 0; --d) {
+                    int64_t q = rem / args.bshape[d];
+                    bc[d] = (int)(rem - q * args.bshape[d]);
+                    rem = q;
+                }
+            }
+            const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
+            const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = 0; kb < args.num_kb; ++kb) {
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) break;
+                const uint32_t full = full0 + 8u * stage;
+                const uint32_t sa = tiles + (uint32_t)stage * kF3StageBytes;
+                mbar_arrive_expect_tx(full, (uint32_t)kF3StageBytes);
+                const int k0 = kb * BK;
+#pragma unroll
+                for (int pl = 0; pl < 3; ++pl) {   // plane pl of an operand starts pl * rows further down the stacked row dim
+                    tma_load_5d(sa + pl * kF3PlaneBytes, &tmA, full, k0, pl * (int)args.M + m0, a2, a1, a0);
+                    tma_load_5d(sa + (3 + pl) * kF3PlaneBytes, &tmB, full, k0, pl * (int)args.N + n0, b2, b1, b0);
+                }
+                if (++stage == kF3Stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // bf16 operands, fp32 accumulate, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kF3BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint64_t dbase = make_smem_desc(tiles, 16u, 1024u);   // K-major, 128-byte rows, 8-row swizzle atoms 1024 bytes apart
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; ok && kb < args.num_kb; ++kb) {
+                const uint32_t mb = (uint32_t)kb & 1u;
+                if (!mbar_wait(full0 + 8u * stage, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
+                if (!mbar_wait(mfree0 + 8u * mb, (((uint32_t)kb >> 1) & 1u) ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
+                tcgen05_fence_after();
+                // descriptors differ only in their start-address field (16-byte units, no carry out of it below 256 KB): one add each
+                const uint64_t da = dbase + (uint64_t)(((uint32_t)stage * kF3StageBytes) >> 4);
+                const uint64_t db = da + (uint64_t)((3 * kF3PlaneBytes) >> 4);
+                // leading products into the fresh accumulator of this K block
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tcgen05_mma_f16(tmem_base + mb * kF3BN, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, k ? 1u : 0u);
+                tcgen05_commit(mfull0 + 8u * mb);
+                // the five small products, smallest first, into the accumulator that spans all of K
+#pragma unroll
+                for (int t = 0; t < 5; ++t) {
+                    const int pa = (t == 0) ? 2 : (t == 1) ? 1 : (t == 2) ? 0 : (t == 3) ? 1 : 0;
+                    const int pb = (t == 0) ? 0 : (t == 1) ? 1 : (t == 2) ? 2 : (t == 3) ? 0 : 1;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tcgen05_mma_f16(tmem_base + 2 * kF3BN, da + (uint64_t)((pa * kF3PlaneBytes + k * 32) >> 4),
+                                        db + (uint64_t)((pb * kF3PlaneBytes + k * 32) >> 4), idesc, (kb | t | k) ? 1u : 0u);
+                }
+                tcgen05_commit(empty0 + 8u * stage);
+                if (++stage == kF3Stages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) tcgen05_commit(cfull);
+        }
+    } else {
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * 64u;
+        const uint32_t low_base = lane_base + 3 * kF3BN;
+        float total[64];
+#pragma unroll
+        for (int j = 0; j < 64; ++j) total[j] = 0.f;
+        bool ok = true;
+        for (int kb = 0; kb < args.num_kb; ++kb) {
+            const uint32_t mb = (uint32_t)kb & 1u;
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(mfull0 + 8u * mb, ((uint32_t)kb >> 1) & 1u, abort_flag, args.wait_limit_ns));
+            if (!ok) break;
+            tcgen05_fence_after();
+            // chunk c + 1 is on its way from TMEM while chunk c is folded (tcgen05.wait::ld covers every load issued so far)
+            uint32_t r[2][16], lo[2][16];
+            tmem_ld_32x16(lane_base + mb * kF3BN, r[0]);
+            if (kb > 0) tmem_ld_32x16(low_base, lo[0]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld_wait();
+                if (c < 3) {
+                    tmem_ld_32x16(lane_base + mb * kF3BN + (c + 1) * 16, r[(c + 1) & 1]);
+                    if (kb > 0) tmem_ld_32x16(low_base + (c + 1) * 16, lo[(c + 1) & 1]);
+                } else {                            // everything of this accumulator is in registers: the tensor core may refill it
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(mfree0 + 8u * mb);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float e;
+                    two_sum_f3(total[c * 16 + j], __uint_as_float(r[c & 1][j]), total[c * 16 + j], e);
+                    lo[c & 1][j] = __float_as_uint(kb > 0 ? __fadd_rn(__uint_as_float(lo[c & 1][j]), e) : e);
+                }
+                tmem_st_32x16(low_base + c * 16, lo[c & 1]);
+            }
+            tmem_st_wait();
+        }
+        if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(cfull, 0u, abort_flag, args.wait_limit_ns));
+        if (ok) {
+            tcgen05_fence_after();
+            const int64_t row = (int64_t)m0 + quarter * 32 + lane;
+            float *crow = args.C + (batch * args.M + (row < args.M ? row : 0)) * args.N;
+            const bool vec_ok = (args.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[16], lo[16];
+                tmem_ld_32x16(lane_base + 2 * kF3BN + c * 16, r);
+                tmem_ld_32x16(low_base + c * 16, lo);
+                tmem_ld_wait();
+                const int64_t col0 = (int64_t)n0 + half * 64 + c * 16;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float t = total[c * 16 + j];
+                    const float l = __fadd_rn(__uint_as_float(lo[j]), __uint_as_float(r[j]));
+                    v[j] = (fabsf(t) == __int_as_float(0x7F800000)) ? t : __fadd_rn(t, l);
+                }
+                if (row < args.M) {
+                    if (vec_ok && col0 + 16 <= args.N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            *reinterpret_cast<float4 *>(crow + col0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col0 + j < args.N) crow[col0 + j] = v[j];
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, kStatusTimeout);
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kF3TmemCols) : "memory");
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1307,6 +1570,69 @@ int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, in
     if (bn == 128) { LAUNCH(128); }
     LAUNCH(64);
 #undef LAUNCH
+}
+
+// ---- float32 through split operands ---------------------------------------------------------------------------------
+namespace {
+bool describe_planes(const GemmProblem &p, bool is_a, const void *planes, OperandDesc &o) {
+    const PlaneLayout l = plane_layout(p, is_a);
+    o.base = planes;
+    o.inner_extent = p.K; o.outer_extent = 3 * l.rows; o.outer_pitch = l.kpad;
+    o.box_inner = BK; o.box_outer = BM;
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        o.has[d] = (d < p.nbatch && l.bstride[d] != 0) ? 1 : 0;
+        o.bext[d] = o.has[d] ? p.bshape[d] : 1;
+        o.bstride[d] = l.bstride[d];
+    }
+    return operand_ok(o);
+}
+}  // namespace
+
+bool f32x3_supported(const GemmProblem &p) {
+    if (p.dtype != MAGB200_F32) return false;
+    if (p.M < 1 || p.N < 1 || p.K < 1) return false;
+    if (3 * p.M >= (1ll << 31) || 3 * p.N >= (1ll << 31) || p.K >= (1ll << 31)) return false;
+    const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + kF3BN - 1) / kF3BN) * p.batch_total;
+    if (tiles >= (1ll << 31)) return false;
+    for (int d = 0; d < p.nbatch; ++d)
+        if (p.bshape[d] >= (1ll << 31)) return false;
+    OperandDesc a, b;
+    return describe_planes(p, true, nullptr, a) && describe_planes(p, false, nullptr, b);
+}
+
+int launch_gemm_f32x3(const GemmProblem &p, const void *planes_a, const void *planes_b, const int *skip_if_set, int *status_word_dev,
+                      cudaStream_t st) {
+    OperandDesc a, b;
+    if (!describe_planes(p, true, planes_a, a) || !describe_planes(p, false, planes_b, b)) {
+        set_error("matmul: the split-operand planes cannot be described to TMA");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = encode(a, MAGB200_BF16, &ta)) || (rc = encode(b, MAGB200_BF16, &tb))) return rc;
+    F3Args args;
+    memset(&args, 0, sizeof(args));
+    args.C = reinterpret_cast<float *>(p.C);
+    args.M = p.M; args.N = p.N; args.K = p.K;
+    args.nbatch = p.nbatch;
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        args.bshape[d] = d < p.nbatch ? p.bshape[d] : 1;
+        args.a_has[d] = a.has[d];
+        args.b_has[d] = b.has[d];
+    }
+    args.tiles_m = (p.M + BM - 1) / BM;
+    args.tiles_n = (p.N + kF3BN - 1) / kF3BN;
+    args.num_kb = (int)((p.K + BK - 1) / BK);
+    args.status = status_word_dev;
+    args.skip_if_set = skip_if_set;
+    args.wait_limit_ns = g_wait_limit_ns.load();
+    const int64_t tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    static std::atomic<uint32_t> optin{0};
+    if ((rc = ensure_smem_optin(gemm_f32x3_kernel, kF3SmemBytes, optin))) return rc;
+    gemm_f32x3_kernel<<<(unsigned)tiles, kF3Threads, kF3SmemBytes, st>>>(ta, tb, args);
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
 }
 
 }  // namespace magb200
