@@ -158,8 +158,10 @@ __global__ void __launch_bounds__(kThreads) pack_operand_kernel(const PackArgs a
 }
 
 // ---- fp32 operand -> three bf16 planes (hi, mid, lo with hi + mid + lo == value to 24 bits) -------------------------------
-// Tiles of 32 rows x 64 K values go through shared memory, so the reads walk whichever source dim has the unit stride and
-// the writes always walk K (two values, four bytes, per lane). Both operands of a product are split by one launch.
+// An operand whose K stride is 1 is read four K values per thread (one 16-byte load where the alignment allows) and written
+// as three 8-byte stores, four such groups in flight per thread. An operand whose rows have the unit stride (a [K, N] weight)
+// goes through shared memory in tiles of 32 rows x 64 K values, so the reads walk the rows and the writes walk K. Both
+// operands of a product are split by one launch; a work unit is 1024 groups of four or one tile.
 struct SplitOperand {
     const float *src;
     uint16_t *dst;
@@ -167,8 +169,10 @@ struct SplitOperand {
     int64_t s_row, s_k;                  // source strides (elements)
     int nbatch;
     int64_t bshape[kMaxBatchDims], bsrc[kMaxBatchDims], bdst[kMaxBatchDims];   // packed batch extents (1 where broadcast) and strides
-    int64_t row_tiles, k_tiles, tiles;
-    int k_fast;                          // 1: read with threads along K, 0: along rows
+    int64_t row_tiles, k_tiles, units;
+    int64_t quads_per_row, quads;        // groups of four K values per row (kpad / 4) and in the whole operand
+    int k_fast;                          // 1: K has the unit stride (direct path), 0: tiles through shared memory
+    int vec4;                            // direct path: rows start 16-byte aligned and K % 4 == 0
 };
 struct SplitArgs {
     SplitOperand op[2];
@@ -186,37 +190,73 @@ __device__ __forceinline__ bool unsafe_to_split(float v) {
     // not finite or rounds to a bf16 infinity; or non-zero below 2^-100, where the lower planes leave the normal range
     return a >= 0x7F7F8000u || (a != 0u && a < (27u << 23));
 }
+__device__ __forceinline__ void batch_offsets(const SplitOperand &o, int64_t rem, int64_t &so, int64_t &dof) {
+    so = 0; dof = 0;
+    for (int d = o.nbatch - 1; d >= 0; --d) {
+        const int64_t q = rem / o.bshape[d], idx = rem - q * o.bshape[d];
+        so += idx * o.bsrc[d];
+        dof += idx * o.bdst[d];
+        rem = q;
+    }
+}
 __global__ void __launch_bounds__(kThreads) split3_kernel(const SplitArgs a) {
     __shared__ float tile[32][65];
     const int t = threadIdx.x;
     bool bad = false;
-    const int64_t total = a.op[0].tiles + a.op[1].tiles;
+    const int64_t total = a.op[0].units + a.op[1].units;
     for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
-        const SplitOperand &o = a.op[id >= a.op[0].tiles ? 1 : 0];
-        const int64_t local = id >= a.op[0].tiles ? id - a.op[0].tiles : id;
+        const SplitOperand &o = a.op[id >= a.op[0].units ? 1 : 0];
+        const int64_t local = id >= a.op[0].units ? id - a.op[0].units : id;
+        if (o.k_fast) {
+            float4 v[4];
+            uint16_t *q[4];
+            const int64_t plane = o.rows * o.kpad;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t g = local * 1024 + i * 256 + t;
+                q[i] = nullptr;
+                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (g < o.quads) {
+                    const int64_t rl = g / o.quads_per_row, kq = g - rl * o.quads_per_row;
+                    const int64_t bi = rl / o.rows, row = rl - bi * o.rows;
+                    int64_t so, dof;
+                    batch_offsets(o, bi, so, dof);
+                    const float *src = o.src + so + row * o.s_row + kq * 4;
+                    q[i] = o.dst + dof + row * o.kpad + kq * 4;
+                    if (o.vec4) {
+                        if (kq * 4 < o.K) v[i] = *reinterpret_cast<const float4 *>(src);   // K % 4 == 0: a group is inside the row or past it
+                    } else {
+                        const int64_t k = kq * 4;
+                        if (k < o.K) v[i].x = src[0];
+                        if (k + 1 < o.K) v[i].y = src[1];
+                        if (k + 2 < o.K) v[i].z = src[2];
+                        if (k + 3 < o.K) v[i].w = src[3];
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (!q[i]) continue;
+                bad = bad || unsafe_to_split(v[i].x) || unsafe_to_split(v[i].y) || unsafe_to_split(v[i].z) || unsafe_to_split(v[i].w);
+                uint32_t h[4], m[4], l[4];
+                split3(v[i].x, h[0], m[0], l[0]);
+                split3(v[i].y, h[1], m[1], l[1]);
+                split3(v[i].z, h[2], m[2], l[2]);
+                split3(v[i].w, h[3], m[3], l[3]);
+                *reinterpret_cast<uint2 *>(q[i]) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+                *reinterpret_cast<uint2 *>(q[i] + plane) = make_uint2(m[0] | (m[1] << 16), m[2] | (m[3] << 16));
+                *reinterpret_cast<uint2 *>(q[i] + 2 * plane) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+            }
+            continue;
+        }
         const int64_t kt = local % o.k_tiles;
         int64_t rem = local / o.k_tiles;
         const int64_t rt = rem % o.row_tiles;
         rem /= o.row_tiles;
-        int64_t so = 0, dof = 0;
-        for (int d = o.nbatch - 1; d >= 0; --d) {
-            const int64_t q = rem / o.bshape[d], idx = rem - q * o.bshape[d];
-            so += idx * o.bsrc[d];
-            dof += idx * o.bdst[d];
-            rem = q;
-        }
+        int64_t so, dof;
+        batch_offsets(o, rem, so, dof);
         const int64_t r0 = rt * 32, k0 = kt * 64;
-        if (o.k_fast) {
-            const int kx = t & 63, ry = t >> 6;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = ry + 4 * i;
-                float v = 0.f;
-                if (r0 + r < o.rows && k0 + kx < o.K) v = o.src[so + (r0 + r) * o.s_row + (k0 + kx) * o.s_k];
-                bad = bad || unsafe_to_split(v);
-                tile[r][kx] = v;
-            }
-        } else {
+        {
             const int rx = t & 31, ky = t >> 5;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -345,10 +385,16 @@ int launch_split3(const GemmProblem &p, void *planes_a, void *planes_b, int *uns
         }
         o.row_tiles = (o.rows + 31) / 32;
         o.k_tiles = (o.kpad + 63) / 64;
-        o.tiles = o.row_tiles * o.k_tiles * l.batches;
-        o.k_fast = (o.s_k == 1 || o.s_row != 1) ? 1 : 0;
+        o.quads_per_row = o.kpad / 4;
+        o.quads = o.quads_per_row * o.rows * l.batches;
+        o.k_fast = (o.s_k == 1 || p.K == 1) ? 1 : 0;
+        o.units = o.k_fast ? (o.quads + 1023) / 1024 : o.row_tiles * o.k_tiles * l.batches;
+        bool aligned = (((uintptr_t)o.src) & 15u) == 0 && p.K % 4 == 0 && o.s_row % 4 == 0;
+        for (int d = 0; d < p.nbatch; ++d)
+            if (o.bsrc[d] % 4) aligned = false;
+        o.vec4 = aligned ? 1 : 0;
     }
-    int64_t blocks = a.op[0].tiles + a.op[1].tiles;
+    int64_t blocks = a.op[0].units + a.op[1].units;
     if (blocks < 1) return MAGB200_OK;
     if (blocks > (int64_t)num_sms() * 16) blocks = (int64_t)num_sms() * 16;
     split3_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(a);

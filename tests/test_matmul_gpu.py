@@ -67,6 +67,17 @@ def test_case_simt_kernel(gpu, name, dname):
     check_case(name, dname, dt, xb, yb, got, K)
 
 
+@pytest.mark.parametrize("name", CASE_NAMES)
+def test_case_float32_split_operand_kernel(gpu, name):
+    """Every float32 case through the tensor-core kernel that splits the operands into three bf16 planes: same gate, same
+    own bar and same closeness to the reference as the FFMA kernel (strided, transposed, batched and broadcast operands go
+    through the split pass, ragged shapes through the tile tails)."""
+    dt = O.FLOAT32
+    xb, yb, got, used, K = run_case(gpu, name, dt, "tcgen05_f32x3")
+    assert used == "tcgen05_f32x3"
+    check_case(name, "f32", dt, xb, yb, got, K)
+
+
 TC_CASES = ["sq64", "rect_big", "linear_wT", "linear_wT_tail", "x_T_al", "both_T_al", "batch_y_T", "gqa_scores", "gqa_pv",
             "slice_k", "slice_n", "big_k", "tile_edge", "batch_same", "batch_bcast_y", "batch_mixed", "permute_x"]
 
@@ -117,7 +128,7 @@ def test_single_op_workload_512x2048x2048(gpu, dname):
     xb, wb = bits(dt, rng, (512, 2048), 1.0), bits(dt, rng, (2048, 2048), 0.02)
     tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
     r = tx @ tw.T
-    assert mb.last_kernel() == ("tcgen05" if dt == O.BFLOAT16 else "simt")   # 16 tiles of 256x256: the one-CTA kernel
+    assert mb.last_kernel() == ("tcgen05" if dt == O.BFLOAT16 else "tcgen05_f32x3")   # 16 tiles of 256x256: the one-CTA kernel
     got = r.to_bits()
     truth = O.bits_to_f64(dt, xb) @ O.bits_to_f64(dt, wb).T
     scale = np.abs(O.bits_to_f64(dt, xb)) @ np.abs(O.bits_to_f64(dt, wb)).T

@@ -283,6 +283,86 @@ def test_non_finite_operands_float32(gpu):
             t.release()
 
 
+def test_float32_operands_that_cannot_be_split(gpu):
+    """The float32 tensor-core path writes every element as three bf16 values, which cannot hold an infinity, a NaN, a value
+    that rounds to a bf16 infinity or one so small that its lower parts leave the normal range. The split pass flags such an
+    operand, the tensor-core launch then does nothing and the FFMA kernel that stands by behind it computes the product:
+    the result is bit for bit what the FFMA kernel gives when it is asked for directly. A clean product afterwards takes
+    the tensor-core kernel again (the flag is per call)."""
+    dt = O.FLOAT32
+    rng = np.random.default_rng(15)
+    M, N, K = 256, 384, 512
+    clean_x, clean_w = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.1)
+    patterns = {"inf": 0x7F800000, "nan": 0x7FC00000, "rounds_to_bf16_inf": 0x7F7FFFFF, "tiny": 0x0A000000, "subnormal": 0x00000001}
+    for label, pat in patterns.items():
+        for where in ("x", "w"):
+            xb, wb = clean_x.copy(), clean_w.copy()
+            (xb if where == "x" else wb)[3, K - 5] = pat
+            tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+            results = {}
+            for kernel in ("tcgen05_f32x3", "simt"):
+                mb.force_kernel(kernel)
+                try:
+                    r = tx @ tw.T
+                    assert mb.last_kernel() == kernel
+                    results[kernel] = r.to_bits()
+                    r.release()
+                finally:
+                    mb.force_kernel(None)
+            assert np.array_equal(results["tcgen05_f32x3"], results["simt"]), (label, where)
+            for t in (tx, tw):
+                t.release()
+    # clean operands: the two kernels differ in the last place somewhere, which shows that the tensor-core kernel ran
+    tx, tw = mb.Tensor.from_bits(gpu, dt, clean_x), mb.Tensor.from_bits(gpu, dt, clean_w)
+    out = {}
+    for kernel in ("tcgen05_f32x3", "simt"):
+        mb.force_kernel(kernel)
+        try:
+            r = tx @ tw.T
+            out[kernel] = O.bits_to_f64(dt, r.to_bits())
+            r.release()
+        finally:
+            mb.force_kernel(None)
+    truth = O.bits_to_f64(dt, clean_x) @ O.bits_to_f64(dt, clean_w).T
+    scale = np.abs(O.bits_to_f64(dt, clean_x)) @ np.abs(O.bits_to_f64(dt, clean_w)).T
+    for kernel in out:
+        assert (np.abs(out[kernel] - truth) / scale).max() <= 2.0 ** -24 * 1.5, kernel
+    assert not np.array_equal(out["tcgen05_f32x3"], out["simt"])
+    for t in (tx, tw):
+        t.release()
+
+
+def test_float32_split_operand_kernel_in_a_graph(gpu):
+    """The planes live in the device workspace, so the float32 tensor-core path can be recorded into a CUDA graph once the
+    workspace has its size (one plain call first); replays give the same bits as the plain call."""
+    dt = O.FLOAT32
+    rng = np.random.default_rng(16)
+    M, N, K = 384, 512, 1024
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.1)
+    tx, tw, out = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb), mb.Tensor(gpu, dt, (M, N))
+    L = mb.lib()
+    xv, wv, ov = tx.view_struct(), tw.T.view_struct(), out.view_struct()
+    mb.force_kernel("tcgen05_f32x3")
+    try:
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv), C.byref(ov)))
+        plain = out.to_bits()
+        mb.check(L.magb200_fill(gpu, C.byref(ov), C.c_double(0.0)))
+        graph = C.c_void_p()
+        mb.check(L.magb200_graph_begin_capture(gpu))
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv), C.byref(ov)))
+        assert mb.last_kernel() == "tcgen05_f32x3"
+        mb.check(L.magb200_graph_end_capture(gpu, C.byref(graph)))
+        for _ in range(3):
+            mb.check(L.magb200_graph_launch(gpu, graph))
+        mb.synchronize(gpu)
+        assert np.array_equal(out.to_bits(), plain)
+        mb.check(L.magb200_graph_destroy(graph))
+    finally:
+        mb.force_kernel(None)
+    for t in (tx, tw, out):
+        t.release()
+
+
 @pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_2sm", "skinny", "simt"])
 def test_non_finite_operands(gpu, kernel):
     """NaN and infinities in the operands: rows / columns that meet them are NaN or infinite in the result, every other
