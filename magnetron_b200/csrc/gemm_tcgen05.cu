@@ -980,6 +980,10 @@ __device__ __forceinline__ void two_sum_f3(float a, float b, float &s, float &e)
     s = sum;
 }
 
+// kSplitK: launched as clusters of two CTAs that share one tile: CTA r of the pair walks the r-th half of the K blocks, and
+// at the end CTA 1 hands its (total, low) pairs to CTA 0 through distributed shared memory (CTA 0's stage buffers, idle by
+// then), where they are added with one more TwoSum: an output with fewer tiles than half the SMs keeps twice as many busy.
+template <bool kSplitK>
 __global__ void __launch_bounds__(kF3Threads, 1)
 gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const F3Args args) {
     if (args.skip_if_set && *args.skip_if_set != 0) return;   // the operands cannot be split: the FFMA kernel behind this launch runs
@@ -1018,8 +1022,13 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
 
     int64_t batch, tm, tn;
-    decode_tile((int64_t)blockIdx.x, args.tiles_m, args.tiles_n, batch, tm, tn);
+    decode_tile(kSplitK ? (int64_t)(blockIdx.x >> 1) : (int64_t)blockIdx.x, args.tiles_m, args.tiles_n, batch, tm, tn);
     const int m0 = (int)(tm * BM), n0 = (int)(tn * kF3BN);
+    const uint32_t krank = kSplitK ? cluster_ctarank() : 0u;
+    const int kb_half = (args.num_kb + 1) >> 1;
+    const int kb_begin = kSplitK ? (int)krank * kb_half : 0;
+    const int kb_end = kSplitK ? (kb_begin + kb_half < args.num_kb ? kb_begin + kb_half : args.num_kb) : args.num_kb;
+    const int nkb = kb_end - kb_begin;                 // K blocks of this CTA
 
     if (warp == 0) {
         if (lane == 0) {
@@ -1036,12 +1045,12 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
             int stage = 0;
             uint32_t phase = 0;
-            for (int kb = 0; kb < args.num_kb; ++kb) {
+            for (int kb = 0; kb < nkb; ++kb) {
                 if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) break;
                 const uint32_t full = full0 + 8u * stage;
                 const uint32_t sa = tiles + (uint32_t)stage * kF3StageBytes;
                 mbar_arrive_expect_tx(full, (uint32_t)kF3StageBytes);
-                const int k0 = kb * BK;
+                const int k0 = (kb_begin + kb) * BK;
 #pragma unroll
                 for (int pl = 0; pl < 3; ++pl) {   // plane pl of an operand starts pl * rows further down the stacked row dim
                     tma_load_5d(sa + pl * kF3PlaneBytes, &tmA, full, k0, pl * (int)args.M + m0, a2, a1, a0);
@@ -1050,6 +1059,7 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (++stage == kF3Stages) { stage = 0; phase ^= 1u; }
             }
         }
+        if constexpr (kSplitK) { cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == 1) {
         if (lane == 0) {
             // bf16 operands, fp32 accumulate, both K-major, N = 128, M = 128
@@ -1058,7 +1068,7 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int kb = 0; ok && kb < args.num_kb; ++kb) {
+            for (int kb = 0; ok && kb < nkb; ++kb) {
                 const uint32_t mb = (uint32_t)kb & 1u;
                 if (!mbar_wait(full0 + 8u * stage, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                 if (!mbar_wait(mfree0 + 8u * mb, (((uint32_t)kb >> 1) & 1u) ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
@@ -1086,6 +1096,7 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             if (ok) tcgen05_commit(cfull);
         }
+        if constexpr (kSplitK) { cluster_sync_all(); cluster_sync_all(); }   // the two meeting points of the drain warps below
     } else {
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * 64u;
@@ -1094,7 +1105,7 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 64; ++j) total[j] = 0.f;
         bool ok = true;
-        for (int kb = 0; kb < args.num_kb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
             const uint32_t mb = (uint32_t)kb & 1u;
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(mfull0 + 8u * mb, ((uint32_t)kb >> 1) & 1u, abort_flag, args.wait_limit_ns));
             if (!ok) break;
@@ -1125,8 +1136,30 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tmem_st_wait();
         }
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(cfull, 0u, abort_flag, args.wait_limit_ns));
-        if (ok) {
-            tcgen05_fence_after();
+        tcgen05_fence_after();
+        // slot of element (row, col) of the tile in CTA 0's idle stage buffers: 8 bytes, rows fastest (a warp's lanes are rows)
+        const uint32_t slot0 = (uint32_t)((half * 64) * 128 + quarter * 32 + lane) * 8u;
+        if constexpr (kSplitK) {
+            cluster_sync_all();                     // both CTAs' MMAs have completed: nothing reads CTA 0's stages any more
+            if (krank == 1u && ok) {
+                const uint32_t remote = map_to_cta(tiles, 0u);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[16], lo[16];
+                    tmem_ld_32x16(lane_base + 2 * kF3BN + c * 16, r);
+                    tmem_ld_32x16(low_base + c * 16, lo);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float l = __fadd_rn(__uint_as_float(lo[j]), __uint_as_float(r[j]));
+                        asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};"
+                                     ::"r"(remote + slot0 + (uint32_t)(c * 16 + j) * 1024u), "f"(total[c * 16 + j]), "f"(l) : "memory");
+                    }
+                }
+            }
+            cluster_sync_all();                     // CTA 1's pairs are in CTA 0's shared memory
+        }
+        if (ok && krank == 0u) {
             const int64_t row = (int64_t)m0 + quarter * 32 + lane;
             float *crow = args.C + (batch * args.M + (row < args.M ? row : 0)) * args.N;
             const bool vec_ok = (args.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
@@ -1140,8 +1173,14 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float t = total[c * 16 + j];
-                    const float l = __fadd_rn(__uint_as_float(lo[j]), __uint_as_float(r[j]));
+                    float t = total[c * 16 + j];
+                    float l = __fadd_rn(__uint_as_float(lo[j]), __uint_as_float(r[j]));
+                    if constexpr (kSplitK) {
+                        const float2 other = *reinterpret_cast<const float2 *>(tiles_ptr + slot0 + (uint32_t)(c * 16 + j) * 1024u);
+                        float e;
+                        two_sum_f3(t, other.x, t, e);
+                        l = __fadd_rn(__fadd_rn(l, other.y), e);
+                    }
                     v[j] = (fabsf(t) == __int_as_float(0x7F800000)) ? t : __fadd_rn(t, l);
                 }
                 if (row < args.M) {
@@ -1627,9 +1666,27 @@ int launch_gemm_f32x3(const GemmProblem &p, const void *planes_a, const void *pl
     args.skip_if_set = skip_if_set;
     args.wait_limit_ns = g_wait_limit_ns.load();
     const int64_t tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    if (tiles * 2 <= num_sms() && args.num_kb >= 8) {      // few tiles, long K: pairs of CTAs share a tile along K
+        static std::atomic<uint32_t> optin_split{0};
+        if ((rc = ensure_smem_optin(gemm_f32x3_kernel<true>, kF3SmemBytes, optin_split))) return rc;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)(2 * tiles), 1, 1);
+        cfg.blockDim = dim3(kF3Threads, 1, 1);
+        cfg.dynamicSmemBytes = kF3SmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_f32x3_kernel<true>, ta, tb, args));
+        count_launch();
+        return MAGB200_OK;
+    }
     static std::atomic<uint32_t> optin{0};
-    if ((rc = ensure_smem_optin(gemm_f32x3_kernel, kF3SmemBytes, optin))) return rc;
-    gemm_f32x3_kernel<<<(unsigned)tiles, kF3Threads, kF3SmemBytes, st>>>(ta, tb, args);
+    if ((rc = ensure_smem_optin(gemm_f32x3_kernel<false>, kF3SmemBytes, optin))) return rc;
+    gemm_f32x3_kernel<false><<<(unsigned)tiles, kF3Threads, kF3SmemBytes, st>>>(ta, tb, args);
     count_launch();
     MAGB200_CUDA_TRY(cudaGetLastError());
     return MAGB200_OK;
