@@ -163,6 +163,16 @@ int  magb200_fill(int device, const magb200_view_t *dst, double value);
  * one rounding to the result dtype. */
 int  magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y, const magb200_view_t *r);
 
+/* Gated MLP, r = silu(x @ w_gate) * (x @ w_up): the operator sequence MATMUL, MATMUL, SILU, MUL of a SwiGLU block
+ * (examples/qwen3/model.py:48-49) as one call, with the roundings of that sequence (both matmul results, silu and the
+ * product are each rounded to the tensor dtype), so the result is what the four operators give. bf16 and fp16. When
+ * M >= 256, N >= 128 and TMA can describe the operands, one two-SM GEMM computes gate and up columns of the same outputs
+ * side by side in TMEM and combines them on the drain: the two [M, N] intermediates never reach memory. Other shapes run two
+ * matmuls into pooled temporaries and an elementwise pass (not during graph capture). w_gate and w_up are y operands of
+ * magb200_matmul (e.g. W.T views) of equal shape and strides; r is contiguous. */
+int  magb200_matmul_swiglu(int device, const magb200_view_t *x, const magb200_view_t *w_gate, const magb200_view_t *w_up,
+                           const magb200_view_t *r);
+
 /* `count` (1..4) matmuls that share their first operand: r_i = x @ y_i, e.g. the q, k and v projections or gate and up of a
  * decode step, which magnetron dispatches as consecutive MAG_OP_MATMULs with the same in[0] (examples/qwen3/model.py:109-111,
  * :48-49). Decode-shaped groups (M <= 8, 16-bit K-major weights, no K split) run as ONE launch whose 16-row weight tiles

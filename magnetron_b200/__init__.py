@@ -87,6 +87,7 @@ SIGNATURES = {
     "magb200_fill": (C.c_int, [C.c_int, _VP, C.c_double]),
     "magb200_cat": (C.c_int, [C.c_int, C.POINTER(_VP), C.c_int, C.c_int, _VP]),
     "magb200_matmul": (C.c_int, [C.c_int, _VP, _VP, _VP]),
+    "magb200_matmul_swiglu": (C.c_int, [C.c_int, _VP, _VP, _VP, _VP]),
     "magb200_matmul_grouped": (C.c_int, [C.c_int, _VP, C.c_int, C.POINTER(_VP), C.POINTER(_VP)]),
     "magb200_matmul_result_shape": (C.c_int, [_VP, _VP, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "magb200_last_kernel": (C.c_int, []),
@@ -347,3 +348,12 @@ class Tensor:
         return out
 
     __matmul__ = matmul
+
+    def matmul_swiglu(self, w_gate: "Tensor", w_up: "Tensor") -> "Tensor":   # silu(self @ w_gate) * (self @ w_up)
+        rank = C.c_int32()
+        shape = (C.c_int64 * (MAX_DIMS + 2))()
+        xv, gv, uv = self.view_struct(), w_gate.view_struct(), w_up.view_struct()
+        check(lib().magb200_matmul_result_shape(C.byref(xv), C.byref(gv), C.byref(rank), shape))
+        out = Tensor(self.device, self.dtype, [shape[i] for i in range(rank.value)])
+        check(lib().magb200_matmul_swiglu(self.device, C.byref(xv), C.byref(gv), C.byref(uv), C.byref(out.view_struct())))
+        return out

@@ -902,6 +902,44 @@ int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y,
     return matmul_device(*d, device, x, y, r);
 }
 
+int magb200_matmul_swiglu(int device, const magb200_view_t *x, const magb200_view_t *w_gate, const magb200_view_t *w_up, const magb200_view_t *r) {
+    if (cudaError_t inj = take_injected(MAGB200_FAULT_SITE_LAUNCH)) return cuda_fail(inj, "kernel launch (injected)", __FILE__, __LINE__);
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!x || !w_gate || !w_up || !r) { set_error("matmul_swiglu: null operand"); return MAGB200_ERR_INVALID_ARG; }
+    FullProblem fg, fu;
+    if ((rc = build_problem(x, w_gate, r, fg)) || (rc = build_problem(x, w_up, r, fu))) return rc;
+    const GemmProblem &g = fg.g, &u = fu.g;
+    if (g.dtype != MAGB200_BF16 && g.dtype != MAGB200_F16) { set_error("matmul_swiglu: 16-bit dtypes only"); return MAGB200_ERR_INVALID_ARG; }
+    bool same = fg.n_outer == 0 && fu.n_outer == 0 && g.M == u.M && g.N == u.N && g.K == u.K && g.sBk == u.sBk && g.sBn == u.sBn &&
+                g.nbatch == u.nbatch && g.batch_total == u.batch_total;
+    for (int i = 0; same && i < g.nbatch; ++i) same = g.bsB[i] == u.bsB[i] && g.bshape[i] == u.bshape[i];
+    if (same && g_force.load() == 0 && swiglu_fused_supported(g, u.B)) {
+        g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
+        ordered_point(*d);
+        return launch_gemm_swiglu(g, u.B, d->stream, d->cta_limit, d->status);
+    }
+    // the operator sequence as it is: two matmuls into pooled temporaries, then the elementwise pass
+    if (d->capturing) { set_error("matmul_swiglu: this shape needs temporaries from the pool, which a graph capture cannot take"); return MAGB200_ERR_INVALID_ARG; }
+    const int64_t n = view_numel(r);
+    if (!view_is_contiguous(r) || (n & 1)) { set_error("matmul_swiglu: the result must be contiguous with an even element count"); return MAGB200_ERR_INVALID_ARG; }
+    void *tg = nullptr, *tu = nullptr;
+    const size_t bytes = (size_t)n * dtype_size(g.dtype);
+    if ((rc = magb200_malloc(device, &tg, bytes)) == MAGB200_OK && (rc = magb200_malloc(device, &tu, bytes)) == MAGB200_OK) {
+        magb200_view_t vg = *r, vu = *r;
+        vg.base = tg; vg.offset = 0;
+        vu.base = tu; vu.offset = 0;
+        if (!(rc = matmul_device(*d, device, x, w_gate, &vg)) && !(rc = matmul_device(*d, device, x, w_up, &vu))) {
+            ordered_point(*d);
+            rc = launch_swiglu(g.dtype, tg, tu, view_data(r), n, d->stream);
+        }
+    }
+    if (tg) magb200_free(device, tg);
+    if (tu) magb200_free(device, tu);
+    return rc;
+}
+
 int magb200_matmul_grouped(int device, const magb200_view_t *x, int count, const magb200_view_t *const *ys, const magb200_view_t *const *rs) {
     DeviceState *d;
     int rc = ensure_device(device, &d);

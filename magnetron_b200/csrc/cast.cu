@@ -363,6 +363,32 @@ int launch_pack_operand(GemmProblem &p, bool is_a, void *dst, cudaStream_t strea
     return MAGB200_OK;
 }
 
+namespace {
+template <int DT>
+__global__ void __launch_bounds__(kThreads) swiglu_kernel(const uint32_t *__restrict__ g, const uint32_t *__restrict__ u,
+                                                          uint32_t *__restrict__ out, int64_t pairs) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < pairs; i += stride) out[i] = swiglu_pack2<DT>(g[i], u[i]);
+}
+}  // namespace
+
+int launch_swiglu(int dtype, const void *g, const void *u, void *out, int64_t n, cudaStream_t stream) {
+    if (n <= 0) return MAGB200_OK;
+    if ((n & 1) || (((uintptr_t)g | (uintptr_t)u | (uintptr_t)out) & 3u)) {
+        set_error("swiglu: needs an even element count and 4-byte aligned tensors");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    const int64_t pairs = n / 2;
+    if (dtype == MAGB200_BF16)
+        swiglu_kernel<MAGB200_BF16><<<grid_for(pairs), kThreads, 0, stream>>>((const uint32_t *)g, (const uint32_t *)u, (uint32_t *)out, pairs);
+    else if (dtype == MAGB200_F16)
+        swiglu_kernel<MAGB200_F16><<<grid_for(pairs), kThreads, 0, stream>>>((const uint32_t *)g, (const uint32_t *)u, (uint32_t *)out, pairs);
+    else { set_error("swiglu: 16-bit dtypes only"); return MAGB200_ERR_INVALID_ARG; }
+    count_launch();
+    MAGB200_CUDA_TRY(cudaGetLastError());
+    return MAGB200_OK;
+}
+
 int launch_split3(const GemmProblem &p, void *planes_a, void *planes_b, int *unsafe, cudaStream_t stream) {
     SplitArgs a;
     memset(&a, 0, sizeof(a));

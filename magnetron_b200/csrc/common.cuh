@@ -112,6 +112,27 @@ template <> __device__ __forceinline__ uint32_t pack2_rn<MAGB200_F16>(float lo, 
     return d;
 }
 
+// silu(g) * u as the unfused operator sequence of a gated MLP computes it (examples/qwen3/model.py:48-49: two matmuls, SILU,
+// MUL, each rounding its result to the tensor dtype): `packed_g` and `packed_u` hold two matmul results each, already rounded
+// to DT; silu is rounded once more, then the product. Shared by the fused GEMM epilogue and the elementwise kernel, so both
+// give the same bits.
+template <int DT> __device__ __forceinline__ void unpack2(uint32_t w, float &lo, float &hi);
+template <> __device__ __forceinline__ void unpack2<MAGB200_BF16>(uint32_t w, float &lo, float &hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+}
+template <> __device__ __forceinline__ void unpack2<MAGB200_F16>(uint32_t w, float &lo, float &hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w));
+}
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+template <int DT> __device__ __forceinline__ uint32_t swiglu_pack2(uint32_t packed_g, uint32_t packed_u) {
+    float g0, g1, u0, u1, s0, s1;
+    unpack2<DT>(packed_g, g0, g1);
+    unpack2<DT>(packed_u, u0, u1);
+    unpack2<DT>(pack2_rn<DT>(silu_f32(g0), silu_f32(g1)), s0, s1);
+    return pack2_rn<DT>(s0 * u0, s1 * u1);
+}
+
 // ---- canonical description of one matmul, produced by the front-end in cabi.cu -----------------
 constexpr int kMaxBatchDims = 3;
 struct GemmProblem {
@@ -168,6 +189,15 @@ int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream)
 bool tcgen05_operand_ok(const GemmProblem &p, bool is_a);
 size_t packed_operand_bytes(const GemmProblem &p, bool is_a);
 int launch_pack_operand(GemmProblem &p, bool is_a, void *dst, cudaStream_t stream);
+
+// ---- gated MLP: out = silu(x @ Wg) * (x @ Wu) --------------------------------------------------------------------------
+// Fused form: one two-SM GEMM whose 256 accumulator columns are 128 gate and 128 up columns of the same outputs, combined on
+// the TMEM drain (`p` describes x @ Wg with C = out; `b_up` is Wu with Wg's strides). False / non-zero when the shapes or
+// layouts do not allow it; the caller then runs two matmuls and launch_swiglu.
+bool swiglu_fused_supported(const GemmProblem &p, const void *b_up);
+int launch_gemm_swiglu(const GemmProblem &p, const void *b_up, cudaStream_t st, int cta_limit, int *status_word_dev);
+// out[i] = silu(g[i]) * u[i], contiguous, n elements of a 16-bit dtype (n even, 4-byte aligned pointers)
+int launch_swiglu(int dtype, const void *g, const void *u, void *out, int64_t n, cudaStream_t stream);
 
 // ---- float32 on the tensor cores: every fp32 operand element is written as the sum of three bf16 values (8 + 8 + 8
 // significant bits) and the product is assembled from six bf16 MMAs; see gemm_tcgen05.cu. The three planes of one operand

@@ -573,10 +573,16 @@ __device__ __forceinline__ void tcgen05_mma_f16_2sm_split(uint32_t tmem_d, uint3
 // kTmaStore: the staged 32 x 64 patches leave through cp.async.bulk.tensor stores (one instruction per patch instead of
 // eight shared loads and eight predicated 16-byte global stores per lane); used whenever the result is a plain local
 // tensor TMA can describe. The scatter epilogue (peer stores) and the shared last wave keep the per-lane write-out.
-template <int DT, int KSUB, bool kShare, bool kTmaStore>
+// kSwiGLU: the gated-MLP form out = silu(x @ Wg) * (x @ Wu). A tile is 256 rows x 128 OUTPUT columns: CTA 0 of the pair loads
+// the 128 gate rows of Wg (tmB), CTA 1 the 128 up rows of Wu (tmB2) for the same outputs, so accumulator columns [0,128) hold
+// x @ Wg and [128,256) x @ Wu, and the drain combines column j with column 128 + j (with the roundings of the unfused
+// operator sequence) before the bulk store: half the result bytes of two GEMMs, and no pass over them afterwards.
+template <int DT, int KSUB, bool kShare, bool kTmaStore, bool kSwiGLU>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmC, const TcArgs args) {
+                        const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC, const TcArgs args) {
+    static_assert(!kSwiGLU || (kTmaStore && !kShare), "the gated form leaves through the bulk-store epilogue, whole tiles only");
+    constexpr int kTileN = kSwiGLU ? BN2 / 2 : BN2;      // output columns of a tile
     using C = Cfg2<KSUB>;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -603,6 +609,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
+        if constexpr (kSwiGLU) prefetch_tmap(&tmB2);
     }
     if (warp == 1) {  // both CTAs of the pair allocate, same warp index in each
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -630,7 +637,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 int64_t batch, tm, tn;
                 decode_tile(w.tile, args.tiles_m, args.tiles_n, batch, tm, tn);
                 const int m0 = (int)(tm * 2 * BM) + (int)rank * BM;        // this CTA's 128 rows of the 256-row tile
-                const int n0 = (int)(tn * BN2) + (int)rank * (BN2 / 2);    // this CTA's 128 columns of B
+                // this CTA's 128 columns of B: half of a 256-column tile, or (gated form) the tile's gate / up columns
+                const int n0 = kSwiGLU ? (int)(tn * kTileN) : (int)(tn * BN2) + (int)rank * (BN2 / 2);
+                const CUtensorMap *mapB = (kSwiGLU && rank == 1) ? &tmB2 : &tmB;
                 int bc[kMaxBatchDims] = {0, 0, 0};
                 {
                     int64_t rem = batch;
@@ -665,10 +674,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                             for (int c = 0; c < BM / 64; ++c) tma_load_5d_2sm(ssa + c * 8192, &tmA, full, m0 + c * 64, k0, a2, a1, a0);
                         }
                         if (!args.b_mn) {
-                            tma_load_5d_2sm(ssb, &tmB, full, k0, n0, b2, b1, b0);
+                            tma_load_5d_2sm(ssb, mapB, full, k0, n0, b2, b1, b0);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < (BN2 / 2) / 64; ++c) tma_load_5d_2sm(ssb + c * 8192, &tmB, full, n0 + c * 64, k0, b2, b1, b0);
+                            for (int c = 0; c < (BN2 / 2) / 64; ++c) tma_load_5d_2sm(ssb + c * 8192, mapB, full, n0 + c * 64, k0, b2, b1, b0);
                         }
                     }
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -739,11 +748,50 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             int64_t batch, tm, tn;
             decode_tile(w.tile, args.tiles_m, args.tiles_n, batch, tm, tn);
             const int64_t row = tm * 2 * BM + (int64_t)rank * BM + quarter * 32 + lane;
-            const int64_t n0 = tn * BN2;
+            const int64_t n0 = tn * kTileN;
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag, args.wait_limit_ns));
             if (!ok) break;
             tcgen05_fence_after();
             const int chalf = (warp - 2) >> 2;            // which 128-column half of the tile this warp drains
+            if constexpr (kSwiGLU) {
+                // this warp's 32 rows x 64 output columns [chalf * 64, +64): gate from accumulator column c, up from column 128 + c
+                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + (size_t)(warp - 2) * C::kEpiWarpBytes;
+                const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
+                const uint32_t tb = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * 64;
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t g[32], up[32];
+                    tmem_ld_32x32(tb + h * 32, g);
+                    tmem_ld_32x32(tb + BN2 / 2 + h * 32, up);
+                    tmem_ld_wait();
+                    if (h == 0) {                        // the previous tile's bulk store has read the patch
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    } else {                             // the accumulator has been read completely: hand it back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        o.x = swiglu_pack2<DT>(pack2_rn<DT>(__uint_as_float(g[8 * v + 0]), __uint_as_float(g[8 * v + 1])),
+                                               pack2_rn<DT>(__uint_as_float(up[8 * v + 0]), __uint_as_float(up[8 * v + 1])));
+                        o.y = swiglu_pack2<DT>(pack2_rn<DT>(__uint_as_float(g[8 * v + 2]), __uint_as_float(g[8 * v + 3])),
+                                               pack2_rn<DT>(__uint_as_float(up[8 * v + 2]), __uint_as_float(up[8 * v + 3])));
+                        o.z = swiglu_pack2<DT>(pack2_rn<DT>(__uint_as_float(g[8 * v + 4]), __uint_as_float(g[8 * v + 5])),
+                                               pack2_rn<DT>(__uint_as_float(up[8 * v + 4]), __uint_as_float(up[8 * v + 5])));
+                        o.w = swiglu_pack2<DT>(pack2_rn<DT>(__uint_as_float(g[8 * v + 6]), __uint_as_float(g[8 * v + 7])),
+                                               pack2_rn<DT>(__uint_as_float(up[8 * v + 6]), __uint_as_float(up[8 * v + 7])));
+                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + (((v + 4 * h) ^ (lane & 7)) << 4)) = o;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0 && row0 < args.M && n0 + chalf * 64 < args.N)
+                    tma_store_5d(&tmC, smem_u32(stg), (int)(n0 + chalf * 64), (int)row0, (int)batch, 0, 0);
+                continue;
+            }
             // This warp's 32 x 128 block of a partial tile in scratch: [32-column chunk][accumulator register][lane], so that
             // the 32 lanes of every store and load touch 128 contiguous bytes. Contributor and owner use the same mapping.
             const size_t warp_block = ((size_t)rank * C::kEpiWarps + (size_t)(warp - 2)) * (32 * (BN2 / 2));
@@ -1460,26 +1508,28 @@ void plan_tail(TcArgs &args, int64_t pairs, const SplitWorkspace *ws, int ksub) 
     args.sk_counters = ws->counters;
 }
 
-template <int DT, int KSUB, bool kShare, bool kTmaStore>
-int launch_2sm_kernel(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const TcArgs &args, const cudaLaunchConfig_t &cfg) {
-    auto kernel = gemm_tcgen05_2sm_kernel<DT, KSUB, kShare, kTmaStore>;
+template <int DT, int KSUB, bool kShare, bool kTmaStore, bool kSwiGLU = false>
+int launch_2sm_kernel(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2, const CUtensorMap &tc, const TcArgs &args,
+                      const cudaLaunchConfig_t &cfg) {
+    auto kernel = gemm_tcgen05_2sm_kernel<DT, KSUB, kShare, kTmaStore, kSwiGLU>;
     static std::atomic<uint32_t> optin{0};
     if (int rc = ensure_smem_optin(kernel, Cfg2<KSUB>::kSmemBytes, optin)) return rc;
-    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, args));
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tb2, tc, args));
     return MAGB200_OK;
 }
 
 // `tc`: tensor map of the result for the bulk-store epilogue, or null when the result cannot leave that way
+// `tb_up`: tensor map of the up-projection weights for the gated form (then `tc` is required), else null
 template <int DT, int KSUB>
 int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap *tc, TcArgs &args, cudaStream_t st,
-               int cta_limit, const SplitWorkspace *ws) {
+               int cta_limit, const SplitWorkspace *ws, const CUtensorMap *tb_up = nullptr) {
     fill_knobs(args);
     args.tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-    args.tiles_n = (p.N + BN2 - 1) / BN2;
+    args.tiles_n = tb_up ? (p.N + BN2 / 2 - 1) / (BN2 / 2) : (p.N + BN2 - 1) / BN2;
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
     const int64_t max_pairs = (cta_limit > 1 ? cta_limit : num_sms()) / 2;
     const unsigned pairs = (unsigned)(args.total_tiles < max_pairs ? args.total_tiles : max_pairs);
-    plan_tail(args, pairs, ws, KSUB);
+    plan_tail(args, pairs, tb_up ? nullptr : ws, KSUB);     // the gated form never shares a tile along K
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -1492,9 +1542,10 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int rc;
-    if (args.tail_slots > 0) rc = launch_2sm_kernel<DT, KSUB, true, false>(ta, tb, ta, args, cfg);
-    else if (tc) rc = launch_2sm_kernel<DT, KSUB, false, true>(ta, tb, *tc, args, cfg);
-    else rc = launch_2sm_kernel<DT, KSUB, false, false>(ta, tb, ta, args, cfg);
+    if (tb_up) rc = launch_2sm_kernel<DT, KSUB, false, true, true>(ta, tb, *tb_up, *tc, args, cfg);
+    else if (args.tail_slots > 0) rc = launch_2sm_kernel<DT, KSUB, true, false>(ta, tb, tb, ta, args, cfg);
+    else if (tc) rc = launch_2sm_kernel<DT, KSUB, false, true>(ta, tb, tb, *tc, args, cfg);
+    else rc = launch_2sm_kernel<DT, KSUB, false, false>(ta, tb, tb, ta, args, cfg);
     if (rc) return rc;
     count_launch();
     return MAGB200_OK;
@@ -1575,6 +1626,57 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
     }
     return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16, 2>(p, ta, tb, tc, args, st, cta_limit, ws)
                                    : launch_2sm<MAGB200_F16, 2>(p, ta, tb, tc, args, st, cta_limit, ws);
+}
+
+// ---- gated MLP: out = silu(x @ Wg) * (x @ Wu) in one launch -----------------------------------------------------------------
+namespace {
+// the result [batch][M][N] as boxes of 64 columns x 32 rows for the epilogue's bulk stores
+bool describe_result(const GemmProblem &p, OperandDesc &c) {
+    if (p.N % 8) return false;
+    memset(&c, 0, sizeof(c));
+    c.base = p.C; c.inner_extent = p.N; c.outer_extent = p.M; c.outer_pitch = p.N;
+    c.box_inner = 64; c.box_outer = 32;
+    for (int d = 0; d < kMaxBatchDims; ++d) { c.bext[d] = 1; c.bstride[d] = 0; c.has[d] = 0; }
+    if (p.batch_total > 1) { c.bext[kMaxBatchDims - 1] = p.batch_total; c.bstride[kMaxBatchDims - 1] = p.M * p.N; c.has[kMaxBatchDims - 1] = 1; }
+    return operand_ok(c);
+}
+}  // namespace
+
+bool swiglu_fused_supported(const GemmProblem &p, const void *b_up) {
+    if (!tcgen05_supported(p) || p.M < 256 || p.N < 128) return false;
+    GemmProblem q = p;
+    q.B = b_up;
+    OperandDesc o;
+    int mn;
+    if (!describe(q, false, 128, o, mn)) return false;
+    return describe_result(p, o) && ((uintptr_t)p.C & 15u) == 0;
+}
+
+int launch_gemm_swiglu(const GemmProblem &p, const void *b_up, cudaStream_t st, int cta_limit, int *status_word_dev) {
+    GemmProblem q = p;
+    q.B = b_up;
+    OperandDesc a, b, b2, c;
+    int amn = 0, bmn = 0, b2mn = 0;
+    if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn) || !describe(q, false, 128, b2, b2mn) || bmn != b2mn ||
+        !describe_result(p, c)) {
+        set_error("gated matmul: operand layout cannot be described by TMA tensor maps");
+        return MAGB200_ERR_INVALID_ARG;
+    }
+    CUtensorMap ta, tb, tb2, tc;
+    int rc;
+    if ((rc = encode(a, p.dtype, &ta)) || (rc = encode(b, p.dtype, &tb)) || (rc = encode(b2, p.dtype, &tb2)) || (rc = encode(c, p.dtype, &tc))) return rc;
+    TcArgs args;
+    memset(&args, 0, sizeof(args));
+    args.C = p.C; args.M = p.M; args.N = p.N; args.K = p.K; args.dtype = p.dtype;
+    args.a_mn = amn; args.b_mn = bmn; args.nbatch = p.nbatch;
+    for (int d = 0; d < kMaxBatchDims; ++d) {
+        args.bshape[d] = d < p.nbatch ? p.bshape[d] : 1;
+        args.a_has[d] = a.has[d]; args.b_has[d] = b.has[d];
+    }
+    args.num_kb = (int)((p.K + BK - 1) / BK);
+    args.status = status_word_dev;
+    return p.dtype == MAGB200_BF16 ? launch_2sm<MAGB200_BF16, 2>(p, ta, tb, &tc, args, st, cta_limit, nullptr, &tb2)
+                                   : launch_2sm<MAGB200_F16, 2>(p, ta, tb, &tc, args, st, cta_limit, nullptr, &tb2);
 }
 
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {

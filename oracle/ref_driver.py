@@ -131,6 +131,8 @@ class MagApi:
             "mag_permute": (C.c_int, [VP, C.POINTER(P), P, I64P, I64]),
             "mag_view_slice": (C.c_int, [VP, C.POINTER(P), P, I64, I64, I64, I64]),
             "mag_matmul": (C.c_int, [VP, C.POINTER(P), P, P]),
+            "mag_silu": (C.c_int, [VP, C.POINTER(P), P]),
+            "mag_mul": (C.c_int, [VP, C.POINTER(P), P, P]),
             "mag_tensor_rank": (I64, [P]),
             "mag_tensor_shape_ptr": (I64P, [P]),
             "mag_tensor_strides_ptr": (I64P, [P]),
@@ -218,3 +220,9 @@ class MagApi:
 
     def matmul(self, x: Tensor, y: Tensor) -> Tensor:
         return self._call(self.lib.mag_matmul, x.ptr, y.ptr)
+
+    def silu(self, x: Tensor) -> Tensor:          # include/magnetron/magnetron.h:342
+        return self._call(self.lib.mag_silu, x.ptr)
+
+    def mul(self, x: Tensor, y: Tensor) -> Tensor:  # include/magnetron/magnetron.h:362
+        return self._call(self.lib.mag_mul, x.ptr, y.ptr)

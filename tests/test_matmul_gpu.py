@@ -493,3 +493,61 @@ def test_errors(gpu):
     out = mb.Tensor(gpu, O.BFLOAT16, (4, 7))
     rc = mb.lib().magb200_matmul(gpu, C.byref(a.view_struct()), C.byref(c.view_struct()), C.byref(out.view_struct()))
     assert rc == mb.ERR_INVALID_ARG      # both inputs must share one dtype (core/mag_op_stubs.c:224-247)
+
+
+# ---- gated MLP: silu(x @ Wg.T) * (x @ Wu.T) ------------------------------------------------------------------------------
+def _swiglu_inputs(dt, M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    return (O.f32_to_bits(dt, cases.gen_storage(rng, (M, K), 1.0)), O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.05)),
+            O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.05)))
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K,transposed", [(512, 1024, 512, True), (300, 200, 328, True), (1024, 384, 256, False), (64, 256, 128, True)])
+def test_gated_mlp_fused_equals_operator_sequence(gpu, dname, M, N, K, transposed):
+    """magb200_matmul_swiglu against (1) the same product computed on the device as two matmuls and the elementwise pass
+    (bit for bit: the fused drain applies the same roundings), (2) the reference CPU backend running MATMUL, MATMUL, SILU,
+    MUL, in the reference tests' 16-bit tolerance, (3) fp64. Shapes: whole tiles, ragged M / N / K, weights as [K, N]
+    instead of W.T views, and one too small for the fused kernel (falls back to the operator sequence by itself)."""
+    dt = cases.DTYPES[dname]
+    xb, gb, ub = _swiglu_inputs(dt, M, N, K, 21)
+    if not transposed:
+        gb, ub = np.ascontiguousarray(gb.T), np.ascontiguousarray(ub.T)
+    tx, tg, tu = (mb.Tensor.from_bits(gpu, dt, b) for b in (xb, gb, ub))
+    wg, wu = (tg.T, tu.T) if transposed else (tg, tu)
+    fused = tx.matmul_swiglu(wg, wu)
+    fused_kernel = mb.last_kernel()
+    mb.force_kernel("tcgen05")          # any forced kernel takes the operator-sequence route; this one sums K in the same order
+    try:
+        plain = tx.matmul_swiglu(wg, wu)
+    finally:
+        mb.force_kernel(None)
+    fb, pb = fused.to_bits(), plain.to_bits()
+    if M >= 256:
+        assert fused_kernel == "tcgen05_2sm"
+        assert np.array_equal(fb, pb)
+    xf = O.bits_to_f64(dt, xb)
+    gf, uf = (O.bits_to_f64(dt, b) for b in (gb, ub))
+    g64, u64 = (xf @ gf.T, xf @ uf.T) if transposed else (xf @ gf, xf @ uf)
+    truth = g64 / (1.0 + np.exp(-g64)) * u64
+    got = O.bits_to_f64(dt, fb)
+    u = unit_roundoff(dt)
+    assert np.all(np.abs(got - truth) <= 6 * u * np.abs(truth) + 4 * u * np.abs(u64) * (np.abs(xf) @ np.abs(gf.T if transposed else gf)) + 1e-30)
+    if R.available():
+        api = R.MagApi("cpu", log_level=1)
+        try:
+            ra, rg, ru = api.from_bits(dt, xb), api.from_bits(dt, gb), api.from_bits(dt, ub)
+            vg, vu = (api.transpose(rg, 0, 1), api.transpose(ru, 0, 1)) if transposed else (rg, ru)
+            mg, mu = api.matmul(ra, vg), api.matmul(ra, vu)
+            sg = api.silu(mg)
+            rr = api.mul(sg, mu)
+            ref = O.bits_to_f64(dt, api.to_bits(rr))
+            for h in (rr, sg, mu, mg) + ((vg, vu) if transposed else ()) + (ru, rg, ra):
+                h.release()
+        finally:
+            api.close(True)
+        # reference operator tests: atol 1e-2, rtol 1e-2 for 16-bit dtypes (test/python/operators/test_matmul.py:7-11)
+        if True:
+            assert np.all(np.abs(got - ref) <= 1e-2 * max(1.0, np.abs(truth).max()) + 1e-2 * np.abs(ref))
+    for t in (fused, plain, tx, tg, tu):
+        t.release()
