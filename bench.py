@@ -15,8 +15,9 @@ One JSON line on stdout. A "step" is one pass of the hot path over one batch of 
          The same line carries every other single-GPU configuration with its own roofline fraction and the
          reference CPU backend timed beside it in the same run: `single_op` (512 x 2048 x 2048 through `W.T`,
          bf16 and fp32), `casts` (16 Mi elements both ways), `decode` (Qwen3-0.6B token pass, M in {1,2,4,8}),
-         `attention` (scores and P.V over broadcast strided views, bf16 and fp16, full size) and `tp_layer_1gpu`
-         (the Qwen3-32B layer unsharded: the denominator of the multi-GPU scaling).
+         `attention` (scores and P.V over broadcast strided views, bf16 and fp16, full size), `tp_layer_1gpu`
+         (the Qwen3-32B layer unsharded: the denominator of the multi-GPU scaling) and `gated_mlp` (the step's
+         silu(gate) * up as one fused GEMM against the operator sequence).
   N > 1  workload "qwen3-32b-tp" (bench_tp.py): the four sharded GEMM groups of one Qwen3-32B layer at M = 8192, one rank
          per GPU. Total work is fixed, so scaling is "strong".
 
@@ -551,6 +552,16 @@ def cast_workload(dev: Dev, cpu: CpuRef, steps: int, warmup: int, hbm_peak: floa
         out[key] = {"ms": ms / max(steps, 20), "gbs": gbs, "frac": gbs / hbm_peak, "frac_of_nominal_8000": gbs / 8000.0}
     for t in f32 + b16:
         t.release()
+    # the same kernels on 128 Mi elements (805 MB per launch): a 16 Mi launch lasts 20 us, much of it the ramp of the DRAM pipes
+    big = 1 << 27
+    bf = mb.Tensor(dev.d, mb.FLOAT32, (big,))
+    bb = mb.Tensor(dev.d, BF16, (big,))
+    mb.check(dev.L.magb200_fill(dev.d, C.byref(bf.view_struct()), C.c_double(1.5)))
+    for key, src, dst in (("f32_to_bf16", bf, bb), ("bf16_to_f32", bb, bf)):
+        sv, dv = src.view_struct(), dst.view_struct()
+        ms, _ = timed(dev, lambda: mb.check(dev.L.magb200_cast(dev.d, C.byref(sv), C.byref(dv))), 5, 2)
+        out[key]["at_128Mi"] = {"ms": ms / 5, "gbs": big * 6 * 5 / ms / 1e6, "frac": big * 6 * 5 / ms / 1e6 / hbm_peak}
+    bf.release(); bb.release()
     if cpu.api:
         api = cpu.api
         xb = np.random.default_rng(1).standard_normal(n, dtype=np.float32).view(np.uint32)
@@ -632,6 +643,54 @@ def attention_workload(dev: Dev, cpu: CpuRef, hbm_peak: float, tensor_peak: floa
             res["scores"]["cpu"] = res["pv"]["cpu"] = cpu.note()
         out[key] = res
     return out
+
+
+def gated_mlp_workload(dev: Dev, cpu: CpuRef, steps: int, warmup: int, tensor_peak: float):
+    """silu(x @ Wg.T) * (x @ Wu.T) of the prefill step's MLP (4096 tokens, 4096 -> 12288): one fused GEMM against the operator
+    sequence on the device (two GEMMs into temporaries and an elementwise pass), FLOPs counted as the two GEMMs' in both."""
+    mb = dev.mb
+    M, N, K = TOKENS, INTER, HIDDEN
+    rng = np.random.default_rng(9)
+    x, wg, wu = dev.random_bf16((M, K), 1.0, rng), dev.random_bf16((N, K), 0.02, rng), dev.random_bf16((N, K), 0.02, rng)
+    out = mb.Tensor(dev.d, BF16, (M, N))
+    xv, gv, uv, ov = x.view_struct(), wg.T.view_struct(), wu.T.view_struct(), out.view_struct()
+    call = lambda: mb.check(dev.L.magb200_matmul_swiglu(dev.d, C.byref(xv), C.byref(gv), C.byref(uv), C.byref(ov)))
+    n = max(3, min(steps, 20))
+    ms, _ = timed(dev, call, n, warmup)
+    mb.force_kernel("tcgen05_2sm")           # a pinned kernel makes the entry point run the operator sequence
+    try:
+        ms_seq, _ = timed(dev, call, n, warmup)
+    finally:
+        mb.force_kernel(None)
+    flops = 4.0 * M * N * K
+    tf = flops * n / ms / 1e9
+    res = {"shape": [M, N, K], "ms": ms / n, "tflops": tf, "operator_sequence_ms": ms_seq / n, "operator_sequence_tflops": flops * n / ms_seq / 1e9,
+           "result_bytes_saved_per_call": 2 * M * N * 2 * 2,
+           "roofline": {"bound": "tensor", "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak}}
+    for t in (x, wg, wu, out):
+        t.release()
+    if cpu.api:
+        api = cpu.api
+        crng = np.random.default_rng(9)
+        cm = 512
+        rx = api.from_bits(BF16, host_bits(BF16, crng, (cm, K), 1.0))
+        rg, ru = api.from_bits(BF16, host_bits(BF16, crng, (N, K), 0.02)), api.from_bits(BF16, host_bits(BF16, crng, (N, K), 0.02))
+        gt, ut = api.transpose(rg, 0, 1), api.transpose(ru, 0, 1)
+
+        def seq():
+            a, b = api.matmul(rx, gt), api.matmul(rx, ut)
+            s_ = api.silu(a)
+            r = api.mul(s_, b)
+            for h in (r, s_, b, a):
+                h.release()
+
+        sec = cpu.seconds(seq, 2)
+        for h in (ut, gt, ru, rg, rx):
+            h.release()
+        res["cpu"] = {"tflops": 4.0 * cm * N * K / sec / 1e12, **cpu.note("MATMUL, MATMUL, SILU, MUL at 512 tokens (rows are independent)")}
+    else:
+        res["cpu"] = cpu.note()
+    return res
 
 
 TP_LAYER = [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600)]
@@ -819,6 +878,7 @@ def main():
     line["casts"] = {"unit": "GB/s", "peak": pk["hbm"], "elements": 1 << 24, **cast_workload(dev, cpu, args.steps, args.warmup, pk["hbm"])}
     line["attention"] = attention_workload(dev, cpu, pk["hbm"], tensor_peak)
     line["tp_layer_1gpu"] = tp_layer_1gpu_workload(dev, cpu, args.steps, args.warmup, tensor_peak)
+    line["gated_mlp"] = gated_mlp_workload(dev, cpu, args.steps, args.warmup, tensor_peak)
     line["cpu_baseline"] = cpu_prefill_step(cpu, 4, 1)
     cpu.close()
     dev.sync()

@@ -312,6 +312,25 @@ MAG_EXPORT mag_status_t mag_b200_download_async(const mag_tensor_t *tensor, void
     return mag_b200_map_status(magb200_download_overlapped(dev, host_data, src, size_bytes), "download");
 }
 
+/* Additive export: the gated MLP out = silu(x @ w_gate) * (x @ w_up) as one call, for callers that would otherwise issue
+ * mag_matmul, mag_matmul, mag_silu, mag_mul (examples/qwen3/model.py:48-49); same result as that sequence. `out` is a
+ * contiguous tensor of the product's shape on this backend (mag_empty). */
+MAG_EXPORT mag_status_t mag_b200_matmul_swiglu(mag_tensor_t *x, mag_tensor_t *w_gate, mag_tensor_t *w_up, mag_tensor_t *out) {
+    mag_tensor_t *all[4] = {x, w_gate, w_up, out};
+    for (int i = 0; i < 4; ++i)
+        if (!all[i] || !all[i]->storage || all[i]->storage->device->id.type != MAG_BACKEND_TYPE_CUDA) {
+            mag_log_error("mag_b200_matmul_swiglu: every tensor must live on the cuda backend");
+            return MAG_STATUS_ERR_INVALID_PARAM;
+        }
+    magb200_view_t vx, vg, vu, vr;
+    mag_b200_view_of(x, &vx);
+    mag_b200_view_of(w_gate, &vg);
+    mag_b200_view_of(w_up, &vu);
+    mag_b200_view_of(out, &vr);
+    const int dev = ((mag_b200_device_t *)out->storage->device->impl)->ordinal;
+    return mag_b200_map_status(magb200_matmul_swiglu(dev, &vx, &vg, &vu, &vr), "matmul_swiglu");
+}
+
 MAG_EXPORT mag_status_t mag_b200_host_alloc(void **out, size_t size_bytes) {
     return mag_b200_map_status(magb200_host_alloc_pinned(out, size_bytes), "page-locked host allocation");
 }

@@ -175,8 +175,48 @@ def test_kv_append_through_the_reference_api(deploy_dir):
         finish(gpu_api, ok)
 
 
+def test_gated_mlp_through_the_module_export(deploy_dir):
+    """mag_b200_matmul_swiglu on "cuda:0" against mag_matmul, mag_matmul, mag_silu, mag_mul on the reference CPU backend of the
+    same process, in the reference operator tests' 16-bit tolerance."""
+    gpu_api = CudaApi(deploy_dir)
+    cpu_api = R.MagApi("cpu", lib_dir=deploy_dir, log_level=1)
+    ok = False
+    try:
+        dt = R.BFLOAT16
+        M, N, K = 512, 768, 256
+        rng = np.random.default_rng(23)
+        xb = O.f32_to_bits(dt, cases.gen_storage(rng, (M, K), 1.0))
+        gb = O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.05))
+        ub = O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.05))
+        # device: one call
+        tx, tg, tu = gpu_api.from_bits(dt, xb), gpu_api.from_bits(dt, gb), gpu_api.from_bits(dt, ub)
+        gt, ut = gpu_api.transpose(tg, 0, 1), gpu_api.transpose(tu, 0, 1)
+        out = gpu_api.empty(dt, (M, N))
+        fn = gpu_api.mod.mag_b200_matmul_swiglu
+        fn.restype, fn.argtypes = C.c_int, [C.c_void_p] * 4
+        assert fn(tx.ptr, gt.ptr, ut.ptr, out.ptr) == 0
+        got = O.bits_to_f64(dt, gpu_api.to_bits(out))
+        for t in (out, ut, gt, tu, tg, tx):
+            t.release()
+        # reference: the four operators
+        rx, rg, ru = cpu_api.from_bits(dt, xb), cpu_api.from_bits(dt, gb), cpu_api.from_bits(dt, ub)
+        rgt, rut = cpu_api.transpose(rg, 0, 1), cpu_api.transpose(ru, 0, 1)
+        mg, mu = cpu_api.matmul(rx, rgt), cpu_api.matmul(rx, rut)
+        sg = cpu_api.silu(mg)
+        rr = cpu_api.mul(sg, mu)
+        ref = O.bits_to_f64(dt, cpu_api.to_bits(rr))
+        for t in (rr, sg, mu, mg, rut, rgt, ru, rg, rx):
+            t.release()
+        assert np.all(np.abs(got - ref) <= 1e-2 * max(1.0, np.abs(ref).max()) + 1e-2 * np.abs(ref))
+        ok = True
+    finally:
+        cpu_api.close(not ok)
+        finish(gpu_api, ok)
+
+
 CASES = {"matmul_cast": test_matmul_and_cast_through_the_reference_api,
          "kv_append": test_kv_append_through_the_reference_api,
+         "gated_mlp": test_gated_mlp_through_the_module_export,
          "gqa_views": test_gqa_broadcast_views_through_the_reference_api,
          "unsupported_op": test_unsupported_opcode_returns_a_status}
 

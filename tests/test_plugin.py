@@ -101,3 +101,10 @@ def test_kv_append_through_the_reference_api(deploy_dir, gpu):
     """mag_cat (KV-cache append) and the scores against the grown cache on "cuda:0", bit-compared with the reference CPU
     backend running the same calls in the same process."""
     run_in_fresh_process("kv_append", deploy_dir)
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_gated_mlp_through_the_module_export(deploy_dir, gpu):
+    """mag_b200_matmul_swiglu (additive export) against MATMUL, MATMUL, SILU, MUL on the reference CPU backend."""
+    run_in_fresh_process("gated_mlp", deploy_dir)
