@@ -122,6 +122,10 @@ int  magb200_mem_info(int device, uint64_t *free_bytes, uint64_t *total_bytes);
 int  magb200_upload(int device, void *dst_device, const void *src_host, size_t bytes);   /* stream-ordered, then synchronised */
 int  magb200_download(int device, void *dst_host, const void *src_device, size_t bytes); /* stream-ordered, then synchronised */
 int  magb200_upload_async(int device, void *dst_device, const void *src_pinned_host, size_t bytes);
+/* `rows` rows of `width_bytes` each from a pitched host matrix into a pitched device matrix, then synchronised: one rank's
+ * slice of a weight that sits whole in a memory-mapped snapshot file (magnetron/core/mag_snapshot.c:566-640 hands out such
+ * tensors on the CPU only) goes to the device without an intermediate copy of the slice. */
+int  magb200_upload_2d(int device, void *dst_device, size_t dst_pitch, const void *src_host, size_t src_pitch, size_t width_bytes, size_t rows);
 int  magb200_download_async(int device, void *dst_pinned_host, const void *src_device, size_t bytes);
 /* Transfers on the library's two copy streams, so host<->device traffic of one operator runs beside the kernels of
  * others and uploads run beside downloads (the link is full duplex). No reference counterpart: magnetron's module ABI

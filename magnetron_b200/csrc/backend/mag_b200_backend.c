@@ -331,6 +331,54 @@ MAG_EXPORT mag_status_t mag_b200_matmul_swiglu(mag_tensor_t *x, mag_tensor_t *w_
     return mag_b200_map_status(magb200_matmul_swiglu(dev, &vx, &vg, &vu, &vr), "matmul_swiglu");
 }
 
+/* Additive export: a tensor that lives on the CPU backend -- typically one handed out by mag_snapshot_deserialize, which
+ * maps the .mag file and works on a CPU context only (magnetron/core/mag_snapshot.c:566-640) -- becomes a tensor of the cuda
+ * context `ctx`, whole (shard_dim < 0) or as one rank's equal share of dimension `shard_dim` (rank `shard` of `shards`: the
+ * row block of a column-sharded nn.Linear weight [N, K] is shard_dim 0, the K slice of a row-sharded one shard_dim 1). The
+ * bytes go straight from the mapped file to device memory; a slice of an inner dim is a pitched copy. `src` must be
+ * contiguous. */
+MAG_EXPORT mag_status_t mag_b200_tensor_to_device(mag_context_t *ctx, const mag_tensor_t *src, int64_t shard_dim, int64_t shard, int64_t shards,
+                                                  mag_tensor_t **out) {
+    if (!ctx || !ctx->active_device || ctx->active_device->id.type != MAG_BACKEND_TYPE_CUDA || !src || !out || !src->storage ||
+        src->storage->device->id.type != MAG_BACKEND_TYPE_CPU || !mag_tensor_is_contiguous(src)) {
+        mag_log_error("mag_b200_tensor_to_device: needs a cuda context and a contiguous tensor of the CPU backend");
+        return MAG_STATUS_ERR_INVALID_PARAM;
+    }
+    const int64_t rank = src->coords.rank;
+    int64_t shape[MAG_MAX_DIMS];
+    for (int64_t i = 0; i < rank; ++i) shape[i] = src->coords.shape[i];
+    int64_t outer = 1, inner = 1, len = 1, first = 0;
+    if (shard_dim >= 0) {
+        if (shard_dim >= rank || shards < 1 || shard < 0 || shard >= shards || shape[shard_dim] % shards) {
+            mag_log_error("mag_b200_tensor_to_device: dimension %lld of extent %lld cannot be cut into %lld equal shards",
+                          (long long)shard_dim, (long long)(shard_dim < rank ? shape[shard_dim] : -1), (long long)shards);
+            return MAG_STATUS_ERR_INVALID_PARAM;
+        }
+        len = shape[shard_dim];
+        for (int64_t i = 0; i < shard_dim; ++i) outer *= shape[i];
+        for (int64_t i = shard_dim + 1; i < rank; ++i) inner *= shape[i];
+        shape[shard_dim] = len / shards;
+        first = shard * shape[shard_dim];
+    }
+    mag_error_t err;
+    mag_status_t st = mag_empty(&err, out, ctx, src->dtype, rank, shape);
+    if (st != MAG_STATUS_OK) return st;
+    mag_tensor_t *dst = *out;
+    const size_t es = mag_type_trait(src->dtype)->size;
+    const int dev = ((mag_b200_device_t *)dst->storage->device->impl)->ordinal;
+    char *d = (char *)dst->storage->base + dst->storage_offset * (int64_t)es;
+    const char *s = (const char *)src->storage->base + src->storage_offset * (int64_t)es;
+    int rc;
+    if (shard_dim < 0) {
+        rc = magb200_upload(dev, d, s, (size_t)src->numel * es);
+    } else {
+        const size_t width = (size_t)(shape[shard_dim] * inner) * es, pitch = (size_t)(len * inner) * es;
+        rc = magb200_upload_2d(dev, d, width, s + (size_t)(first * inner) * es, pitch, width, (size_t)outer);
+    }
+    if (rc != MAGB200_OK) { mag_tensor_decref(dst); *out = NULL; }
+    return mag_b200_map_status(rc, "tensor_to_device");
+}
+
 MAG_EXPORT mag_status_t mag_b200_host_alloc(void **out, size_t size_bytes) {
     return mag_b200_map_status(magb200_host_alloc_pinned(out, size_bytes), "page-locked host allocation");
 }

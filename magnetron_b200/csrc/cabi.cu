@@ -816,6 +816,17 @@ int magb200_upload(int device, void *dst, const void *src, size_t bytes) {
     MAGB200_CUDA_TRY(cudaStreamSynchronize(g_dev[device].stream));
     return MAGB200_OK;
 }
+int magb200_upload_2d(int device, void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t rows) {
+    DeviceState *d;
+    int rc = ensure_device(device, &d);
+    if (rc) return rc;
+    if (!dst || !src || width_bytes > dst_pitch || width_bytes > src_pitch) { set_error("upload_2d: a row is wider than a pitch"); return MAGB200_ERR_INVALID_ARG; }
+    if (width_bytes == 0 || rows == 0) return MAGB200_OK;
+    ordered_point(*d);
+    MAGB200_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyHostToDevice, d->stream));
+    MAGB200_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return MAGB200_OK;
+}
 int magb200_download(int device, void *dst, const void *src, size_t bytes) {
     int rc = magb200_download_async(device, dst, src, bytes);
     if (rc) return rc;

@@ -214,9 +214,88 @@ def test_gated_mlp_through_the_module_export(deploy_dir):
         finish(gpu_api, ok)
 
 
+def test_snapshot_tensors_to_the_device(deploy_dir):
+    """A .mag snapshot written and read back by the reference itself (CPU context; its tensors borrow the mapped file) goes to
+    "cuda:0" through mag_b200_tensor_to_device: whole, as the row block of a column-sharded weight and as the K slice of a
+    row-sharded one; every copy is bit-compared with the numpy slice, and the shards reproduce the unsharded product."""
+    import os
+    import tempfile
+    gpu_api = CudaApi(deploy_dir)
+    cpu_api = R.MagApi("cpu", lib_dir=deploy_dir, log_level=1)
+    lib = cpu_api.lib
+    P = C.c_void_p
+    for name, res, args in (("mag_snapshot_new", P, [P]), ("mag_snapshot_deserialize", P, [P, C.c_char_p]),
+                            ("mag_snapshot_serialize", C.c_bool, [P, C.c_char_p]), ("mag_snapshot_get_tensor", P, [P, C.c_char_p]),
+                            ("mag_snapshot_put_tensor", C.c_bool, [P, C.c_char_p, P]), ("mag_snapshot_free", None, [P])):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    to_device = gpu_api.mod.mag_b200_tensor_to_device
+    to_device.restype, to_device.argtypes = C.c_int, [P, P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(P)]
+    ok = False
+    tmp = tempfile.mkdtemp(prefix="magsnap_")
+    path = os.path.join(tmp, "weights.mag").encode()
+    try:
+        dt = R.BFLOAT16
+        N, K, M, ranks = 512, 384, 256, 2
+        rng = np.random.default_rng(31)
+        wb = O.f32_to_bits(dt, cases.gen_storage(rng, (N, K), 0.05))
+        f32b = rng.standard_normal((3, 5, 7), dtype=np.float32).view(np.uint32)
+        snap = lib.mag_snapshot_new(cpu_api.ctx)
+        tw, tf = cpu_api.from_bits(dt, wb), cpu_api.from_bits(R.FLOAT32, f32b)
+        assert lib.mag_snapshot_put_tensor(snap, b"layer.weight", tw.ptr) and lib.mag_snapshot_put_tensor(snap, b"misc.f32", tf.ptr)
+        assert lib.mag_snapshot_serialize(snap, path)
+        lib.mag_snapshot_free(snap)
+        tw.release(); tf.release()
+        snap = lib.mag_snapshot_deserialize(cpu_api.ctx, path)
+        assert snap
+        src_w, src_f = lib.mag_snapshot_get_tensor(snap, b"layer.weight"), lib.mag_snapshot_get_tensor(snap, b"misc.f32")
+        assert src_w and src_f
+
+        def upload(src, dim, r, n):
+            out = P()
+            assert to_device(gpu_api.ctx, src, dim, r, n, C.byref(out)) == 0
+            return R.Tensor(gpu_api, out.value)
+
+        whole = upload(src_w, -1, 0, 1)
+        assert np.array_equal(gpu_api.to_bits(whole), wb)
+        f = upload(src_f, -1, 0, 1)
+        assert np.array_equal(gpu_api.to_bits(f), f32b)
+        mid = upload(src_f, 1, 3, 5)                       # one of five slices of the middle dim of a rank-3 tensor
+        assert np.array_equal(gpu_api.to_bits(mid), f32b[:, 3:4, :])
+        rows = [upload(src_w, 0, r, ranks) for r in range(ranks)]       # column-sharded nn.Linear: rows of W
+        cols = [upload(src_w, 1, r, ranks) for r in range(ranks)]       # row-sharded: K slices of W
+        for r in range(ranks):
+            assert np.array_equal(gpu_api.to_bits(rows[r]), wb[r * (N // ranks):(r + 1) * (N // ranks)])
+            assert np.array_equal(gpu_api.to_bits(cols[r]), wb[:, r * (K // ranks):(r + 1) * (K // ranks)])
+        bad = P()
+        assert to_device(gpu_api.ctx, src_f, 2, 0, 2, C.byref(bad)) != 0            # 7 is not divisible by 2
+        # the column shards give the columns of the unsharded product
+        xb = O.f32_to_bits(dt, cases.gen_storage(rng, (M, K), 1.0))
+        x = gpu_api.from_bits(dt, xb)
+        wt = gpu_api.transpose(whole, 0, 1)
+        full = gpu_api.matmul(x, wt)
+        full_bits = gpu_api.to_bits(full)
+        for r in range(ranks):
+            rt = gpu_api.transpose(rows[r], 0, 1)
+            part = gpu_api.matmul(x, rt)
+            assert np.array_equal(gpu_api.to_bits(part), full_bits[:, r * (N // ranks):(r + 1) * (N // ranks)])
+            part.release(); rt.release()
+        for t in [full, wt, x, mid, f, whole] + rows + cols:
+            t.release()
+        lib.mag_tensor_decref(src_w); lib.mag_tensor_decref(src_f)
+        lib.mag_snapshot_free(snap)
+        ok = True
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+        cpu_api.close(not ok)
+        finish(gpu_api, ok)
+
+
 CASES = {"matmul_cast": test_matmul_and_cast_through_the_reference_api,
          "kv_append": test_kv_append_through_the_reference_api,
          "gated_mlp": test_gated_mlp_through_the_module_export,
+         "snapshot": test_snapshot_tensors_to_the_device,
          "gqa_views": test_gqa_broadcast_views_through_the_reference_api,
          "unsupported_op": test_unsupported_opcode_returns_a_status}
 

@@ -108,3 +108,11 @@ def test_kv_append_through_the_reference_api(deploy_dir, gpu):
 def test_gated_mlp_through_the_module_export(deploy_dir, gpu):
     """mag_b200_matmul_swiglu (additive export) against MATMUL, MATMUL, SILU, MUL on the reference CPU backend."""
     run_in_fresh_process("gated_mlp", deploy_dir)
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_snapshot_tensors_to_the_device(deploy_dir, gpu):
+    """.mag snapshot (written and mapped by the reference on its CPU context) -> "cuda:0": whole tensors and the shards of a
+    tensor-parallel weight, bit-compared; column shards reproduce the unsharded product."""
+    run_in_fresh_process("snapshot", deploy_dir)
