@@ -44,7 +44,8 @@ def plugin_handle(deploy_dir):
 def test_module_hooks_and_cookie(deploy_dir):
     h = plugin_handle(deploy_dir)
     for sym in ("mag_backend_module_hook_abi_cookie", "mag_backend_module_hook_init", "mag_backend_module_hook_shutdown",
-                "mag_b200_upload", "mag_b200_download", "mag_b200_synchronize"):
+                "mag_b200_upload", "mag_b200_download", "mag_b200_synchronize", "mag_b200_upload_async", "mag_b200_download_async",
+                "mag_b200_matmul_swiglu", "mag_b200_tensor_to_device", "mag_b200_status_of"):
         assert hasattr(h, sym), sym
     h.mag_backend_module_hook_abi_cookie.restype = C.c_uint32
     assert h.mag_backend_module_hook_abi_cookie() == (ord("M") | ord("A") << 8 | ord("G") << 16 | 1 << 24)
