@@ -196,6 +196,11 @@ void     magb200_launch_count_reset(void);
 /* Restrict routing (testing / profiling): 0 = automatic, otherwise a magb200_kernel_t that must be
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
+/* Decode-shaped products whose weight matrix has few 16-row tiles (the 1024-row o and down projections of a small model) run
+ * as clusters of up to `max_cluster` CTAs (1, 2 or 4; default 4) that split K once more and meet through distributed shared
+ * memory, so that more SMs stream weights. 1 switches the clusters off (tests compare the two). */
+int  magb200_set_decode_cluster(int max_cluster);
+
 /* The two-SM kernel can share the tiles of a partial last wave out among all CTA pairs along K (fp32 partial tiles in the
  * library's workspace, summed in a fixed order, so results are reproducible). mode 1 (default): only where it pays (few
  * left-over tiles, K >= 4096); 0: never; 2: whenever the shape allows (tests). */

@@ -70,17 +70,35 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
-int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster, Args &&...args) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (cluster > 1) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)cluster; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
     return MAGB200_OK;
+}
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    return launch_pdl_cluster(kernel, grid, block, smem, st, 1, static_cast<Args &&>(args)...);
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
@@ -246,16 +264,22 @@ __device__ __forceinline__ void stage_activations(const SkinnyArgs &a, int M, in
 }
 
 // KW warps of the CTA split the CTA's K range, RW = 8 / KW warps take different 16-row tiles.
+// CL > 1: a cluster of CL CTAs shares the same tiles and splits K once more (a weight matrix with few 16-row tiles, e.g.
+// the 1024-row o and down projections of a small model, otherwise keeps most SMs idle): CTA r of the cluster takes K slices
+// [r * KW, (r + 1) * KW), the CTAs r > 0 hand their sums to CTA 0 through distributed shared memory (two buffers alternating
+// by round, one cluster barrier per round), and CTA 0 adds them in rank order and stores.
 // Fragment bookkeeping (g = lane / 4, t = lane % 4): the thread loads K values [k, k+8) of weight rows
 // r0+g and r0+g+8 and of activation row g. Instruction 1 takes K values k+0..3, instruction 2 takes
 // k+4..7: slots (2t, 2t+1) <- first pair, slots (2t+8, 2t+9) <- second pair, the same in A and B.
-template <int DT, int KW>
+template <int DT, int KW, int CL>
 __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
     constexpr int RW = kWarps / KW;
     constexpr int kPre = 4;                                                  // weight steps loaded ahead of the activations
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t *xs = reinterpret_cast<uint16_t *>(smem);                      // [M][xstride]
     float *red = reinterpret_cast<float *>(smem + (size_t)M * xstride * 2);  // [KW][RW][128] when KW > 1
+    float *red2 = red + (KW > 1 ? kWarps * 128 : 0);                         // [2][CL - 1][RW][128] when CL > 1
+    const int cr = CL > 1 ? (int)cluster_rank() : 0;
 
     pdl_launch_dependents();
     const int split = blockIdx.y;
@@ -268,9 +292,9 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rw = warp / KW, kw = warp % KW;
     const int g = lane >> 2, t = lane & 3;
-    int per = (kc + KW - 1) / KW;
+    int per = (kc + KW * CL - 1) / (KW * CL);
     per = (per + 31) / 32 * 32;
-    const int ks = min(kc, kw * per), ke = min(kc, ks + per);
+    const int ks = min(kc, (cr * KW + kw) * per), ke = min(kc, ks + per);
     const int nfull = (ke - ks) >> 5;
     const uint16_t *xrow = xs + g * xstride;
     const bool has_x = g < M;
@@ -293,8 +317,8 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
     // 16-row tiles are dealt out evenly: unit u (a row-warp slot of some CTA) takes tiles [u*T/U, (u+1)*T/U).
     // Every warp of a CTA runs the same number of rounds (the K-slice reduction below has CTA barriers).
     const int64_t T = a.ngroups > 1 ? a.gtile0[a.ngroups] : (a.N + 15) / 16;
-    const int64_t U = (int64_t)gridDim.x * RW;
-    const int64_t u = (int64_t)blockIdx.x * RW + rw;
+    const int64_t U = (int64_t)(gridDim.x / CL) * RW;
+    const int64_t u = (int64_t)(blockIdx.x / CL) * RW + rw;
     const int64_t t_begin = u * T / U, t_end = (u + 1) * T / U;
     const int64_t rounds = (T + U - 1) / U;
 
@@ -381,7 +405,24 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_mma_kernel(const Skinny
             }
             __syncthreads();
         }
-        if (active && kw == 0) {
+        if constexpr (CL > 1) {
+            float *buf = red2 + (size_t)(round & 1) * (CL - 1) * RW * 128;
+            if (cr != 0 && kw == 0) {
+                const uint32_t local = (uint32_t)__cvta_generic_to_shared(buf + ((cr - 1) * RW + rw) * 128 + lane * 4);
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]) : "memory");
+            }
+            cluster_barrier();
+            if (cr == 0 && kw == 0) {
+#pragma unroll
+                for (int r = 0; r < CL - 1; ++r) {
+                    const float4 o = *reinterpret_cast<const float4 *>(buf + (r * RW + rw) * 128 + lane * 4);
+                    c[0] += o.x; c[1] += o.y; c[2] += o.z; c[3] += o.w;
+                }
+            }
+        }
+        if (active && kw == 0 && cr == 0) {
             // c[0], c[1]: weight row r0+g, tokens 2t, 2t+1;  c[2], c[3]: weight row r0+g+8
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -600,11 +641,18 @@ __global__ void __launch_bounds__(kThreads) skinny_finalize_kernel(const float *
 
 constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
 
+std::atomic<int> g_cluster_max{4};       // largest cluster the decode planner may use (1: never)
+// K values a warp must keep after the extra split. Measured at M = 1 (us, no cluster / 2 / 4 CTAs): o 1024 x 2048 3.46 / 2.94 /
+// 3.61, down 1024 x 3072 4.76 / 4.19 / 3.97, q 2048 x 1024 2.39 / 3.49: a cluster launch costs about a microsecond, which a
+// slice of 96 or more K values per warp earns back and a shorter one does not.
+std::atomic<int> g_cluster_min_k{96};
+
 struct Plan {
     bool km;       // K-major weights
     bool mma;      // K-major 16-bit weights through mma.sync
     bool async;    // ... with the cp.async ring (plenty of tiles)
     int KW;        // warps along K per CTA (mma)
+    int CL;        // CTAs of a cluster that split K once more (mma, few tiles)
     int64_t xstride;
     int R;         // rows per warp (km)
     int64_t kch;
@@ -628,6 +676,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     pl.km = km;
     pl.mma = false;
     pl.async = false;
+    pl.CL = 1;
     if (km && DT != MAGB200_F32) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
         // activation rows live in shared memory with a pitch of 64 bytes mod 128 so that the 8 row groups
@@ -705,7 +754,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
                 nsplit = best_ns;
                 kch = best_kch;
             }
-            pl.mma = true; pl.async = true; pl.KW = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
+            pl.mma = true; pl.async = true; pl.KW = 1; pl.CL = 1; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
             pl.xstride = (kch + 63) / 64 * 64 + 32;
             pl.smem = kAsyncRingBytes + (size_t)M * pl.xstride * 2;
             const int64_t other = (int64_t)nsplit * p.batch_total;
@@ -720,15 +769,21 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
         pl.xstride = (kch + 63) / 64 * 64 + 32;
 
-        pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0);
         const int RW = kWarps / KW;
         const int64_t blocks = (tiles + RW - 1) / RW;
         const int64_t other = (int64_t)nsplit * p.batch_total;
+        // fewer CTAs than SMs although every warp already has its own K slice: clusters split K once more
+        int CL = 1;
+        if (KW == kWarps)
+            while (CL < 4 && blocks * other * CL * 2 <= (int64_t)num_sms() * 2 && kch / (KW * CL * 2) >= g_cluster_min_k.load()) CL *= 2;
+        if (g_cluster_max.load() < CL) CL = g_cluster_max.load() < 1 ? 1 : g_cluster_max.load();
+        pl.CL = CL;
+        pl.smem = (size_t)M * pl.xstride * 2 + (KW > 1 ? (size_t)kWarps * 128 * 4 : 0) + (CL > 1 ? (size_t)2 * (CL - 1) * RW * 128 * 4 : 0);
         // many short CTAs (one or two tiles per warp) let the hardware scheduler even out the SMs
         int64_t want = (int64_t)num_sms() * 32;
         want = (want + other - 1) / other;
         if (want < 1) want = 1;
-        pl.gridx = (unsigned)(blocks < want ? blocks : want);
+        pl.gridx = (unsigned)(blocks < want ? blocks : want) * (unsigned)CL;
         return pl.nsplit <= 65535;
     }
     if (km) {
@@ -827,9 +882,16 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
         if constexpr (DT != MAGB200_F32) {
 #define LAUNCH_KW(KWV)                                                                                   \
     case KWV:                                                                                            \
-        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
-        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV, 1>, pl.smem))) return rc;                       \
+        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV, 1>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
         break;
+            if (pl.CL == 2) {
+                if ((rc = set_smem(skinny_km_mma_kernel<DT, kWarps, 2>, pl.smem))) return rc;
+                if ((rc = launch_pdl_cluster(skinny_km_mma_kernel<DT, kWarps, 2>, grid, dim3(kThreads), pl.smem, st, 2, a, M, (int)pl.xstride))) return rc;
+            } else if (pl.CL == 4) {
+                if ((rc = set_smem(skinny_km_mma_kernel<DT, kWarps, 4>, pl.smem))) return rc;
+                if ((rc = launch_pdl_cluster(skinny_km_mma_kernel<DT, kWarps, 4>, grid, dim3(kThreads), pl.smem, st, 4, a, M, (int)pl.xstride))) return rc;
+            } else
             switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
 #undef LAUNCH_KW
         }
@@ -910,6 +972,11 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
     pc.N = tiles * 16;
     Plan pl;
     if (!make_plan<DT>(pc, pl) || !pl.mma || pl.async || pl.nsplit != 1) return 1;   // not applicable: the caller launches one by one
+    // the group's results are promised to be the bits of the separate calls: every member alone must cut K the same way
+    for (int i = 0; i < count; ++i) {
+        Plan one;
+        if (!make_plan<DT>(ps[i], one) || !one.mma || one.async || one.nsplit != 1 || one.KW != pl.KW || one.CL != pl.CL) return 1;
+    }
     a.A = pc.A; a.B = nullptr; a.C = nullptr; a.partial = nullptr;
     a.N = pc.N; a.K = pc.K; a.sAm = pc.sAm; a.sAk = pc.sAk; a.ldb = 0;
     a.kch = pl.kch; a.nsplit = 1; a.nbatch = 0; a.batch_total = 1;
@@ -920,9 +987,16 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
     int rc = MAGB200_OK;
 #define LAUNCH_KW(KWV)                                                                                   \
     case KWV:                                                                                            \
-        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV>, pl.smem))) return rc;                          \
-        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, KWV, 1>, pl.smem))) return rc;                       \
+        if ((rc = launch_pdl(skinny_km_mma_kernel<DT, KWV, 1>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc; \
         break;
+    if (pl.CL == 2) {
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, kWarps, 2>, pl.smem))) return rc;
+        if ((rc = launch_pdl_cluster(skinny_km_mma_kernel<DT, kWarps, 2>, grid, dim3(kThreads), pl.smem, st, 2, a, M, (int)pl.xstride))) return rc;
+    } else if (pl.CL == 4) {
+        if ((rc = set_smem(skinny_km_mma_kernel<DT, kWarps, 4>, pl.smem))) return rc;
+        if ((rc = launch_pdl_cluster(skinny_km_mma_kernel<DT, kWarps, 4>, grid, dim3(kThreads), pl.smem, st, 4, a, M, (int)pl.xstride))) return rc;
+    } else
     switch (pl.KW) { LAUNCH_KW(1) LAUNCH_KW(2) LAUNCH_KW(4) LAUNCH_KW(8) }
 #undef LAUNCH_KW
     count_launch();
@@ -930,6 +1004,8 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
     return MAGB200_OK;
 }
 }  // namespace
+
+void set_decode_cluster_max(int max_cluster) { g_cluster_max.store(max_cluster < 1 ? 1 : (max_cluster > 4 ? 4 : max_cluster)); }
 
 // Several decode-shaped products with the same activation rows in one launch: r_i = x . y_i. Returns 1 when the group cannot
 // run as one launch (mixed layouts, a K split, too many tiles: those shapes are better off alone anyway).

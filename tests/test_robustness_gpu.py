@@ -70,6 +70,38 @@ def test_shared_last_wave(gpu, M, N, K, layout, dname):
         t.release()
 
 
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 4104), (48, 8192)])
+def test_decode_clusters_split_k_like_one_cta(gpu, M, N, K):
+    """Weight matrices with few 16-row tiles run as clusters of 2 or 4 CTAs that split K and meet through distributed shared
+    memory: against fp64 within the usual bar, reproducible, and within two roundings of the one-CTA result."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(33)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.05)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    truth, scale = xf @ wf.T, np.abs(xf) @ np.abs(wf).T
+    got = {}
+    try:
+        for cl in (1, 2, 4):
+            mb.check(L.magb200_set_decode_cluster(cl))
+            r1, r2 = tx @ tw.T, tx @ tw.T
+            assert mb.last_kernel() in ("skinny", "skinny_splitk")
+            got[cl] = r1.to_bits()
+            assert np.array_equal(got[cl], r2.to_bits())
+            m = O.error_metrics(dt, got[cl], truth, scale)
+            assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, (cl, m)
+            r1.release(); r2.release()
+    finally:
+        mb.check(L.magb200_set_decode_cluster(4))
+    a, b = O.bits_to_f64(dt, got[1]), O.bits_to_f64(dt, got[4])
+    assert np.all(np.abs(a - b) <= 2 * unit_roundoff(dt) * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -20 * scale)
+    for t in (tx, tw):
+        t.release()
+    assert L.magb200_set_decode_cluster(3) != 0
+
+
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("dname", ["bf16", "f16"])
 def test_grouped_decode_matches_separate_calls(gpu, M, dname):
