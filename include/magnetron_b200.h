@@ -180,7 +180,10 @@ int  magb200_matmul_swiglu(int device, const magb200_view_t *x, const magb200_vi
 /* `count` (1..4) matmuls that share their first operand: r_i = x @ y_i, e.g. the q, k and v projections or gate and up of a
  * decode step, which magnetron dispatches as consecutive MAG_OP_MATMULs with the same in[0] (examples/qwen3/model.py:109-111,
  * :48-49). Decode-shaped groups (M <= 8, 16-bit K-major weights, no K split) run as ONE launch whose 16-row weight tiles
- * span all the y_i; anything else is executed product by product. Results are bit-identical to `count` magb200_matmul calls. */
+ * span all the y_i; anything else is executed product by product. Each result is the fp32-accumulated product rounded once,
+ * as from magb200_matmul; it has the same bits as a separate call whenever the group and the separate call cut K into the same
+ * number of slices (always for fewer than 297 row tiles in total, e.g. q/k/v of a small model), otherwise the fp32 sums are
+ * taken in another order. */
 int  magb200_matmul_grouped(int device, const magb200_view_t *x, int count, const magb200_view_t *const *ys,
                             const magb200_view_t *const *rs);
 

@@ -765,7 +765,10 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             return pl.nsplit <= 65535;
         }
         int KW = 1;
-        while (KW < kWarps && tiles * KW * nsplit * p.batch_total < warps_wanted && kch / (KW * 2) >= 128) KW *= 2;
+        // more warps along K while the GPU has room for them: past its resident capacity (16 warps per SM) the extra CTAs
+        // would only queue behind the first wave (384 tiles x 8 warps: 6.0 us, x 4 warps in one wave: see the measurements
+        // beside g_cluster_min_k)
+        while (KW < kWarps && tiles * KW * 2 * nsplit * p.batch_total <= warps_wanted && kch / (KW * 2) >= 128) KW *= 2;
         pl.mma = true; pl.KW = KW; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
         pl.xstride = (kch + 63) / 64 * 64 + 32;
 
@@ -972,11 +975,8 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
     pc.N = tiles * 16;
     Plan pl;
     if (!make_plan<DT>(pc, pl) || !pl.mma || pl.async || pl.nsplit != 1) return 1;   // not applicable: the caller launches one by one
-    // the group's results are promised to be the bits of the separate calls: every member alone must cut K the same way
-    for (int i = 0; i < count; ++i) {
-        Plan one;
-        if (!make_plan<DT>(ps[i], one) || !one.mma || one.async || one.nsplit != 1 || one.KW != pl.KW || one.CL != pl.CL) return 1;
-    }
+    // (a member launched alone may cut K into a different number of slices than the group does: same products, another
+    // order of the fp32 sums)
     a.A = pc.A; a.B = nullptr; a.C = nullptr; a.partial = nullptr;
     a.N = pc.N; a.K = pc.K; a.sAm = pc.sAm; a.sAk = pc.sAk; a.ldb = 0;
     a.kch = pl.kch; a.nsplit = 1; a.nbatch = 0; a.batch_total = 1;

@@ -105,8 +105,8 @@ def test_decode_clusters_split_k_like_one_cta(gpu, M, N, K):
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("dname", ["bf16", "f16"])
 def test_grouped_decode_matches_separate_calls(gpu, M, dname):
-    """q/k/v and gate/up of a decode step as one grouped launch each: bit-identical to the separate matmuls, also when a
-    weight's row count is not a multiple of the 16-row tile, and a group that cannot be one launch (a prefill-shaped x)
+    """q/k/v and gate/up of a decode step as one grouped launch each: bit-identical to the separate matmuls when both cut K the
+    same way (within two roundings otherwise), also when a weight's row count is not a multiple of the 16-row tile, and a group that cannot be one launch (a prefill-shaped x)
     still gives the separate calls' results."""
     dt = cases.DTYPES[dname]
     L = mb.lib()
@@ -128,8 +128,14 @@ def test_grouped_decode_matches_separate_calls(gpu, M, dname):
         mb.check(L.magb200_matmul_grouped(gpu, C.byref(tx.view_struct()), len(Ns), ys, rs))
         assert L.magb200_launch_count() == 1, "the group did not run as one launch"
         mb.synchronize(gpu)
+        same_slicing = sum((N + 15) // 16 for N in Ns) <= 296      # else the group cuts K into fewer slices than a member alone
         for o, wnt in zip(outs, want):
-            assert np.array_equal(o.to_bits(), wnt)
+            if same_slicing:
+                assert np.array_equal(o.to_bits(), wnt)
+            else:
+                a, b = O.bits_to_f64(dt, o.to_bits()), O.bits_to_f64(dt, wnt)
+                assert np.all(np.abs(a - b) <= 2 * unit_roundoff(dt) * np.maximum(np.abs(a), np.abs(b)) + 1e-3 * unit_roundoff(dt) * K)
+                assert np.mean(a != b) < 0.2
         for t in ws + outs:
             t.release()
     # prefill-shaped: falls back to one matmul per product
