@@ -74,7 +74,7 @@ static size_t size_class(size_t bytes) {
 // ---- per-device state ---------------------------------------------------------------------------
 constexpr int kMaxDevices = 16;
 constexpr size_t kStatusBytes = 4096;
-constexpr int kSplitFlagWord = 8;                          // "operands cannot be split" word of the float32 tensor-core path
+constexpr int kSplitFlagWord = 8;                          // "operands cannot be split" word of the float32 tensor-core path (+ a CTA counter)
 constexpr int kCounterWord0 = 64, kCounterTiles = 256;   // counters of the two-SM kernel's shared last wave live in the status buffer
 struct AddrRange { uintptr_t lo, hi; };
 struct DeviceState {
@@ -458,7 +458,7 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
                 ordered_point(d);
                 int *unsafe = d.status + kSplitFlagWord;
                 char *planes = reinterpret_cast<char *>(d.scratch);
-                MAGB200_CUDA_TRY(cudaMemsetAsync(unsafe, 0, sizeof(int), d.stream));
+                // `unsafe` is clear here: the stand-by launch of the call that raised it has lowered it again
                 int rc = launch_split3(g, planes, planes + bytes_a, unsafe, d.stream);
                 if (!rc) rc = launch_gemm_f32x3(g, planes, planes + bytes_a, unsafe, d.status, d.stream);
                 if (!rc) rc = launch_gemm_simt(g, d.stream, nullptr, 0, unsafe);

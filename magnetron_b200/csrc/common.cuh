@@ -151,8 +151,9 @@ struct GemmProblem {
 };
 
 // kernel launchers (each returns a magb200_status_t); `stream` is the device's launch stream
-// `run_if_set` (optional): a device word read at kernel start; the launch does nothing when it is zero.
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, const int *run_if_set = nullptr);
+// `run_if_set` (optional): two device words. The launch does nothing when word 0 is zero; when it ran, its last CTA clears
+// word 0 again (word 1 counts the finished CTAs).
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *run_if_set = nullptr);
 size_t simt_scratch_bytes(const GemmProblem &p);
 bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled);

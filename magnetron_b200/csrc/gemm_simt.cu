@@ -58,8 +58,11 @@ __device__ __forceinline__ float fold_low(float total, float low) {
 template <int DT, bool AKF, bool BNF>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nsplit, int64_t kchunk, float *__restrict__ partial,
-                 const int *__restrict__ run_if_set) {
-    if (run_if_set && *run_if_set == 0) return;        // stand-by launch behind the split-operand tensor-core kernel
+                 int *run_if_set) {
+    // Stand-by launch behind the split-operand tensor-core kernel: runs only when the split pass raised the word. The word
+    // is lowered again by the last CTA of this launch to finish (run_if_set[1] counts them), by which time every CTA of
+    // both kernels has read it, so the next call finds it clear without a memset of its own.
+    if (run_if_set && *reinterpret_cast<volatile int *>(run_if_set) == 0) return;
     extern __shared__ __align__(16) unsigned char simt_smem[];
     typedef float Tile[BK][BM + PAD];
     Tile *As = reinterpret_cast<Tile *>(simt_smem);                   // As[2][BK][BM + PAD]
@@ -235,6 +238,17 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
             }
         }
     }
+    if (run_if_set) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(run_if_set + 1, 1) == (int)gridDim.x - 1) {
+                run_if_set[1] = 0;
+                run_if_set[0] = 0;
+                __threadfence();
+            }
+        }
+    }
 }
 
 // partial[nsplit][2][elems] -> C[elems]: the splits' (total, low) pairs added in split order without losing the low parts
@@ -296,7 +310,7 @@ size_t simt_scratch_bytes(const GemmProblem &p) {
     return pl.nsplit > 1 ? (size_t)pl.nsplit * 2 * (size_t)(p.batch_total * p.M * p.N) * sizeof(float) : 0;
 }
 
-int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, size_t scratch_bytes, const int *run_if_set) {
+int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, size_t scratch_bytes, int *run_if_set) {
     SimtPlan pl = plan_simt(p);
     if (pl.tiles <= 0) return MAGB200_OK;
     if (run_if_set) scratch = nullptr;                // the stand-by form never splits K: its finalize pass would be unconditional
