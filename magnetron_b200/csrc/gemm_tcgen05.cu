@@ -124,7 +124,8 @@ __device__ __forceinline__ void tma_store_5d(const CUtensorMap *map, uint32_t sr
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the newest bulk store of this thread have read their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -764,14 +765,13 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     tmem_ld_32x32(tb + h * 32, g);
                     tmem_ld_32x32(tb + BN2 / 2 + h * 32, up);
                     tmem_ld_wait();
-                    if (h == 0) {                        // the previous tile's bulk store has read the patch
-                        if (lane == 0) tma_store_wait_read();
-                        __syncwarp();
-                    } else {                             // the accumulator has been read completely: hand it back
+                    if (h == 1) {                        // the accumulator has been read completely: hand it back
                         tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
                     }
+                    if (lane == 0) tma_store_wait_read_but_one();   // the store that last used this half of the patch has read it
+                    __syncwarp();
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         uint4 o;
@@ -783,13 +783,13 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                                                pack2_rn<DT>(__uint_as_float(up[8 * v + 4]), __uint_as_float(up[8 * v + 5])));
                         o.w = swiglu_pack2<DT>(pack2_rn<DT>(__uint_as_float(g[8 * v + 6]), __uint_as_float(g[8 * v + 7])),
                                                pack2_rn<DT>(__uint_as_float(up[8 * v + 6]), __uint_as_float(up[8 * v + 7])));
-                        *reinterpret_cast<uint4 *>(stg + lane * C::kEpiPitch + (((v + 4 * h) ^ (lane & 7)) << 4)) = o;
+                        *reinterpret_cast<uint4 *>(stg + h * 2048 + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = o;
                     }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && row0 < args.M && n0 + chalf * 64 + h * 32 < args.N)
+                        tma_store_5d(&tmC, smem_u32(stg + h * 2048), (int)(n0 + chalf * 64 + h * 32), (int)row0, (int)batch, 0, 0);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0 && row0 < args.M && n0 + chalf * 64 < args.N)
-                    tma_store_5d(&tmC, smem_u32(stg), (int)(n0 + chalf * 64), (int)row0, (int)batch, 0, 0);
                 continue;
             }
             // This warp's 32 x 128 block of a partial tile in scratch: [32-column chunk][accumulator register][lane], so that
@@ -833,7 +833,48 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 __threadfence();                           // acquire: the contributions are read after the counter
             }
             const float *contrib = args.sk_partial + (size_t)(w.tail_idx < 0 ? 0 : w.tail_idx) * args.tail_slots * (size_t)(2 * BM * BN2) + warp_block;
-            if (vec_ok) {
+            if constexpr (kTmaStore) {
+                // Bulk-store epilogue: the warp's 4 KB patch is two halves of 32 rows x 32 columns, each laid out as a
+                // 64-byte-swizzled box (row = lane, 16-byte chunk c kept at chunk c ^ ((row >> 1) & 3): conflict-free stores).
+                // A half is converted and handed to one bulk tensor store while the store of the other half is still reading
+                // its shared memory and the next TMEM load is in flight; rows beyond M and columns beyond N are clipped by TMA.
+                unsigned char *stg = tiles_ptr + (size_t)C::kStages * C::kStageBytes + (size_t)(warp - 2) * C::kEpiWarpBytes;
+                const int64_t row0 = tm * 2 * BM + (int64_t)rank * BM + quarter * 32;
+                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2 + chalf * (BN2 / 2);
+                uint32_t ra[32];
+                tmem_ld_32x32(tbase, ra);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN2 / 2; c0 += 32) {
+                    unsigned char *half = stg + ((c0 >> 5) & 1) * 2048;
+                    tmem_ld_wait();
+                    uint4 o[4];
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        o[v].x = pack2_rn<DT>(__uint_as_float(ra[8 * v + 0]), __uint_as_float(ra[8 * v + 1]));
+                        o[v].y = pack2_rn<DT>(__uint_as_float(ra[8 * v + 2]), __uint_as_float(ra[8 * v + 3]));
+                        o[v].z = pack2_rn<DT>(__uint_as_float(ra[8 * v + 4]), __uint_as_float(ra[8 * v + 5]));
+                        o[v].w = pack2_rn<DT>(__uint_as_float(ra[8 * v + 6]), __uint_as_float(ra[8 * v + 7]));
+                    }
+                    if (c0 + 32 < BN2 / 2) {
+                        tmem_ld_32x32(tbase + c0 + 32, ra);          // in flight during the write-out
+                    } else {
+                        // the accumulator has been read completely: hand it back before the last write-out, so the next
+                        // tile's MMAs do not wait for this tile's stores
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
+                    }
+                    if (lane == 0) tma_store_wait_read_but_one();   // the store that last used this half has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<uint4 *>(half + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = o[v];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && row0 < args.M && n0 + chalf * (BN2 / 2) + c0 < args.N)
+                        tma_store_5d(&tmC, smem_u32(half), (int)(n0 + chalf * (BN2 / 2) + c0), (int)row0, (int)batch, 0, 0);
+                }
+            } else if (vec_ok) {
                 // Staged epilogue: TMEM -> registers -> this warp's shared-memory patch (row = lane, 16-byte chunk c of a row
                 // kept at chunk c ^ (row & 7), conflict-free both ways), then 8 lanes write one row's 128 contiguous bytes, so
                 // global and peer stores are whole 128-byte segments. The next TMEM loads are issued before the write-out.
@@ -846,10 +887,6 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN2 / 2; c0 += C::kEpiCols) {
                     tmem_ld_wait();
-                    if constexpr (kTmaStore) {          // the previous bulk store has read the patch before it is overwritten
-                        if (lane == 0) tma_store_wait_read();
-                        __syncwarp();
-                    }
                     for (int j = 1; kShare && j < w.parts; ++j) {      // contributions in run order: the sum does not depend on timing
                         const float *pj = contrib + (size_t)(j - 1) * (size_t)(2 * BM * BN2) + (size_t)c0 * 32 + lane;
 #pragma unroll
@@ -882,14 +919,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                         __syncwarp();
                         if (lane == 0) mbar_arrive_remote_relaxed(tempty_leader0 + 8u * acc);
                     }
-                    if constexpr (kTmaStore) {
-                        // the patch is laid out exactly as a 128-byte-swizzled 64 x 32 box: make the writes visible to the async
-                        // proxy, then one lane stores the whole patch; rows beyond M and columns beyond N are clipped by TMA
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0 && row0 < args.M && n0 + chalf * (BN2 / 2) + c0 < args.N)
-                            tma_store_5d(&tmC, smem_u32(stg), (int)(n0 + chalf * (BN2 / 2) + c0), (int)row0, (int)batch, 0, 0);
-                    } else {
+                    {
                     __syncwarp();
                     const int64_t col = n0 + chalf * (BN2 / 2) + c0 + (lane & 7) * 8;
 #pragma unroll
@@ -1287,6 +1317,7 @@ struct OperandDesc {
     int64_t bext[kMaxBatchDims], bstride[kMaxBatchDims];
     int has[kMaxBatchDims];
     uint32_t box_inner, box_outer;
+    int swizzle64 = 0;                                // 1: 64-byte swizzle (box_inner of 32 elements), else 128-byte
 };
 
 bool operand_ok(const OperandDesc &o) {
@@ -1311,7 +1342,7 @@ struct MapKey {
     int64_t bext[kMaxBatchDims], bstride[kMaxBatchDims];
     int32_t has[kMaxBatchDims];
     uint32_t box_inner, box_outer;
-    int32_t dtype;
+    int32_t dtype, swizzle64;
 };
 constexpr int kMapCacheSlots = 128;
 struct MapCache {
@@ -1333,7 +1364,7 @@ int encode(const OperandDesc &o, int dtype, CUtensorMap *out) {
     memset(&k, 0, sizeof(k));             // padding bytes take part in the hash
     k.base = o.base; k.inner_extent = o.inner_extent; k.outer_extent = o.outer_extent; k.outer_pitch = o.outer_pitch;
     for (int d = 0; d < kMaxBatchDims; ++d) { k.bext[d] = o.bext[d]; k.bstride[d] = o.has[d] ? o.bstride[d] : 0; k.has[d] = o.has[d]; }
-    k.box_inner = o.box_inner; k.box_outer = o.box_outer; k.dtype = dtype;
+    k.box_inner = o.box_inner; k.box_outer = o.box_outer; k.dtype = dtype; k.swizzle64 = o.swizzle64;
     const uint64_t h = hash_key(k);
     const int s0 = (int)(h % kMapCacheSlots), s1 = (int)((h >> 20) % kMapCacheSlots);   // two candidate slots per key
     for (int s : {s0, s1})
@@ -1366,7 +1397,8 @@ int encode_uncached(const OperandDesc &o, int dtype, CUtensorMap *out) {
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = fn(out, dtype == MAGB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
                     const_cast<void *>(o.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    o.swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with %d (dims %llu %llu %llu %llu %llu, strides %llu %llu %llu %llu, box %u %u)", (int)r,
                   (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2], (unsigned long long)dims[3],
@@ -1612,14 +1644,14 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
         args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
         for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
     }
-    // the result as TMA sees it: [batch][M][N] contiguous -> boxes of 64 columns x 32 rows for the epilogue's bulk stores
+    // the result as TMA sees it: [batch][M][N] contiguous -> boxes of 32 columns x 32 rows (64-byte swizzle) for the epilogue's bulk stores
     CUtensorMap tcm;
     const CUtensorMap *tc = nullptr;
     if (!scatter && p.N % 8 == 0) {
         OperandDesc c;
         memset(&c, 0, sizeof(c));
         c.base = p.C; c.inner_extent = p.N; c.outer_extent = p.M; c.outer_pitch = p.N;
-        c.box_inner = 64; c.box_outer = 32;
+        c.box_inner = 32; c.box_outer = 32; c.swizzle64 = 1;
         for (int d = 0; d < kMaxBatchDims; ++d) { c.bext[d] = 1; c.bstride[d] = 0; c.has[d] = 0; }
         if (p.batch_total > 1) { c.bext[kMaxBatchDims - 1] = p.batch_total; c.bstride[kMaxBatchDims - 1] = p.M * p.N; c.has[kMaxBatchDims - 1] = 1; }
         if (operand_ok(c) && encode(c, p.dtype, &tcm) == MAGB200_OK) tc = &tcm;
@@ -1630,12 +1662,12 @@ int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit
 
 // ---- gated MLP: out = silu(x @ Wg) * (x @ Wu) in one launch -----------------------------------------------------------------
 namespace {
-// the result [batch][M][N] as boxes of 64 columns x 32 rows for the epilogue's bulk stores
+// the result [batch][M][N] as boxes of 32 columns x 32 rows (64-byte swizzle) for the epilogue's bulk stores
 bool describe_result(const GemmProblem &p, OperandDesc &c) {
     if (p.N % 8) return false;
     memset(&c, 0, sizeof(c));
     c.base = p.C; c.inner_extent = p.N; c.outer_extent = p.M; c.outer_pitch = p.N;
-    c.box_inner = 64; c.box_outer = 32;
+    c.box_inner = 32; c.box_outer = 32; c.swizzle64 = 1;
     for (int d = 0; d < kMaxBatchDims; ++d) { c.bext[d] = 1; c.bstride[d] = 0; c.has[d] = 0; }
     if (p.batch_total > 1) { c.bext[kMaxBatchDims - 1] = p.batch_total; c.bstride[kMaxBatchDims - 1] = p.M * p.N; c.has[kMaxBatchDims - 1] = 1; }
     return operand_ok(c);
