@@ -199,6 +199,11 @@ void     magb200_launch_count_reset(void);
 /* Restrict routing (testing / profiling): 0 = automatic, otherwise a magb200_kernel_t that must be
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
+/* 16-bit products with K >= 1024 whose output has at most 74 tiles of 128 x 128 (e.g. 512 x 2048 x 2048) run as clusters of
+ * two CTAs that split K and exchange halves of their fp32 accumulators through distributed shared memory, so twice as many
+ * SMs work (default on; 0 keeps one CTA per tile: tests compare the two). */
+int  magb200_set_small_output_split(int on);
+
 /* Decode-shaped products whose weight matrix has few 16-row tiles (the 1024-row o and down projections of a small model) run
  * as clusters of up to `max_cluster` CTAs (1, 2 or 4; default 4) that split K once more and meet through distributed shared
  * memory, so that more SMs stream weights. 1 switches the clusters off (tests compare the two). */

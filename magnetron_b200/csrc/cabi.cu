@@ -1113,6 +1113,10 @@ int magb200_multimem_reduce_broadcast(int device, void *cuda_stream, const void 
 int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }
+int magb200_set_small_output_split(int on) {
+    set_split_small(on);
+    return MAGB200_OK;
+}
 int magb200_set_decode_cluster(int max_cluster) {
     if (max_cluster != 1 && max_cluster != 2 && max_cluster != 4) { set_error("set_decode_cluster: 1, 2 or 4"); return MAGB200_ERR_INVALID_ARG; }
     set_decode_cluster_max(max_cluster);

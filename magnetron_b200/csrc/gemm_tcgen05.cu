@@ -163,6 +163,20 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
 // Tile order: tiles are walked in groups of kGroupM tile rows, column by column inside a group, so the CTAs that run
 // at the same time share a few A row panels and a band of B column panels that together fit in L2 (walking N fastest over
 // a wide N would stream all of B once per wave).
@@ -191,10 +205,20 @@ template <int BN> struct Cfg {
     static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * kEpiWarpBytes;
 };
 
-template <int BN, int DT>
+// kSplit2: launched as clusters of two CTAs, one tile per cluster: CTA r walks the r-th half of the K blocks, then each CTA
+// keeps the half of the tile's columns it owns, sends the other half of its fp32 accumulator to its peer through
+// distributed shared memory (the peer's stage buffers, idle by then), adds what it received and stores its columns. For
+// outputs with so few tiles that most SMs would idle (512 x 2048 x 2048: 64 tiles of 128 x 128 become 128 CTAs).
+template <int BN, int DT, bool kSplit2 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
     using C = Cfg<BN>;
+    const uint32_t krank = kSplit2 ? cluster_ctarank() : 0u;
+    const int kb_half = (args.num_kb + 1) >> 1;
+    const int kb_begin = kSplit2 ? (int)krank * kb_half : 0;
+    const int kb_end = kSplit2 ? (kb_begin + kb_half < args.num_kb ? kb_begin + kb_half : args.num_kb) : args.num_kb;
+    const int64_t first_tile = kSplit2 ? (int64_t)(blockIdx.x >> 1) : (int64_t)blockIdx.x;
+    const int64_t tile_step = kSplit2 ? args.total_tiles : (int64_t)gridDim.x;     // split form: one tile per cluster
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;             // 1024-byte alignment for the 128B swizzle
@@ -235,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x) {
+            for (int64_t tile = first_tile; ok && tile < args.total_tiles; tile += tile_step) {
                 int64_t batch, tm, tn;
                 decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
                 const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
@@ -251,7 +275,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 // TMA coordinates are fastest-dim first: {inner, outer, b2, b1, b0}
                 const int a2 = args.a_has[2] ? bc[2] : 0, a1 = args.a_has[1] ? bc[1] : 0, a0 = args.a_has[0] ? bc[0] : 0;
                 const int b2 = args.b_has[2] ? bc[2] : 0, b1 = args.b_has[1] ? bc[1] : 0, b0 = args.b_has[0] ? bc[0] : 0;
-                for (int kb = 0; kb < args.num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                     if (kb == args.skip_kb && tile == (int64_t)blockIdx.x) {   // test hook: this stage is never armed, its consumer's wait runs out
                         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -280,6 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
             }
         }
+        if constexpr (kSplit2) { cluster_sync_all(); cluster_sync_all(); }   // the two meeting points of the epilogue warps
     } else if (warp == 1) {
         // ===================== MMA issuer (one thread) =====================
         if (lane == 0) {
@@ -296,12 +321,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0;
             uint32_t titer = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
+            for (int64_t tile = first_tile; ok && tile < args.total_tiles; tile += tile_step, ++titer) {
                 const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * acc, acc_phase ^ 1u, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < args.num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(full0 + 8u * stage, phase, abort_flag, args.wait_limit_ns)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t sa = tiles + (uint32_t)stage * C::kStageBytes;
@@ -310,7 +335,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t ad = make_smem_desc(sa + k * a_step, a_lbo, 1024u);
                         const uint64_t bd = make_smem_desc(sb + k * b_step, b_lbo, 1024u);
-                        tcgen05_mma_f16(tmem_d, ad, bd, idesc, (kb | k) ? 1u : 0u);
+                        tcgen05_mma_f16(tmem_d, ad, bd, idesc, ((kb - kb_begin) | k) ? 1u : 0u);
                     }
                     tcgen05_commit(empty0 + 8u * stage);   // stage is free once these MMAs have read it
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -318,6 +343,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (ok) tcgen05_commit(tfull0 + 8u * acc);  // accumulator complete
             }
         }
+        if constexpr (kSplit2) { cluster_sync_all(); cluster_sync_all(); }
     } else {
         // ===================== epilogue (4 warps, 32 TMEM lanes each) =====================
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
@@ -325,7 +351,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         bool ok = true;
         const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15u) == 0);
         const bool staged = args.total_tiles > (int64_t)gridDim.x || args.scatter_ranks > 0;
-        for (int64_t tile = blockIdx.x; ok && tile < args.total_tiles; tile += gridDim.x, ++titer) {
+        for (int64_t tile = first_tile; ok && tile < args.total_tiles; tile += tile_step, ++titer) {
             const uint32_t acc = titer & 1u, acc_phase = (titer >> 1) & 1u;
             int64_t batch, tm, tn;
             decode_tile(tile, args.tiles_m, args.tiles_n, batch, tm, tn);
@@ -334,6 +360,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // every lane waits (each needs the acquire), then the warp agrees on one outcome so that the
             // warp-wide tcgen05.ld below is never reached by a partial warp
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull0 + 8u * acc, acc_phase, abort_flag, args.wait_limit_ns));
+            if constexpr (kSplit2) {
+                // both halves of K are complete in the two CTAs' TMEM and nobody reads the stage buffers any more
+                tcgen05_fence_after();
+                cluster_sync_all();
+                constexpr int kOwn = BN / 2;                                  // columns this CTA finishes: [krank * kOwn, +kOwn)
+                const uint32_t tb = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+                const uint32_t slot = (uint32_t)(quarter * 32 + lane) * 4u;   // element (row, col) of a half: (col * 128 + row) * 4 bytes
+                if (ok) {
+                    const uint32_t remote = map_to_cta(tiles, krank ^ 1u);
+#pragma unroll 1
+                    for (int c = 0; c < kOwn; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tb + (krank ^ 1u) * kOwn + c, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + (uint32_t)(c + j) * 512u + slot), "r"(r[j]) : "memory");
+                    }
+                }
+                cluster_sync_all();                                           // the peer's half of my columns has arrived
+                if (ok) {
+                    uint16_t *crow = output_row(args, batch, row < args.M ? row : 0) + n0 + krank * kOwn;
+#pragma unroll 1
+                    for (int c = 0; c < kOwn; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tb + krank * kOwn + c, r);
+                        tmem_ld_wait();
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            f[j] = __uint_as_float(r[j]) + *reinterpret_cast<const float *>(tiles_ptr + (size_t)(c + j) * 512 + slot);
+                        if (row < args.M) {
+                            const int64_t col0 = n0 + krank * kOwn + c;
+                            if (vec_ok) {
+#pragma unroll
+                                for (int v = 0; v < 4; ++v)
+                                    if (col0 + 8 * v < args.N) {
+                                        uint4 o;
+                                        o.x = pack2_rn<DT>(f[8 * v + 0], f[8 * v + 1]);
+                                        o.y = pack2_rn<DT>(f[8 * v + 2], f[8 * v + 3]);
+                                        o.z = pack2_rn<DT>(f[8 * v + 4], f[8 * v + 5]);
+                                        o.w = pack2_rn<DT>(f[8 * v + 6], f[8 * v + 7]);
+                                        *reinterpret_cast<uint4 *>(crow + c + 8 * v) = o;
+                                    }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < args.N) store_from_f32<DT>(crow, c + j, f[j]);
+                            }
+                        }
+                    }
+                }
+                break;                                                        // one tile per cluster
+            }
             if (!ok) break;
             tcgen05_fence_after();
             if (vec_ok && !staged) {
@@ -483,16 +563,6 @@ template <int KSUB> struct Cfg2 {
     static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256 + kEpiWarps * kEpiWarpBytes;
 };
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -501,9 +571,6 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 // has nothing to publish, and with the fence every tile paid a store round trip before the next MMA could start.
 __device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
 __device__ __forceinline__ void tma_load_5d_2sm(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
                                                 int c0, int c1, int c2, int c3, int c4) {
@@ -1459,6 +1526,7 @@ int pick_bn(const GemmProblem &p) {
 std::atomic<uint64_t> g_wait_limit_ns{1000ull * 1000ull * 1000ull};
 std::atomic<int> g_skip_kb_once{-1};      // consumed by the next tensor-core launch
 std::atomic<int> g_balance_tail{1};       // sharing of a partial last wave along K: 0 off, 1 when it pays, 2 whenever possible
+std::atomic<int> g_split_small{1};        // one-CTA kernel: CTA pairs split K when the output has few tiles (0: never)
 
 // cudaFuncSetAttribute applies to the current device only, so the opt-in to more than 48 KB of dynamic shared memory is
 // remembered per (kernel, device): bit d of `done` is set once device d has it.
@@ -1477,6 +1545,34 @@ int ensure_smem_optin(K kernel, size_t bytes, std::atomic<uint32_t> &done) {
 void fill_knobs(TcArgs &args) {
     args.wait_limit_ns = g_wait_limit_ns.load();
     args.skip_kb = g_skip_kb_once.exchange(-1);
+}
+
+// Few tiles and a long K: clusters of two CTAs split K (128 x 128 tiles only)
+template <int DT>
+int launch_cfg_split2(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &tb, TcArgs &args, cudaStream_t st) {
+    using C = Cfg<128>;
+    auto kernel = gemm_tcgen05_kernel<128, DT, true>;
+    static std::atomic<uint32_t> optin{0};
+    if (int rc = ensure_smem_optin(kernel, C::kSmemBytes, optin)) return rc;
+    fill_knobs(args);
+    args.skip_kb = -1;                                   // the unarmed-stage hook belongs to the persistent kernels
+    args.tiles_m = (p.M + BM - 1) / BM;
+    args.tiles_n = (p.N + 127) / 128;
+    args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * args.total_tiles), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
+    count_launch();
+    return MAGB200_OK;
 }
 
 template <int BN, int DT>
@@ -1589,6 +1685,7 @@ void set_wait_limit_ns(uint64_t ns) { g_wait_limit_ns.store(ns); }
 uint64_t get_wait_limit_ns() { return g_wait_limit_ns.load(); }
 void set_skip_kb_once(int kb) { g_skip_kb_once.store(kb); }
 void set_balance_tail(int mode) { g_balance_tail.store(mode); }   // 0: off, 1: when it pays, 2: whenever possible
+void set_split_small(int on) { g_split_small.store(on ? 1 : 0); }
 
 bool tcgen05_supported(const GemmProblem &p) {
     if (p.dtype != MAGB200_BF16 && p.dtype != MAGB200_F16) return false;
@@ -1712,7 +1809,10 @@ int launch_gemm_swiglu(const GemmProblem &p, const void *b_up, cudaStream_t st, 
 }
 
 int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
-    const int bn = pick_bn(p);
+    // an output of at most 74 tiles of 128 x 128 with K >= 1024: pairs of CTAs split K, twice as many SMs work
+    const int64_t tiles128 = ((p.M + BM - 1) / BM) * ((p.N + 127) / 128) * p.batch_total;
+    const bool split2 = !scatter && cta_limit <= 0 && p.N > 64 && tiles128 * 2 <= num_sms() && p.K >= 1024 && g_split_small.load() && g_skip_kb_once.load() < 0;
+    const int bn = split2 ? 128 : pick_bn(p);
     OperandDesc a, b;
     int amn = 0, bmn = 0;
     if (!describe(p, true, bn, a, amn) || !describe(p, false, bn, b, bmn)) {
@@ -1736,6 +1836,8 @@ int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, in
         args.scatter_ranks = scatter->ranks; args.scatter_rank = scatter->rank; args.rows_per_rank = scatter->rows_per_rank;
         for (int i = 0; i < scatter->ranks; ++i) args.peer_stage[i] = scatter->stage[i];
     }
+    if (split2)
+        return p.dtype == MAGB200_BF16 ? launch_cfg_split2<MAGB200_BF16>(p, ta, tb, args, st) : launch_cfg_split2<MAGB200_F16>(p, ta, tb, args, st);
 #define LAUNCH(BNV)                                                                                   \
     return p.dtype == MAGB200_BF16 ? launch_cfg<BNV, MAGB200_BF16>(p, ta, tb, args, st, cta_limit)                \
                                    : launch_cfg<BNV, MAGB200_F16>(p, ta, tb, args, st, cta_limit)

@@ -70,6 +70,39 @@ def test_shared_last_wave(gpu, M, N, K, layout, dname):
         t.release()
 
 
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+@pytest.mark.parametrize("batch,M,N,K", [((), 512, 2048, 2048), ((), 128, 128, 1024), ((), 300, 200, 1096), ((2, 3), 130, 136, 4160)])
+def test_small_outputs_split_k_over_cta_pairs(gpu, dname, batch, M, N, K):
+    """Outputs of at most 74 tiles of 128 x 128 with a long K: two CTAs per tile split K and exchange accumulator halves through
+    distributed shared memory. Against fp64 within the own bar, reproducible, and within two roundings of the one-CTA-per-tile
+    result; ragged M, N, K and batches included."""
+    dt = cases.DTYPES[dname]
+    L = mb.lib()
+    rng = np.random.default_rng(35)
+    xb, wb = bits(dt, rng, batch + (M, K), 1.0), bits(dt, rng, (N, K), 0.05)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    truth, scale = xf @ wf.T, np.abs(xf) @ np.abs(wf).T
+    got = {}
+    mb.force_kernel("tcgen05")
+    try:
+        for on in (1, 0):
+            mb.check(L.magb200_set_small_output_split(on))
+            r1, r2 = tx @ tw.T, tx @ tw.T
+            got[on] = r1.to_bits()
+            assert np.array_equal(got[on], r2.to_bits())
+            m = O.error_metrics(dt, got[on], truth, scale)
+            assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, (on, m)
+            r1.release(); r2.release()
+    finally:
+        mb.force_kernel(None)
+        mb.check(L.magb200_set_small_output_split(1))
+    a, b = O.bits_to_f64(dt, got[1]), O.bits_to_f64(dt, got[0])
+    assert np.all(np.abs(a - b) <= 2 * unit_roundoff(dt) * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -20 * scale)
+    for t in (tx, tw):
+        t.release()
+
+
 @pytest.mark.parametrize("M", [1, 5, 8])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 4104), (48, 8192)])
 def test_decode_clusters_split_k_like_one_cta(gpu, M, N, K):
