@@ -204,6 +204,11 @@ int  magb200_force_kernel(int kernel);
  * SMs work (default on; 0 keeps one CTA per tile: tests compare the two). */
 int  magb200_set_small_output_split(int on);
 
+/* Decode-shaped products with plenty of weight rows (lm_head, the projections of a large model) stream their weights with
+ * copies of 512 contiguous bytes of one row per warp instruction (default); 0 selects the older kernel in which every lane
+ * keeps to its own two rows (64 bytes from each of 8 rows per instruction). Same arithmetic, another order of the fp32 sums. */
+int  magb200_set_decode_row_streaming(int on);
+
 /* Decode-shaped products whose weight matrix has few 16-row tiles (the 1024-row o and down projections of a small model) run
  * as clusters of up to `max_cluster` CTAs (1, 2 or 4; default 4) that split K once more and meet through distributed shared
  * memory, so that more SMs stream weights. 1 switches the clusters off (tests compare the two). */

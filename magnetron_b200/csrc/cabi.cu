@@ -1117,6 +1117,10 @@ int magb200_set_small_output_split(int on) {
     set_split_small(on);
     return MAGB200_OK;
 }
+int magb200_set_decode_row_streaming(int on) {
+    set_decode_row_streaming(on);
+    return MAGB200_OK;
+}
 int magb200_set_decode_cluster(int max_cluster) {
     if (max_cluster != 1 && max_cluster != 2 && max_cluster != 4) { set_error("set_decode_cluster: 1, 2 or 4"); return MAGB200_ERR_INVALID_ARG; }
     set_decode_cluster_max(max_cluster);

@@ -543,6 +543,112 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_km_async_kernel(const Skin
 }
 
 // ------------------------------------------------------------------------------------------------
+// K-major 16-bit weights, row-contiguous streaming: grid = (one CTA per SM, nsplit, batch)
+// ------------------------------------------------------------------------------------------------
+// Same arithmetic as skinny_km_async_kernel, other memory access: there a cp.async instruction of a warp fetches 64 bytes
+// from each of 8 rows (every lane keeps to its own two rows), here it fetches 512 CONTIGUOUS bytes of ONE row -- 256 K values,
+// 16 bytes per lane -- and sixteen such instructions bring one step of a 16-row tile into a ring slot that belongs to the
+// warp ([16 rows][512 + 64 bytes]: the pitch of 64 mod 128 makes the fragment reads, 16 bytes per lane from rows g and g + 8,
+// conflict-free). Two slots per warp: 16 KB per warp, 128 KB per SM in flight, as before; the lanes meet (__syncwarp) after
+// their copies have landed and again before the slot is refilled.
+constexpr int kRowsCh = 256;                                   // K values of a row per step
+constexpr int kRowsPitch = kRowsCh * 2 + 64;                   // bytes
+constexpr int kRowsDepth = 2;
+constexpr size_t kRowsSlotBytes = (size_t)16 * kRowsPitch;     // 9216
+constexpr size_t kRowsRingBytes = (size_t)kWarps * kRowsDepth * kRowsSlotBytes;   // 144 KB
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 1) skinny_km_rows_kernel(const SkinnyArgs a, const int M, const int xstride) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kRowsRingBytes);            // [M][xstride]
+
+    pdl_launch_dependents();
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int kc = (int)min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t T = (a.N + 15) / 16;
+    const int64_t W = (int64_t)gridDim.x * kWarps;
+    const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t t_begin = w * T / W, t_end = (w + 1) * T / W;      // a contiguous, even share of the tiles
+    const int nk = (kc + kRowsCh - 1) / kRowsCh;                       // steps per tile
+    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0;
+    const uint16_t *xrow = xs + g * xstride;
+    const bool has_x = g < M;
+    unsigned char *ring = smem + (size_t)warp * kRowsDepth * kRowsSlotBytes;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring) + (uint32_t)lane * 16u;
+
+    int64_t i_tile = t_begin;
+    int i_ks = 0, i_slot = 0;
+    auto issue = [&]() {
+        if (i_tile < t_end) {
+            const int k = i_ks * kRowsCh + lane * 8;
+            const uint32_t nbytes = (k < kc) ? 16u : 0u;               // beyond the K range: zero-fill, nothing is read
+            const uint16_t *src = Bbase + ((k < kc) ? k : 0);
+            const uint32_t dst = ring_u32 + (uint32_t)i_slot * (uint32_t)kRowsSlotBytes;
+            const int64_t r0 = i_tile * 16;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int64_t row = min(r0 + r, a.N - 1);              // clamp: tail rows are loaded twice, stored once
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (uint32_t)(r * kRowsPitch)), "l"(src + row * a.ldb), "r"(nbytes) : "memory");
+            }
+            if (++i_ks == nk) { i_ks = 0; ++i_tile; }
+        }
+        i_slot ^= 1;
+        asm volatile("cp.async.commit_group;" ::: "memory");          // one group per step, empty past the end
+    };
+
+    if (!a.early_weights) pdl_wait();
+    for (int q = 0; q < kRowsDepth; ++q) issue();
+
+    pdl_wait();
+    stage_activations(a, M, xstride, offA, k0, kc, xs);
+    __syncthreads();
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+    int c_ks = 0, c_slot = 0;
+    for (int64_t tile = t_begin; tile < t_end;) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRowsDepth - 1) : "memory");
+        __syncwarp();                                                   // every lane's copies of this step have landed
+        const unsigned char *slot = ring + (size_t)c_slot * kRowsSlotBytes;
+        const int kbase = c_ks * kRowsCh;
+#pragma unroll
+        for (int sub = 0; sub < kRowsCh / 32; ++sub) {
+            if (kbase + sub * 32 < kc) {                                // uniform over the warp
+                const int k = kbase + sub * 32 + t * 8;
+                const uint4 wa = *reinterpret_cast<const uint4 *>(slot + g * kRowsPitch + (sub * 32 + t * 8) * 2);
+                const uint4 wb = *reinterpret_cast<const uint4 *>(slot + (g + 8) * kRowsPitch + (sub * 32 + t * 8) * 2);
+                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                if (has_x && k < kc) xv = *reinterpret_cast<const uint4 *>(xrow + k);
+                mma_16816<DT>(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+                mma_16816<DT>(c2, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+            }
+        }
+        __syncwarp();                                                   // the slot has been read by every lane
+        c_slot ^= 1;
+        issue();
+        if (++c_ks == nk) {
+            const int64_t r0 = tile * 16;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int64_t n = r0 + g + (i >> 1) * 8;
+                const int m = 2 * t + (i & 1);
+                if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[i] + c2[i]);
+                c[i] = 0.f;
+                c2[i] = 0.f;
+            }
+            c_ks = 0;
+            ++tile;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------------
 // N-major weights: grid = (column blocks, nsplit, batch); a CTA covers 32*V columns
 // ------------------------------------------------------------------------------------------------
 template <int DT, int M>
@@ -641,6 +747,7 @@ __global__ void __launch_bounds__(kThreads) skinny_finalize_kernel(const float *
 
 constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
 
+std::atomic<int> g_row_streaming{1};     // streaming decode kernel: 1 row-contiguous copies (one CTA per SM), 0 per-lane ring
 std::atomic<int> g_cluster_max{4};       // largest cluster the decode planner may use (1: never)
 // K values a warp must keep after the extra split. Measured at M = 1 (us, no cluster / 2 / 4 CTAs): o 1024 x 2048 3.46 / 2.94 /
 // 3.61, down 1024 x 3072 4.76 / 4.19 / 3.97, q 2048 x 1024 2.39 / 3.49: a cluster launch costs about a microsecond, which a
@@ -651,6 +758,7 @@ struct Plan {
     bool km;       // K-major weights
     bool mma;      // K-major 16-bit weights through mma.sync
     bool async;    // ... with the cp.async ring (plenty of tiles)
+    bool rows;     // ... in its row-contiguous form (one CTA per SM)
     int KW;        // warps along K per CTA (mma)
     int CL;        // CTAs of a cluster that split K once more (mma, few tiles)
     int64_t xstride;
@@ -676,6 +784,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     pl.km = km;
     pl.mma = false;
     pl.async = false;
+    pl.rows = false;
     pl.CL = 1;
     if (km && DT != MAGB200_F32) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
@@ -758,7 +867,13 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
             pl.xstride = (kch + 63) / 64 * 64 + 32;
             pl.smem = kAsyncRingBytes + (size_t)M * pl.xstride * 2;
             const int64_t other = (int64_t)nsplit * p.batch_total;
-            const int per_sm = pl.smem <= 110 * 1024 ? 2 : 1;
+            int per_sm = pl.smem <= 110 * 1024 ? 2 : 1;
+            {
+                // the row-contiguous form whenever its ring and the activation rows fit one CTA's shared memory (measured at
+                // M = 1: 151936 x 1024 5.43 -> 5.92 TB/s, 65536 x 4096 5.56 -> 6.19, 51200 x 5120 5.15 -> 6.51; M = 8 gains 2-4 %)
+                const size_t rows_smem = kRowsRingBytes + (size_t)M * pl.xstride * 2;
+                if (g_row_streaming.load() && rows_smem <= (size_t)224 * 1024) { pl.rows = true; pl.smem = rows_smem; per_sm = 1; }
+            }
             int64_t want = ((int64_t)num_sms() * per_sm + other - 1) / other;
             if (want < 1) want = 1;
             pl.gridx = (unsigned)want;
@@ -878,8 +993,19 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
     int rc = MAGB200_OK;
     if (pl.async) {
         if constexpr (DT != MAGB200_F32) {
+            if (pl.rows) {
+                static std::atomic<uint32_t> optin{0};
+                int dev = 0;
+                MAGB200_CUDA_TRY(cudaGetDevice(&dev));
+                if (!(optin.load() & (1u << (dev & 31)))) {
+                    MAGB200_CUDA_TRY(cudaFuncSetAttribute(skinny_km_rows_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+                    optin.fetch_or(1u << (dev & 31));
+                }
+                if ((rc = launch_pdl(skinny_km_rows_kernel<DT>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc;
+            } else {
             if ((rc = set_smem(skinny_km_async_kernel<DT>, pl.smem))) return rc;
             if ((rc = launch_pdl(skinny_km_async_kernel<DT>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc;
+            }
         }
     } else if (pl.mma) {
         if constexpr (DT != MAGB200_F32) {
@@ -1005,6 +1131,7 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
 }
 }  // namespace
 
+void set_decode_row_streaming(int on) { g_row_streaming.store(on ? 1 : 0); }
 void set_decode_cluster_max(int max_cluster) { g_cluster_max.store(max_cluster < 1 ? 1 : (max_cluster > 4 ? 4 : max_cluster)); }
 
 // Several decode-shaped products with the same activation rows in one launch: r_i = x . y_i. Returns 1 when the group cannot

@@ -103,6 +103,38 @@ def test_small_outputs_split_k_over_cta_pairs(gpu, dname, batch, M, N, K):
         t.release()
 
 
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(1, 40000, 1024), (8, 39993, 1032), (3, 24000, 4096), (8, 20000, 5120), (2, 50000, 264)])
+def test_decode_streaming_kernels_agree(gpu, dname, M, N, K):
+    """Weight matrices with plenty of rows: the row-contiguous streaming kernel and the per-lane-ring kernel against fp64 within
+    the own bar, each reproducible, and within two roundings of each other; ragged N, K not a multiple of the 256-wide step,
+    and a K that needs a split across CTAs."""
+    dt = cases.DTYPES[dname]
+    L = mb.lib()
+    rng = np.random.default_rng(37)
+    xb, wb = bits(dt, rng, (M, K), 1.0), bits(dt, rng, (N, K), 0.05)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    truth, scale = xf @ wf.T, np.abs(xf) @ np.abs(wf).T
+    got = {}
+    try:
+        for on in (1, 0):
+            mb.check(L.magb200_set_decode_row_streaming(on))
+            r1, r2 = tx @ tw.T, tx @ tw.T
+            assert mb.last_kernel() in ("skinny", "skinny_splitk")
+            got[on] = r1.to_bits()
+            assert np.array_equal(got[on], r2.to_bits())
+            m = O.error_metrics(dt, got[on], truth, scale)
+            assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, (on, m)
+            r1.release(); r2.release()
+    finally:
+        mb.check(L.magb200_set_decode_row_streaming(1))
+    a, b = O.bits_to_f64(dt, got[1]), O.bits_to_f64(dt, got[0])
+    assert np.all(np.abs(a - b) <= 2 * unit_roundoff(dt) * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -20 * scale)
+    for t in (tx, tw):
+        t.release()
+
+
 @pytest.mark.parametrize("M", [1, 5, 8])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 4104), (48, 8192)])
 def test_decode_clusters_split_k_like_one_cta(gpu, M, N, K):
