@@ -872,7 +872,11 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
                 // the row-contiguous form whenever its ring and the activation rows fit one CTA's shared memory (measured at
                 // M = 1: 151936 x 1024 5.43 -> 5.92 TB/s, 65536 x 4096 5.56 -> 6.19, 51200 x 5120 5.15 -> 6.51; M = 8 gains 2-4 %)
                 const size_t rows_smem = kRowsRingBytes + (size_t)M * pl.xstride * 2;
-                if (g_row_streaming.load() && rows_smem <= (size_t)224 * 1024) { pl.rows = true; pl.smem = rows_smem; per_sm = 1; }
+                // ... and every one of its 8 warps per SM gets whole tiles to stream: with few row tiles and K split over CTAs the
+                // per-lane-ring kernel, with twice the warps, balances better (5120 x 5120 at M = 1: 13.0 us against 19.9;
+                // 12288 x 4096, 768 tiles: 21.7 against 19.2 the other way)
+                const bool enough_tiles = tiles * p.batch_total >= (int64_t)num_sms() * 5;
+                if (g_row_streaming.load() && enough_tiles && rows_smem <= (size_t)224 * 1024) { pl.rows = true; pl.smem = rows_smem; per_sm = 1; }
             }
             int64_t want = ((int64_t)num_sms() * per_sm + other - 1) / other;
             if (want < 1) want = 1;
