@@ -649,6 +649,135 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_km_rows_kernel(const Skinn
 }
 
 // ------------------------------------------------------------------------------------------------
+// N-major 16-bit weights (a contiguous [K, N] matrix) through mma.sync: grid = (one CTA per SM, nsplit, batch)
+// ------------------------------------------------------------------------------------------------
+// A warp owns strips of 128 weight columns and streams its CTA's K chunk of them: a cp.async instruction copies two K rows
+// of the strip (2 x 256 contiguous bytes), eight of them one step of 16 K rows into a ring slot owned by the warp
+// ([16 K rows][256 + 16 bytes]; two slots per warp, sixteen warps per SM). ldmatrix.x4.trans turns a 16 x 16 block of the slot
+// into the A fragment of mma.sync.m16n8k16 (rows = weight columns, K along the fragment's K), the activation rows are the
+// B operand straight from shared memory; eight mma per step, 32 accumulators per thread. The ring runs on across strips.
+// With few strips K is split across CTAs (fp32 partial sums, summed in split order by skinny_finalize_kernel).
+// The FFMA kernel below did 8 x M FMAs plus the unpacking per 16-byte load and fell from 5.6 TB/s at M = 1 to 2.2-3.4 at
+// M = 2..8; it stays for float32 and for layouts this kernel does not take.
+constexpr int kNmCols = 128;                                   // columns of a strip
+constexpr int kNmPitch = kNmCols * 2 + 16;                     // bytes: 16 mod 128 keeps the 8 row addresses of an ldmatrix apart
+constexpr int kNmDepth = 2;                                    // two CTAs per SM: 16 warps x 8 KB in flight
+constexpr size_t kNmSlotBytes = (size_t)16 * kNmPitch;         // 4352
+constexpr size_t kNmRingBytes = (size_t)kWarps * kNmDepth * kNmSlotBytes;   // 136 KB
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2) skinny_nm_mma_kernel(const SkinnyArgs a, const int M, const int xstride) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint16_t *xs = reinterpret_cast<uint16_t *>(smem + kNmRingBytes);               // [M][xstride]
+
+    pdl_launch_dependents();
+    const int split = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t k0 = (int64_t)split * a.kch;
+    const int kc = (int)min(a.kch, a.K - k0);
+    int64_t offA, offB;
+    batch_offsets(a, batch, offA, offB);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t S = (a.N + kNmCols - 1) / kNmCols;                 // strips
+    const int64_t W = (int64_t)gridDim.x * kWarps;
+    const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t s_begin = w * S / W, s_end = (w + 1) * S / W;       // a contiguous, even share of the strips
+    const int nk = (kc + 15) >> 4;                                     // steps of 16 K rows per strip
+    const uint16_t *Bbase = reinterpret_cast<const uint16_t *>(a.B) + offB + k0 * a.ldb;
+    unsigned char *ring = smem + (size_t)warp * kNmDepth * kNmSlotBytes;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
+    // this lane's 16 bytes of a copy instruction: K row (lane >> 4) of the pair, columns (lane & 15) * 8 .. + 7 of the strip
+    const int cp_row = lane >> 4, cp_col = (lane & 15) * 8;
+    const uint32_t cp_dst = ring_u32 + (uint32_t)(cp_row * kNmPitch + cp_col * 2);
+    // this lane's row address of an ldmatrix.x4.trans: matrix (lane >> 3) = {K rows 0-7 | 8-15} x {columns 0-7 | 8-15} of a tile
+    const uint32_t lm_off = (uint32_t)((((lane >> 4) & 1) * 8 + (lane & 7)) * kNmPitch + ((lane >> 3) & 1) * 16);
+
+    int64_t i_strip = s_begin;
+    int i_ks = 0, i_slot = 0;
+    auto issue = [&]() {
+        if (i_strip < s_end) {
+            const int64_t col = i_strip * kNmCols + cp_col;
+            const bool col_ok = col < a.N;                            // N is a multiple of 8: a lane's 8 columns are all in or all out
+            const uint16_t *src = Bbase + (col_ok ? col : 0);
+            const uint32_t dst = cp_dst + (uint32_t)i_slot * (uint32_t)kNmSlotBytes;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int k = i_ks * 16 + 2 * i + cp_row;
+                const bool ok = col_ok && k < kc;                     // outside the matrix: zero-fill, nothing is read
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (uint32_t)(2 * i * kNmPitch)),
+                             "l"(src + (int64_t)(ok ? k : 0) * a.ldb), "r"(ok ? 16u : 0u) : "memory");
+            }
+            if (++i_ks == nk) { i_ks = 0; ++i_strip; }
+        }
+        i_slot = (i_slot + 1) & (kNmDepth - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (!a.early_weights) pdl_wait();
+    for (int q = 0; q < kNmDepth; ++q) issue();
+
+    pdl_wait();
+    stage_activations(a, M, xstride, offA, k0, kc, xs);
+    {
+        // K need not be a multiple of 8 in this layout: the last K % 8 values, which the 16-byte staging loop leaves out, one by
+        // one; then zeros up to the next multiple of 16 (a step always multiplies 16 K rows)
+        const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
+        for (int i = threadIdx.x; i < M * 8; i += kThreads) {
+            const int m = i >> 3, k = (kc & ~7) + (i & 7);
+            if (k < kc) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
+        }
+        for (int i = threadIdx.x; i < M * 16; i += kThreads) {
+            const int m = i >> 4, k = kc + (i & 15);
+            if (k < ((kc + 15) & ~15)) xs[m * xstride + k] = 0;
+        }
+    }
+    __syncthreads();
+    const uint16_t *xrow = xs + g * xstride;
+    const bool has_x = g < M;
+    float c[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f; }
+    int c_ks = 0, c_slot = 0;
+    for (int64_t strip = s_begin; strip < s_end;) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kNmDepth - 1) : "memory");
+        __syncwarp();                                                   // every lane's copies of this step have landed
+        const uint32_t slot = ring_u32 + (uint32_t)c_slot * (uint32_t)kNmSlotBytes + lm_off;
+        uint32_t b0 = 0u, b1 = 0u;
+        if (has_x) {
+            b0 = *reinterpret_cast<const uint32_t *>(xrow + c_ks * 16 + 2 * t);
+            b1 = *reinterpret_cast<const uint32_t *>(xrow + c_ks * 16 + 2 * t + 8);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t a0, a1, a2, a3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(slot + (uint32_t)(j * 32)) : "memory");
+            mma_16816<DT>(c[j], a0, a1, a2, a3, b0, b1);
+        }
+        __syncwarp();                                                   // the slot has been read by every lane
+        c_slot = (c_slot + 1) & (kNmDepth - 1);
+        issue();
+        if (++c_ks == nk) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int64_t n = strip * kNmCols + j * 16 + g + (i >> 1) * 8;
+                    const int m = 2 * t + (i & 1);
+                    if (n < a.N && m < M) store_result<DT>(a, batch, split, m, M, n, c[j][i]);
+                    c[j][i] = 0.f;
+                }
+            }
+            c_ks = 0;
+            ++strip;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------------
 // N-major weights: grid = (column blocks, nsplit, batch); a CTA covers 32*V columns
 // ------------------------------------------------------------------------------------------------
 template <int DT, int M>
@@ -747,6 +876,7 @@ __global__ void __launch_bounds__(kThreads) skinny_finalize_kernel(const float *
 
 constexpr size_t kSmemBudget = 96 * 1024;  // two CTAs per SM
 
+std::atomic<int> g_nm_mma{1};            // N-major 16-bit weights: 1 mma.sync kernel, 0 the FFMA kernel
 std::atomic<int> g_row_streaming{1};     // streaming decode kernel: 1 row-contiguous copies (one CTA per SM), 0 per-lane ring
 std::atomic<int> g_cluster_max{4};       // largest cluster the decode planner may use (1: never)
 // K values a warp must keep after the extra split. Measured at M = 1 (us, no cluster / 2 / 4 CTAs): o 1024 x 2048 3.46 / 2.94 /
@@ -759,6 +889,7 @@ struct Plan {
     bool mma;      // K-major 16-bit weights through mma.sync
     bool async;    // ... with the cp.async ring (plenty of tiles)
     bool rows;     // ... in its row-contiguous form (one CTA per SM)
+    bool nm_mma;   // N-major 16-bit weights through mma.sync
     int KW;        // warps along K per CTA (mma)
     int CL;        // CTAs of a cluster that split K once more (mma, few tiles)
     int64_t xstride;
@@ -785,6 +916,7 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
     pl.mma = false;
     pl.async = false;
     pl.rows = false;
+    pl.nm_mma = false;
     pl.CL = 1;
     if (km && DT != MAGB200_F32) {
         if (p.K % V || (p.N > 1 && p.sBn % V)) return false;
@@ -939,6 +1071,43 @@ bool make_plan(const GemmProblem &p, Plan &pl) {
         pl.gridx = (unsigned)(blocks < cap ? blocks : cap);
     } else {
         if (p.N % V || p.sBk % V) return false;
+        if (DT != MAGB200_F32 && g_nm_mma.load()) {
+            // Strips of 128 columns, each with a K chunk, are the units dealt out to 16 warps per SM. The number of K chunks is
+            // searched: a warp's share is whole units, so the launch lasts ceil(units / warps) units (151936 columns on 1184 warps
+            // were 1187 units: three warps ran a second strip alone, 4.9 TB/s); more chunks cost partial sums and a second kernel.
+            const int64_t strips = (p.N + kNmCols - 1) / kNmCols * p.batch_total;
+            const int64_t warps = (int64_t)num_sms() * 2 * kWarps;
+            int64_t kch_max = ((int64_t)110 * 1024 - (int64_t)kNmRingBytes) / ((int64_t)M * 2) - 48;
+            kch_max -= kch_max % 16;
+            const int ns_min = (int)((p.K + kch_max - 1) / kch_max);
+            int ns_cap = (int)(p.K / 128);
+            if (ns_cap < ns_min) ns_cap = ns_min;
+            if (ns_cap > 64) ns_cap = 64 > ns_min ? 64 : ns_min;
+            int best_ns = ns_min;
+            double best_cost = 1e300;
+            for (int ns = ns_min; ns <= ns_cap; ++ns) {
+                const int64_t units = strips * ns;
+                const int64_t per = (units + warps - 1) / warps;
+                const double eff = (double)units / (double)(per * warps);
+                const double busy = units < warps ? (double)units / (double)warps : 1.0;   // idle warps cost nothing while enough bytes are in flight
+                const double fill = busy < 0.4 ? busy / 0.4 : 1.0;
+                const double cost = 1.0 / (units < warps ? fill : eff) * (ns > 1 ? 1.05 + 4.0 * ns * M / (double)p.K : 1.0);
+                if (cost < best_cost - 1e-9) { best_cost = cost; best_ns = ns; }
+            }
+            int nsplit = best_ns;
+            int64_t kch = (p.K + nsplit - 1) / nsplit;
+            kch = (kch + 15) / 16 * 16;
+            nsplit = (int)((p.K + kch - 1) / kch);
+            pl.nm_mma = true; pl.kch = kch; pl.nsplit = nsplit; pl.R = 0;
+            pl.xstride = (kch + 15) / 16 * 16 + 40;                  // 80 bytes mod 128: the 8 activation rows of a fragment read spread over the banks
+            pl.smem = kNmRingBytes + (size_t)M * pl.xstride * 2;
+            int64_t gx = ((int64_t)num_sms() * 2 + (int64_t)nsplit * p.batch_total - 1) / ((int64_t)nsplit * p.batch_total);
+            if (gx < 1) gx = 1;
+            const int64_t strips_one = (p.N + kNmCols - 1) / kNmCols;
+            if (gx * kWarps > strips_one) gx = (strips_one + kWarps - 1) / kWarps;
+            pl.gridx = (unsigned)gx;
+            return pl.nsplit <= 65535;
+        }
         const int CB = 32 * V;
         int64_t kch_max = (int64_t)((kSmemBudget - (size_t)M * CB * 4) / ((size_t)M * 4));
         kch_max -= kch_max % 32;
@@ -1041,6 +1210,17 @@ int launch_m(const GemmProblem &p, const Plan &pl, const SkinnyArgs &a, cudaStre
             if ((rc = set_smem(skinny_km_kernel<DT, M, 1>, pl.smem))) return rc;
             skinny_km_kernel<DT, M, 1><<<grid, kThreads, pl.smem, st>>>(a);
         }
+    } else if (pl.nm_mma) {
+        if constexpr (DT != MAGB200_F32) {
+            static std::atomic<uint32_t> optin{0};
+            int dev = 0;
+            MAGB200_CUDA_TRY(cudaGetDevice(&dev));
+            if (!(optin.load() & (1u << (dev & 31)))) {
+                MAGB200_CUDA_TRY(cudaFuncSetAttribute(skinny_nm_mma_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+                optin.fetch_or(1u << (dev & 31));
+            }
+            if ((rc = launch_pdl(skinny_nm_mma_kernel<DT>, grid, dim3(kThreads), pl.smem, st, a, M, (int)pl.xstride))) return rc;
+        }
     } else {
         if ((rc = set_smem(skinny_nm_kernel<DT, M>, pl.smem))) return rc;
         skinny_nm_kernel<DT, M><<<grid, kThreads, pl.smem, st>>>(a);
@@ -1135,7 +1315,7 @@ int launch_grouped_dt(const GemmProblem *ps, int count, cudaStream_t st, bool we
 }
 }  // namespace
 
-void set_decode_row_streaming(int on) { g_row_streaming.store(on ? 1 : 0); }
+void set_decode_row_streaming(int on) { g_row_streaming.store(on ? 1 : 0); g_nm_mma.store(on ? 1 : 0); }
 void set_decode_cluster_max(int max_cluster) { g_cluster_max.store(max_cluster < 1 ? 1 : (max_cluster > 4 ? 4 : max_cluster)); }
 
 // Several decode-shaped products with the same activation rows in one launch: r_i = x . y_i. Returns 1 when the group cannot

@@ -104,6 +104,39 @@ def test_small_outputs_split_k_over_cta_pairs(gpu, dname, batch, M, N, K):
 
 
 @pytest.mark.parametrize("dname", ["bf16", "f16"])
+@pytest.mark.parametrize("batch,M,N,K", [((), 1, 40000, 1024), ((), 8, 39992, 1031), ((), 4, 12288, 4096), ((), 5, 136, 777), ((3,), 2, 1000, 300),
+                                         ((), 8, 8, 20)])
+def test_decode_with_n_major_weights(gpu, dname, batch, M, N, K):
+    """y = a contiguous [K, N] weight (the layout of the reference's GEMV fast path, magnetron/cpu/mag_cpu_impl_ops_matmul.inl:2940):
+    the mma.sync kernel with transposing fragment loads against fp64 within the own bar, reproducible, and within two roundings
+    of the FFMA kernel; K not a multiple of 8 or 16, ragged strips, K split across CTAs, batches."""
+    dt = cases.DTYPES[dname]
+    L = mb.lib()
+    rng = np.random.default_rng(39)
+    xb, wb = bits(dt, rng, batch + (M, K), 1.0), bits(dt, rng, (K, N), 0.05)
+    tx, tw = mb.Tensor.from_bits(gpu, dt, xb), mb.Tensor.from_bits(gpu, dt, wb)
+    xf, wf = O.bits_to_f64(dt, xb), O.bits_to_f64(dt, wb)
+    truth, scale = xf @ wf, np.abs(xf) @ np.abs(wf)
+    got = {}
+    try:
+        for on in (1, 0):
+            mb.check(L.magb200_set_decode_row_streaming(on))
+            r1, r2 = tx @ tw, tx @ tw
+            assert mb.last_kernel() in ("skinny", "skinny_splitk")
+            got[on] = r1.to_bits()
+            assert np.array_equal(got[on], r2.to_bits())
+            m = O.error_metrics(dt, got[on], truth, scale)
+            assert m["e"] <= unit_roundoff(dt) + K * 2.0 ** -24, (on, m)
+            r1.release(); r2.release()
+    finally:
+        mb.check(L.magb200_set_decode_row_streaming(1))
+    a, b = O.bits_to_f64(dt, got[1]), O.bits_to_f64(dt, got[0])
+    assert np.all(np.abs(a - b) <= 2 * unit_roundoff(dt) * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -20 * scale)
+    for t in (tx, tw):
+        t.release()
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
 @pytest.mark.parametrize("M,N,K", [(1, 40000, 1024), (8, 39993, 1032), (3, 24000, 4096), (8, 20000, 5120), (2, 50000, 264)])
 def test_decode_streaming_kernels_agree(gpu, dname, M, N, K):
     """Weight matrices with plenty of rows: the row-contiguous streaming kernel and the per-lane-ring kernel against fp64 within
