@@ -242,21 +242,17 @@ __device__ __forceinline__ void stage_activations(const SkinnyArgs &a, int M, in
     const uint16_t *A = reinterpret_cast<const uint16_t *>(a.A) + offA + k0 * a.sAk;
     const bool vec = a.sAk == 1 && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0) && (M == 1 || a.sAm % 8 == 0);
     if (vec) {
-        const int chunks = kc >> 3;                 // kc is a multiple of 8
+        // asynchronous 16-byte copies, all in flight at once (eight rows of K = 4096 are 16 copies per thread: through registers,
+        // four at a time, that was four L2 round trips on the critical path of every CTA), then one wait; the wait also covers
+        // the weight copies a streaming kernel has issued before, which it needs next anyway
+        const int chunks = kc >> 3;                 // whole groups of 8 K values (callers whose K is not a multiple of 8 add the rest)
         const int total = M * chunks;
-        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kThreads) {
-            uint4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * kThreads;
-                if (i < total) { const int m = i / chunks, c = i - m * chunks; v[u] = reinterpret_cast<const uint4 *>(A + (int64_t)m * a.sAm)[c]; }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * kThreads;
-                if (i < total) { const int m = i / chunks, c = i - m * chunks; reinterpret_cast<uint4 *>(xs + m * xstride)[c] = v[u]; }
-            }
+        for (int i = threadIdx.x; i < total; i += kThreads) {
+            const int m = i / chunks, c = i - m * chunks;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs + m * xstride + c * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(A + (int64_t)m * a.sAm + c * 8) : "memory");
         }
+        asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     } else {
         for (int m = 0; m < M; ++m)
             for (int k = threadIdx.x; k < kc; k += kThreads) xs[m * xstride + k] = A[(int64_t)m * a.sAm + (int64_t)k * a.sAk];
