@@ -48,7 +48,7 @@ PREFILL_GEMMS = [("q", HIDDEN, HIDDEN, "x"), ("k", KV_DIM, HIDDEN, "x"), ("v", K
 DECODE_LAYER = [("q", 2048, 1024), ("k", 1024, 1024), ("v", 1024, 1024), ("o", 1024, 2048),
                 ("gate", 3072, 1024), ("up", 3072, 1024), ("down", 1024, 3072)]
 DECODE_LAYERS, VOCAB = 28, 151936
-# dram__bytes_read of one gemm_tcgen05_2sm_kernel launch on 4096^3 divided by its A + B bytes (ncu, one launch)
+# dram__bytes_read of one gemm_tcgen05_2sm_kernel launch on 4096^3 divided by its A + B bytes (one ncu capture of one launch)
 DRAM_READ_FACTOR = 1.31
 
 

@@ -4,7 +4,7 @@
 and down, and the two exchanges of the paired schedule inside the timed region, run with the schedule that the library
 itself picks (`TPLayer(exchange="auto")` -> magb200_tp_plan: which exchange, how many token chunks); time is the maximum
 over ranks of CUDA-event time. The same line reports the NCCL op-by-op schedule as the baseline the fused exchange is
-measured against, the variant that also all-gathers the column-sharded outputs (the configuration as BASELINE words it),
+measured against, the variant that also all-gathers the column-sharded outputs (the configuration with gathered outputs),
 a correctness check against the unsharded product, the planner's per-operator decisions and the token sweep M in
 {1, 8, 512}. `--all-schedules` (an environment switch, MAGB200_TP_ALL=1) additionally times every other schedule.
 `bench.py --gpus 1 --workload tp` runs the same layer unsharded (the one-GPU line of `bench.py` carries the same figure
