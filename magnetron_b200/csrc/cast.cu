@@ -231,6 +231,7 @@ __device__ __forceinline__ void batch_offsets(const SplitOperand &o, int64_t rem
     }
 }
 __global__ void __launch_bounds__(kThreads) split3_kernel(const SplitArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the GEMM behind this pass may set itself up meanwhile (it waits before it reads)
     __shared__ float tile[32][65];
     const int t = threadIdx.x;
     bool bad = false;

@@ -27,6 +27,7 @@
 #include "common.cuh"
 
 #include <atomic>
+#include <cstring>
 
 namespace magb200 {
 
@@ -62,7 +63,10 @@ gemm_simt_kernel(const GemmProblem p, int64_t tiles_m, int64_t tiles_n, int nspl
     // Stand-by launch behind the split-operand tensor-core kernel: runs only when the split pass raised the word. The word
     // is lowered again by the last CTA of this launch to finish (run_if_set[1] counts them), by which time every CTA of
     // both kernels has read it, so the next call finds it clear without a memset of its own.
-    if (run_if_set && *reinterpret_cast<volatile int *>(run_if_set) == 0) return;
+    if (run_if_set) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");          // launched as a programmatic dependent of the tensor-core kernel
+        if (*reinterpret_cast<volatile int *>(run_if_set) == 0) return;
+    }
     extern __shared__ __align__(16) unsigned char simt_smem[];
     typedef float Tile[BK][BM + PAD];
     Tile *As = reinterpret_cast<Tile *>(simt_smem);                   // As[2][BK][BM + PAD]
@@ -333,8 +337,16 @@ int launch_gemm_simt(const GemmProblem &p, cudaStream_t stream, float *scratch, 
     do {                                                                                                     \
         static std::atomic<uint32_t> optin{0};                                                               \
         if (int rc = simt_smem_optin(gemm_simt_kernel<DT, AKF, BNF>, simt_smem_bytes<DT>(), optin)) return rc; \
-        gemm_simt_kernel<DT, AKF, BNF><<<(unsigned)grid, THREADS, simt_smem_bytes<DT>(), stream>>>(          \
-            p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, scratch, run_if_set);                                     \
+        cudaLaunchConfig_t cfg;                                                                              \
+        memset(&cfg, 0, sizeof(cfg));                                                                        \
+        cfg.gridDim = dim3((unsigned)grid, 1, 1); cfg.blockDim = dim3(THREADS, 1, 1);                        \
+        cfg.dynamicSmemBytes = simt_smem_bytes<DT>(); cfg.stream = stream;                                   \
+        cudaLaunchAttribute attr[1];                                                                         \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                     \
+        attr[0].val.programmaticStreamSerializationAllowed = 1;                                              \
+        cfg.attrs = attr; cfg.numAttrs = run_if_set ? 1 : 0;                                                 \
+        MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_simt_kernel<DT, AKF, BNF>, p, pl.tiles_m, pl.tiles_n, pl.nsplit, pl.kchunk, \
+                                            scratch, run_if_set));                                           \
     } while (0)
 #define MAGB200_SIMT_LAUNCH(DT)                                                                              \
     if (akf) { if (bnf) MAGB200_SIMT_GO(DT, true, true); else MAGB200_SIMT_GO(DT, true, false); }            \

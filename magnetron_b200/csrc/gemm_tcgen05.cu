@@ -1131,7 +1131,6 @@ __device__ __forceinline__ void two_sum_f3(float a, float b, float &s, float &e)
 template <bool kSplitK>
 __global__ void __launch_bounds__(kF3Threads, 1)
 gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const F3Args args) {
-    if (args.skip_if_set && *args.skip_if_set != 0) return;   // the operands cannot be split: the FFMA kernel behind this launch runs
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -1166,6 +1165,14 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Launched as a programmatic dependent of the split pass: everything above ran beside it; its planes and its verdict are
+    // read only from here on. The stand-by FFMA launch behind this kernel may set itself up now (it waits before it reads).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // the operands cannot be split: nothing to do here, the FFMA kernel computes the product (same answer in every thread
+    // of both CTAs of a cluster, so the cluster's meeting points below are skipped by all of them)
+    const bool skip = args.skip_if_set && *reinterpret_cast<const volatile int *>(args.skip_if_set) != 0;
+
     int64_t batch, tm, tn;
     decode_tile(kSplitK ? (int64_t)(blockIdx.x >> 1) : (int64_t)blockIdx.x, args.tiles_m, args.tiles_n, batch, tm, tn);
     const int m0 = (int)(tm * BM), n0 = (int)(tn * kF3BN);
@@ -1175,7 +1182,9 @@ gemm_f32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int kb_end = kSplitK ? (kb_begin + kb_half < args.num_kb ? kb_begin + kb_half : args.num_kb) : args.num_kb;
     const int nkb = kb_end - kb_begin;                 // K blocks of this CTA
 
-    if (warp == 0) {
+    if (skip) {
+        // straight to the teardown
+    } else if (warp == 0) {
         if (lane == 0) {
             int bc[kMaxBatchDims] = {0, 0, 0};
             {
@@ -1902,27 +1911,32 @@ int launch_gemm_f32x3(const GemmProblem &p, const void *planes_a, const void *pl
     args.skip_if_set = skip_if_set;
     args.wait_limit_ns = g_wait_limit_ns.load();
     const int64_t tiles = args.tiles_m * args.tiles_n * p.batch_total;
+    // a programmatic dependent of the split pass: its set-up (barriers, TMEM, tensor maps) runs beside that pass's tail
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.blockDim = dim3(kF3Threads, 1, 1);
+    cfg.dynamicSmemBytes = kF3SmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
     if (tiles * 2 <= num_sms() && args.num_kb >= 8) {      // few tiles, long K: pairs of CTAs share a tile along K
         static std::atomic<uint32_t> optin_split{0};
         if ((rc = ensure_smem_optin(gemm_f32x3_kernel<true>, kF3SmemBytes, optin_split))) return rc;
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3((unsigned)(2 * tiles), 1, 1);
-        cfg.blockDim = dim3(kF3Threads, 1, 1);
-        cfg.dynamicSmemBytes = kF3SmemBytes;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = 2;
         MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_f32x3_kernel<true>, ta, tb, args));
         count_launch();
         return MAGB200_OK;
     }
     static std::atomic<uint32_t> optin{0};
     if ((rc = ensure_smem_optin(gemm_f32x3_kernel<false>, kF3SmemBytes, optin))) return rc;
-    gemm_f32x3_kernel<false><<<(unsigned)tiles, kF3Threads, kF3SmemBytes, st>>>(ta, tb, args);
+    cfg.gridDim = dim3((unsigned)tiles, 1, 1);
+    cfg.numAttrs = 1;
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_f32x3_kernel<false>, ta, tb, args));
     count_launch();
     MAGB200_CUDA_TRY(cudaGetLastError());
     return MAGB200_OK;
