@@ -199,6 +199,15 @@ void     magb200_launch_count_reset(void);
 /* Restrict routing (testing / profiling): 0 = automatic, otherwise a magb200_kernel_t that must be
  * able to run the problem, else the call fails with MAGB200_ERR_INVALID_ARG. */
 int  magb200_force_kernel(int kernel);
+/* Tensor-core matmuls submitted back to back (consecutive magb200_matmul calls on a device with nothing but pool
+ * allocations and releases in between, on the library's own stream): one that reads nothing the ones before it write and
+ * writes nothing they read or write is launched as a programmatic dependent without a wait, so its first CTAs run on the SMs
+ * that the partial last wave of the matmul before it leaves idle (q, k, v of one input; gate and up). Any overlap of the
+ * address ranges, any other operation in between, or a stream installed by the caller gives the ordinary, fully ordered
+ * launch. Default on; 0 orders every launch. The counter says how many launches overlapped (tests). */
+int      magb200_set_gemm_overlap(int on);
+uint64_t magb200_overlapped_launch_count(void);
+
 /* 16-bit products with K >= 1024 whose output has at most 74 tiles of 128 x 128 (e.g. 512 x 2048 x 2048) run as clusters of
  * two CTAs that split K and exchange halves of their fp32 accumulators through distributed shared memory, so twice as many
  * SMs work (default on; 0 keeps one CTA per tile: tests compare the two). */

@@ -89,6 +89,8 @@ SIGNATURES = {
     "magb200_matmul": (C.c_int, [C.c_int, _VP, _VP, _VP]),
     "magb200_upload_2d": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
     "magb200_set_decode_cluster": (C.c_int, [C.c_int]),
+    "magb200_set_gemm_overlap": (C.c_int, [C.c_int]),
+    "magb200_overlapped_launch_count": (C.c_uint64, []),
     "magb200_set_decode_row_streaming": (C.c_int, [C.c_int]),
     "magb200_set_small_output_split": (C.c_int, [C.c_int]),
     "magb200_matmul_swiglu": (C.c_int, [C.c_int, _VP, _VP, _VP, _VP]),

@@ -98,6 +98,14 @@ struct DeviceState {
     AddrRange in_flight[32];
     int n_in_flight = 0;
     bool in_flight_overflow = false;
+    // Tensor-core GEMMs submitted back to back (nothing else put on the stream in between): what they read and write. A GEMM
+    // that touches none of it is launched as a programmatic dependent without a wait, so its first CTAs run on the SMs that
+    // the partial last wave of the GEMM before it leaves idle.
+    AddrRange tc_reads[32], tc_writes[16];
+    int n_tc_reads = 0, n_tc_writes = 0;
+    bool chain_open = false;            // the last operation this library put on the stream was a tensor-core GEMM
+    bool chain_open_at_entry = false;   // ... as of the start of the current entry point (every entry point closes the chain;
+                                        // those that put nothing else on the stream restore it)
     MemPool *pool = nullptr;
 
     void reset() {
@@ -105,6 +113,7 @@ struct DeviceState {
         for (int i = 0; i < 3; ++i) { staging[i] = nullptr; staging_bytes[i] = 0; }
         name[0] = 0; capturing = false; cta_limit = 0; h2d_stream = d2h_stream = nullptr; d2h_pending = false;
         n_in_flight = 0; in_flight_overflow = false;
+        n_tc_reads = n_tc_writes = 0; chain_open = chain_open_at_entry = false;
         ready.store(false, std::memory_order_release);
     }
 };
@@ -149,9 +158,12 @@ static int ensure_device(int device, DeviceState **out) {
         }
     }
     MAGB200_CUDA_TRY(cudaSetDevice(device));
+    d.chain_open_at_entry = d.chain_open;
+    d.chain_open = false;
     *out = &d;
     return MAGB200_OK;
 }
+static void keep_chain(DeviceState &d) { d.chain_open = d.chain_open_at_entry; }   // for entry points that put nothing on the stream before a GEMM
 
 static int ensure_scratch(DeviceState &d, size_t bytes) {
     if (bytes <= d.scratch_bytes) return MAGB200_OK;
@@ -170,7 +182,69 @@ static int ensure_scratch(DeviceState &d, size_t bytes) {
 }
 
 // ---- which results may still be in flight under programmatic dependent launch -----------------------------------------
-static void ordered_point(DeviceState &d) { d.n_in_flight = 0; d.in_flight_overflow = false; }   // a fully ordered launch or copy
+static void ordered_point(DeviceState &d) {   // a fully ordered launch or copy
+    d.n_in_flight = 0; d.in_flight_overflow = false;
+    d.n_tc_reads = d.n_tc_writes = 0; d.chain_open = false;
+}
+
+// ---- back-to-back tensor-core GEMMs that may overlap --------------------------------------------------------------------
+static std::atomic<int> g_gemm_overlap{1};
+static std::atomic<uint64_t> g_overlapped_launches{0};
+__global__ void order_kernel() {}
+static bool operand_range(const void *base, size_t es, int64_t e0, int64_t s0, int64_t e1, int64_t s1, const GemmProblem &g, const int64_t *bs,
+                          AddrRange &r) {
+    if (s0 < 0 || s1 < 0) return false;
+    int64_t reach = (e0 - 1) * s0 + (e1 - 1) * s1;
+    for (int d = 0; d < g.nbatch; ++d) {
+        if (bs[d] < 0) return false;
+        reach += (g.bshape[d] - 1) * bs[d];
+    }
+    r.lo = (uintptr_t)base;
+    r.hi = r.lo + (size_t)(reach + 1) * es;
+    return true;
+}
+static bool hits(const AddrRange *list, int n, const AddrRange &r) {
+    for (int i = 0; i < n; ++i)
+        if (r.lo < list[i].hi && list[i].lo < r.hi) return true;
+    return false;
+}
+// Decide how the next tensor-core GEMM is launched and record what it touches. True: as a programmatic dependent of the GEMM
+// before it (they may run side by side). False: an ordinary, fully ordered launch.
+static bool next_gemm_overlaps(DeviceState &d, const GemmProblem &g) {
+    const size_t es = dtype_size(g.dtype);
+    AddrRange ra, rb, rc;
+    const int64_t cb[kMaxBatchDims] = {0, 0, 0};
+    const bool known = operand_range(g.A, es, g.M, g.sAm, g.K, g.sAk, g, g.bsA, ra) && operand_range(g.B, es, g.K, g.sBk, g.N, g.sBn, g, g.bsB, rb);
+    (void)cb;
+    rc.lo = (uintptr_t)g.C;
+    rc.hi = rc.lo + (size_t)(g.batch_total * g.M * g.N) * es;
+    bool overlap = g_gemm_overlap.load() && d.chain_open && known && d.stream == d.own_stream && d.n_in_flight == 0 && !d.in_flight_overflow &&
+                   d.n_tc_reads + 2 <= 32 && d.n_tc_writes + 1 <= 16;
+    if (overlap)
+        overlap = !hits(d.tc_reads, d.n_tc_reads, rc) && !hits(d.tc_writes, d.n_tc_writes, rc) && !hits(d.tc_writes, d.n_tc_writes, ra) &&
+                  !hits(d.tc_writes, d.n_tc_writes, rb);
+    if (!overlap) ordered_point(d);               // everything submitted before is complete when this launch starts
+    if (known) {
+        d.tc_reads[d.n_tc_reads++] = ra;
+        d.tc_reads[d.n_tc_reads++] = rb;
+        d.tc_writes[d.n_tc_writes++] = rc;
+    }
+    d.chain_open = known;
+    if (overlap) g_overlapped_launches.fetch_add(1);
+    return overlap;
+}
+// A decode kernel is itself launched as a programmatic dependent: behind a run of overlapping GEMMs it could start while an
+// earlier one of them still runs. An empty, fully ordered launch in between closes the run.
+static int close_gemm_chain(DeviceState &d) {
+    if (d.chain_open || d.chain_open_at_entry) {
+        order_kernel<<<1, 32, 0, d.stream>>>();
+        MAGB200_CUDA_TRY(cudaGetLastError());
+        d.chain_open_at_entry = false;
+    }
+    d.n_tc_reads = d.n_tc_writes = 0;
+    d.chain_open = false;
+    return MAGB200_OK;
+}
 static void note_early_result(DeviceState &d, const void *ptr, size_t bytes) {
     const uintptr_t lo = (uintptr_t)ptr, hi = lo + bytes;
     for (int i = 0; i < d.n_in_flight; ++i)          // a decode loop writes the same few result buffers over and over
@@ -431,21 +505,23 @@ static int run_one(DeviceState &d, int device, const GemmProblem &g, int kernel)
         case MAGB200_KERNEL_SKINNY: {
             int rc = ensure_scratch(d, skinny_scratch_bytes(g));
             if (rc) return rc;
+            if ((rc = close_gemm_chain(d))) return rc;
             int split = 0;
             rc = launch_skinny(g, d.stream, d.scratch, d.scratch_bytes, &split, weights_settled(d, g));
             g_last_kernel = split ? MAGB200_KERNEL_SKINNY_SPLITK : MAGB200_KERNEL_SKINNY;
             note_early_result(d, g.C, (size_t)(g.batch_total * g.M * g.N) * dtype_size(g.dtype));
             return rc;
         }
-        case MAGB200_KERNEL_TCGEN05:
+        case MAGB200_KERNEL_TCGEN05: {
             g_last_kernel = MAGB200_KERNEL_TCGEN05;
-            ordered_point(d);
-            return launch_gemm_tcgen05(g, d.stream, d.cta_limit, d.status);
+            const bool overlapped = next_gemm_overlaps(d, g);
+            return launch_gemm_tcgen05(g, d.stream, d.cta_limit, d.status, nullptr, overlapped);
+        }
         case MAGB200_KERNEL_TCGEN05_2SM: {
             g_last_kernel = MAGB200_KERNEL_TCGEN05_2SM;
-            ordered_point(d);
+            const bool overlapped = next_gemm_overlaps(d, g);
             const SplitWorkspace ws = split_workspace(d);
-            return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status, nullptr, &ws);
+            return launch_gemm_tcgen05_2sm(g, d.stream, d.cta_limit, d.status, nullptr, &ws, overlapped);
         }
         case MAGB200_KERNEL_TCGEN05_F32X3: {
             // planes of both operands in the workspace; the FFMA kernel stands by behind the tensor-core launch and runs
@@ -487,6 +563,7 @@ static int run_packed(DeviceState &d, int device, const GemmProblem &g) {
     const bool pack_a = !tcgen05_operand_ok(g, true), pack_b = !tcgen05_operand_ok(g, false);
     if (!pack_a && !pack_b) return 1;
     if (d.capturing) return 1;                     // the scratch comes from the pool: not while a graph is being recorded
+    ordered_point(d);                              // the pack kernels below are ordinary launches: the GEMM behind them must wait for them
     GemmProblem gp = g;
     void *ta = nullptr, *tb = nullptr;
     int rc = MAGB200_OK;
@@ -672,6 +749,7 @@ int magb200_malloc(int device, void **out, size_t bytes) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
+    keep_chain(*d);                        // nothing goes on the launch stream here
     MemPool &p = *d->pool;
     const size_t cls = size_class(bytes ? bytes : 1);
     std::lock_guard<std::mutex> lock(p.mu);
@@ -709,6 +787,7 @@ int magb200_free(int device, void *ptr) {
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
+    keep_chain(*d);                        // nothing goes on the launch stream here
     if (!ptr) return MAGB200_OK;
     MemPool &p = *d->pool;
     std::lock_guard<std::mutex> lock(p.mu);
@@ -910,6 +989,7 @@ int magb200_matmul(int device, const magb200_view_t *x, const magb200_view_t *y,
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
+    keep_chain(*d);                        // a GEMM right behind the GEMM of the call before may run beside it
     return matmul_device(*d, device, x, y, r);
 }
 
@@ -967,6 +1047,7 @@ int magb200_matmul_grouped(int device, const magb200_view_t *x, int count, const
         settled = settled && weights_settled(*d, gs[i]);
     }
     if (one_launch) {
+        if ((rc = close_gemm_chain(*d))) return rc;
         rc = launch_skinny_grouped(gs, count, d->stream, settled);
         if (rc == MAGB200_OK) {
             g_last_kernel = MAGB200_KERNEL_SKINNY;
@@ -1113,6 +1194,11 @@ int magb200_multimem_reduce_broadcast(int device, void *cuda_stream, const void 
 int magb200_last_kernel(void) { return g_last_kernel; }
 uint64_t magb200_launch_count(void) { return g_launches.load(); }
 void magb200_launch_count_reset(void) { g_launches.store(0); }
+int magb200_set_gemm_overlap(int on) {
+    g_gemm_overlap.store(on ? 1 : 0);
+    return MAGB200_OK;
+}
+uint64_t magb200_overlapped_launch_count(void) { return g_overlapped_launches.load(); }
 int magb200_set_small_output_split(int on) {
     set_split_small(on);
     return MAGB200_OK;

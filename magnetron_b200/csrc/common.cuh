@@ -168,7 +168,10 @@ struct ScatterTarget {
     int64_t rows_per_rank;
     void *stage[8];
 };
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr);
+// `overlapped`: launch as a programmatic dependent of the kernel before it on the stream, without a wait inside -- only when the
+// caller knows that this product touches nothing that kernel (and those it may itself overlap) reads or writes
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr,
+                        bool overlapped = false);
 bool tcgen05_2sm_supported(const GemmProblem &p);
 bool tcgen05_2sm_preferred(const GemmProblem &p);
 // Workspace for the shared-out last wave of the two-SM kernel: fp32 partial tiles and per-tile counters (zero between launches).
@@ -179,7 +182,7 @@ struct SplitWorkspace {
     int max_tiles;
 };
 int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t stream, int cta_limit, int *status_word_dev, const ScatterTarget *scatter = nullptr,
-                            const SplitWorkspace *ws = nullptr);
+                            const SplitWorkspace *ws = nullptr, bool overlapped = false);
 void set_balance_tail(int enabled);
 int launch_reduce_broadcast(int dtype, const void *stage, void *const *peer_out, int ranks, int rank, int64_t block_elems, cudaStream_t stream);
 

@@ -213,6 +213,10 @@ template <int BN, int DT, bool kSplit2 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
     using C = Cfg<BN>;
+    // a GEMM launched behind this one as a programmatic dependent (the host has established that it touches nothing this one
+    // reads or writes) may take over SMs as this kernel's CTAs finish: the partial last wave of one GEMM runs beside the first
+    // wave of the next
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t krank = kSplit2 ? cluster_ctarank() : 0u;
     const int kb_half = (args.num_kb + 1) >> 1;
     const int kb_begin = kSplit2 ? (int)krank * kb_half : 0;
@@ -650,6 +654,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC, const TcArgs args) {
     static_assert(!kSwiGLU || (kTmaStore && !kShare), "the gated form leaves through the bulk-store epilogue, whole tiles only");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // see gemm_tcgen05_kernel
     constexpr int kTileN = kSwiGLU ? BN2 / 2 : BN2;      // output columns of a tile
     using C = Cfg2<KSUB>;
     extern __shared__ unsigned char smem_raw[];
@@ -1531,6 +1536,16 @@ int pick_bn(const GemmProblem &p) {
     return best;
 }
 
+// Set by launch_gemm_tcgen05 / _2sm for the launch they are about to make: launch as a programmatic dependent of the kernel
+// before it on the stream (no wait inside: the caller has checked that the two are independent).
+thread_local bool t_launch_overlapped = false;
+inline void add_overlap_attr(cudaLaunchAttribute *attr, unsigned &n) {
+    if (!t_launch_overlapped) return;
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+}
+
 // ---- run-time knobs (set through the C ABI) ---------------------------------------------------------------------------
 std::atomic<uint64_t> g_wait_limit_ns{1000ull * 1000ull * 1000ull};
 std::atomic<int> g_skip_kb_once{-1};      // consumed by the next tensor-core launch
@@ -1574,11 +1589,12 @@ int launch_cfg_split2(const GemmProblem &p, const CUtensorMap &ta, const CUtenso
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    add_overlap_attr(attr, cfg.numAttrs);
     MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
     count_launch();
     return MAGB200_OK;
@@ -1596,9 +1612,18 @@ int launch_cfg(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     args.total_tiles = args.tiles_m * args.tiles_n * p.batch_total;
     const int64_t max_ctas = cta_limit > 0 ? cta_limit : num_sms();
     const unsigned grid = (unsigned)(args.total_tiles < max_ctas ? args.total_tiles : max_ctas);
-    kernel<<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, args);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    add_overlap_attr(attr, cfg.numAttrs);
+    MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
     count_launch();
-    MAGB200_CUDA_TRY(cudaGetLastError());
     return MAGB200_OK;
 }
 
@@ -1673,11 +1698,12 @@ int launch_2sm(const GemmProblem &p, const CUtensorMap &ta, const CUtensorMap &t
     cfg.blockDim = dim3(kThreads2, 1, 1);
     cfg.dynamicSmemBytes = Cfg2<KSUB>::kSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    add_overlap_attr(attr, cfg.numAttrs);
     int rc;
     if (tb_up) rc = launch_2sm_kernel<DT, KSUB, false, true, true>(ta, tb, *tb_up, *tc, args, cfg);
     else if (args.tail_slots > 0) rc = launch_2sm_kernel<DT, KSUB, true, false>(ta, tb, tb, ta, args, cfg);
@@ -1726,7 +1752,9 @@ bool tcgen05_2sm_preferred(const GemmProblem &p) {
 }
 
 int launch_gemm_tcgen05_2sm(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter,
-                            const SplitWorkspace *ws) {
+                            const SplitWorkspace *ws, bool overlapped) {
+    struct Scope { Scope(bool v) { t_launch_overlapped = v; } ~Scope() { t_launch_overlapped = false; } } scope(overlapped && !scatter);
+    if (overlapped) ws = nullptr;             // the shared last wave uses a workspace that the kernel before this one may be using
     OperandDesc a, b;
     int amn = 0, bmn = 0;
     if (!describe(p, true, 128, a, amn) || !describe(p, false, 128, b, bmn)) {
@@ -1817,7 +1845,9 @@ int launch_gemm_swiglu(const GemmProblem &p, const void *b_up, cudaStream_t st, 
                                    : launch_2sm<MAGB200_F16, 2>(p, ta, tb, &tc, args, st, cta_limit, nullptr, &tb2);
 }
 
-int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter) {
+int launch_gemm_tcgen05(const GemmProblem &p, cudaStream_t st, int cta_limit, int *status_word_dev, const ScatterTarget *scatter,
+                        bool overlapped) {
+    struct Scope { Scope(bool v) { t_launch_overlapped = v; } ~Scope() { t_launch_overlapped = false; } } scope(overlapped && !scatter);
     // an output of at most 74 tiles of 128 x 128 with K >= 1024: pairs of CTAs split K, twice as many SMs work
     const int64_t tiles128 = ((p.M + BM - 1) / BM) * ((p.N + 127) / 128) * p.batch_total;
     const bool split2 = !scatter && cta_limit <= 0 && p.N > 64 && tiles128 * 2 <= num_sms() && p.K >= 1024 && g_split_small.load() && g_skip_kb_once.load() < 0;

@@ -70,6 +70,78 @@ def test_shared_last_wave(gpu, M, N, K, layout, dname):
         t.release()
 
 
+def test_back_to_back_gemms_overlap_only_when_independent(gpu):
+    """Consecutive magb200_matmul calls: products that share nothing but read-only operands are launched so that they may run
+    side by side (counted), and give the bits of the fully ordered launches; a product that reads the result of the one
+    before it, one that overwrites an operand of the one before it, one that writes the same result again, and a product
+    after any other operation are ordered (not counted) -- and right."""
+    dt = O.BFLOAT16
+    L = mb.lib()
+    rng = np.random.default_rng(41)
+    M, N, K = 1024, 1024, 1024
+    xb = bits(dt, rng, (M, K), 1.0)
+    wbs = [bits(dt, rng, (N, K), 0.05) for _ in range(5)]
+    tx = mb.Tensor.from_bits(gpu, dt, xb)
+    tws = [mb.Tensor.from_bits(gpu, dt, w) for w in wbs]
+    outs = [mb.Tensor(gpu, dt, (M, N)) for _ in range(5)]
+    xv = tx.view_struct()
+    wv = [w.T.view_struct() for w in tws]
+    ov = [o.view_struct() for o in outs]
+
+    def run_independent():
+        mb.synchronize(gpu)
+        before = L.magb200_overlapped_launch_count()
+        for i in range(5):
+            mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[i]), C.byref(ov[i])))
+        n = L.magb200_overlapped_launch_count() - before
+        mb.synchronize(gpu)
+        return n, [o.to_bits() for o in outs]
+
+    try:
+        mb.check(L.magb200_set_gemm_overlap(1))
+        n_on, got_on = run_independent()
+        mb.check(L.magb200_set_gemm_overlap(0))
+        n_off, got_off = run_independent()
+        assert n_on == 4 and n_off == 0
+        for a, b in zip(got_on, got_off):
+            assert np.array_equal(a, b)
+        mb.check(L.magb200_set_gemm_overlap(1))
+        # a chain of dependent products: out0 = x @ w0.T, out1 = out0 @ w1.T, out2 = out1 @ w2.T
+        mb.synchronize(gpu)
+        before = L.magb200_overlapped_launch_count()
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[0]), C.byref(ov[0])))
+        mb.check(L.magb200_matmul(gpu, C.byref(ov[0]), C.byref(wv[1]), C.byref(ov[1])))
+        mb.check(L.magb200_matmul(gpu, C.byref(ov[1]), C.byref(wv[2]), C.byref(ov[2])))
+        # overwrites an operand of the product before it (out1), then writes the same result again
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[3]), C.byref(ov[1])))
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[4]), C.byref(ov[1])))
+        assert L.magb200_overlapped_launch_count() == before
+        mb.synchronize(gpu)
+        f = lambda b: O.bits_to_f64(dt, b)
+        r0 = f(O.f32_to_bits(dt, (f(xb) @ f(wbs[0]).T).astype(np.float32)))
+        assert np.array_equal(outs[0].to_bits(), got_on[0])
+        r1 = f(outs[0].to_bits()) @ f(wbs[1]).T
+        # out2 was computed from the out1 of the chain, before out1 was overwritten
+        chain1 = O.f32_to_bits(dt, r1.astype(np.float32))
+        r2 = f(chain1) @ f(wbs[2]).T
+        got2 = f(outs[2].to_bits())
+        assert np.max(np.abs(got2 - r2)) <= 2.0 ** -7 * np.max(np.abs(r2)) + 1e-6
+        assert np.array_equal(outs[1].to_bits(), got_on[4])                       # the last writer of out1 was x @ w4.T
+        # another operation in between (a cast) closes the run: the product behind it is ordered
+        before = L.magb200_overlapped_launch_count()
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[0]), C.byref(ov[0])))
+        c = tx.cast(mb.FLOAT32)
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[2]), C.byref(ov[2])))
+        assert L.magb200_overlapped_launch_count() == before
+        mb.synchronize(gpu)
+        assert np.array_equal(outs[2].to_bits(), got_on[2])
+        c.release()
+    finally:
+        mb.check(L.magb200_set_gemm_overlap(1))
+    for t in [tx] + tws + outs:
+        t.release()
+
+
 @pytest.mark.parametrize("dname", ["bf16", "f16"])
 @pytest.mark.parametrize("batch,M,N,K", [((), 512, 2048, 2048), ((), 128, 128, 1024), ((), 300, 200, 1096), ((2, 3), 130, 136, 4160)])
 def test_small_outputs_split_k_over_cta_pairs(gpu, dname, batch, M, N, K):
