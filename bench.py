@@ -429,7 +429,8 @@ def single_op_workload(dev: Dev, cpu: CpuRef, pk):
     rotate (201 MB, more than L2); the launches are replayed from a CUDA graph so the figure is the kernel's, not the host's."""
     mb = dev.mb
     M, N, K = 512, 2048, 2048
-    out = {"shape": [M, N, K], "l2": "16 rotating operand sets (201 MB bf16 / 403 MB fp32), graph replay of 208 calls "
+    out = {"shape": [M, N, K], "l2": "16 rotating operand sets (201 MB bf16 / 403 MB fp32), graph replay of 208 calls; consecutive calls "
+           "touch different tensors, so the library lets a launch start on the SMs the one before it has left "
            "(fp32: each call clears a flag, splits both operands into bf16 planes, runs the tensor-core kernel and a stand-by FFMA launch)"}
     for key, dt, peak, bound in (("bf16", BF16, pk["tensor_burst"], "tensor"), ("fp32", mb.FLOAT32, pk["tensor_burst"] / 6.0,
                                   "tensor: six bf16 MMAs assemble one fp32 product, so the ceiling is the bf16 peak / 6")):
