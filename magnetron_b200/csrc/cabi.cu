@@ -208,30 +208,30 @@ static bool hits(const AddrRange *list, int n, const AddrRange &r) {
         if (r.lo < list[i].hi && list[i].lo < r.hi) return true;
     return false;
 }
-// Decide how the next tensor-core GEMM is launched and record what it touches. True: as a programmatic dependent of the GEMM
-// before it (they may run side by side). False: an ordinary, fully ordered launch.
-static bool next_gemm_overlaps(DeviceState &d, const GemmProblem &g) {
-    const size_t es = dtype_size(g.dtype);
-    AddrRange ra, rb, rc;
-    const int64_t cb[kMaxBatchDims] = {0, 0, 0};
-    const bool known = operand_range(g.A, es, g.M, g.sAm, g.K, g.sAk, g, g.bsA, ra) && operand_range(g.B, es, g.K, g.sBk, g.N, g.sBn, g, g.bsB, rb);
-    (void)cb;
-    rc.lo = (uintptr_t)g.C;
-    rc.hi = rc.lo + (size_t)(g.batch_total * g.M * g.N) * es;
+// Decide how the next kernel of a run (a tensor-core GEMM or a contiguous cast: both let their successor start early) is
+// launched, and record what it touches. True: as a programmatic dependent of the kernel before it (they may run side by
+// side). False: an ordinary, fully ordered launch. `known`: the ranges below describe everything the kernel touches.
+static bool next_kernel_overlaps(DeviceState &d, const AddrRange *reads, int n_reads, const AddrRange &write, bool known) {
     bool overlap = g_gemm_overlap.load() && d.chain_open && known && d.stream == d.own_stream && d.n_in_flight == 0 && !d.in_flight_overflow &&
-                   d.n_tc_reads + 2 <= 32 && d.n_tc_writes + 1 <= 16;
-    if (overlap)
-        overlap = !hits(d.tc_reads, d.n_tc_reads, rc) && !hits(d.tc_writes, d.n_tc_writes, rc) && !hits(d.tc_writes, d.n_tc_writes, ra) &&
-                  !hits(d.tc_writes, d.n_tc_writes, rb);
+                   d.n_tc_reads + n_reads <= 32 && d.n_tc_writes + 1 <= 16;
+    if (overlap) overlap = !hits(d.tc_reads, d.n_tc_reads, write) && !hits(d.tc_writes, d.n_tc_writes, write);
+    for (int i = 0; overlap && i < n_reads; ++i) overlap = !hits(d.tc_writes, d.n_tc_writes, reads[i]);
     if (!overlap) ordered_point(d);               // everything submitted before is complete when this launch starts
     if (known) {
-        d.tc_reads[d.n_tc_reads++] = ra;
-        d.tc_reads[d.n_tc_reads++] = rb;
-        d.tc_writes[d.n_tc_writes++] = rc;
+        for (int i = 0; i < n_reads; ++i) d.tc_reads[d.n_tc_reads++] = reads[i];
+        d.tc_writes[d.n_tc_writes++] = write;
     }
     d.chain_open = known;
     if (overlap) g_overlapped_launches.fetch_add(1);
     return overlap;
+}
+static bool next_gemm_overlaps(DeviceState &d, const GemmProblem &g) {
+    const size_t es = dtype_size(g.dtype);
+    AddrRange r[2], rc;
+    const bool known = operand_range(g.A, es, g.M, g.sAm, g.K, g.sAk, g, g.bsA, r[0]) && operand_range(g.B, es, g.K, g.sBk, g.N, g.sBn, g, g.bsB, r[1]);
+    rc.lo = (uintptr_t)g.C;
+    rc.hi = rc.lo + (size_t)(g.batch_total * g.M * g.N) * es;
+    return next_kernel_overlaps(d, r, 2, rc, known);
 }
 // A decode kernel is itself launched as a programmatic dependent: behind a run of overlapping GEMMs it could start while an
 // earlier one of them still runs. An empty, fully ordered launch in between closes the run.
@@ -622,8 +622,13 @@ static int cast_device(DeviceState &d, const magb200_view_t *src, const magb200_
     if (n != view_numel(dst)) { set_error("cast: element counts differ (%lld vs %lld)", (long long)n, (long long)view_numel(dst)); return MAGB200_ERR_SHAPE; }
     if (!view_is_contiguous(dst)) { set_error("cast: result must be contiguous"); return MAGB200_ERR_INVALID_ARG; }
     CollapsedDims cd = collapse_dims(src->rank, src->shape, src->strides);
-    ordered_point(d);
-    return launch_cast(src->dtype, dst->dtype, view_data(src), view_data(dst), n, cd, view_is_contiguous(src), d.stream);
+    // a contiguous cast behind a GEMM or a cast that touches none of its tensors may start on the SMs that kernel has left
+    const bool contig = view_is_contiguous(src);
+    AddrRange rs, rd;
+    rs.lo = (uintptr_t)view_data(src); rs.hi = rs.lo + (size_t)n * dtype_size(src->dtype);
+    rd.lo = (uintptr_t)view_data(dst); rd.hi = rd.lo + (size_t)n * dtype_size(dst->dtype);
+    const bool overlapped = next_kernel_overlaps(d, &rs, 1, rd, contig && n > 0);
+    return launch_cast(src->dtype, dst->dtype, view_data(src), view_data(dst), n, cd, contig, d.stream, overlapped);
 }
 
 static int ensure_staging(DeviceState &d, int slot, size_t bytes) {
@@ -925,6 +930,7 @@ int magb200_cast(int device, const magb200_view_t *src, const magb200_view_t *ds
     DeviceState *d;
     int rc = ensure_device(device, &d);
     if (rc) return rc;
+    keep_chain(*d);
     return cast_device(*d, src, dst, false);
 }
 int magb200_clone(int device, const magb200_view_t *src, const magb200_view_t *dst) {

@@ -58,6 +58,7 @@ template <int D> __device__ __forceinline__ void store8(void *dst, int64_t i, co
 // Contiguous source and destination, both 16-byte aligned. n8 = number of full 8-element groups.
 template <int S, int D>
 __global__ void __launch_bounds__(kThreads) cast_contig_kernel(const void *__restrict__ src, void *__restrict__ dst, int64_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // an independent kernel behind this one may start as SMs come free
     const int64_t n8 = n / kVec;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     // kUnroll groups per thread and step, all loads issued before the first store: a 16-bit source brings only 16 bytes per
@@ -98,6 +99,7 @@ __global__ void __launch_bounds__(kThreads) cast_contig_kernel(const void *__res
 // flight per thread. This direction writes two bytes for every byte it reads and is bound by the write stream.
 template <int S>
 __global__ void __launch_bounds__(kThreads) cast_widen_kernel(const void *__restrict__ src, void *__restrict__ dst, int64_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int kU = 8;
     const int64_t n4 = n / 4;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -341,13 +343,25 @@ int grid_for_unrolled(int64_t groups, int unroll) {
 }
 
 template <int S, int D>
-int launch_pair(const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t stream) {
+int launch_pair(const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t stream, bool overlapped) {
     const bool aligned = (((uintptr_t)src | (uintptr_t)dst) & 15u) == 0;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlapped ? 1 : 0;      // the caller has checked that this cast touches nothing the kernels before it use
     if (contig && aligned && D == MAGB200_F32 && S != MAGB200_F32) {
-        if constexpr (D == MAGB200_F32 && S != MAGB200_F32)
-            cast_widen_kernel<S><<<grid_for_unrolled((n + 3) / 4, 8), kThreads, 0, stream>>>(src, dst, n);
+        if constexpr (D == MAGB200_F32 && S != MAGB200_F32) {
+            cfg.gridDim = dim3((unsigned)grid_for_unrolled((n + 3) / 4, 8), 1, 1);
+            MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, cast_widen_kernel<S>, src, dst, n));
+        }
     } else if (contig && aligned) {
-        cast_contig_kernel<S, D><<<grid_for_unrolled((n + kVec - 1) / kVec, 4), kThreads, 0, stream>>>(src, dst, n);
+        cfg.gridDim = dim3((unsigned)grid_for_unrolled((n + kVec - 1) / kVec, 4), 1, 1);
+        MAGB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, cast_contig_kernel<S, D>, (const void *)src, dst, n));
     } else {
         CollapsedDims d = dims;
         if (contig) { d.rank = 1; d.shape[0] = n; d.strides[0] = 1; }
@@ -360,9 +374,9 @@ int launch_pair(const void *src, void *dst, int64_t n, const CollapsedDims &dims
 
 }  // namespace
 
-int launch_cast(int s, int d, const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t st) {
+int launch_cast(int s, int d, const void *src, void *dst, int64_t n, const CollapsedDims &dims, bool contig, cudaStream_t st, bool overlapped) {
     if (n <= 0) return MAGB200_OK;
-#define PAIR(SS, DD) if (s == SS && d == DD) return launch_pair<SS, DD>(src, dst, n, dims, contig, st);
+#define PAIR(SS, DD) if (s == SS && d == DD) return launch_pair<SS, DD>(src, dst, n, dims, contig, st, overlapped);
     PAIR(MAGB200_F32, MAGB200_F32) PAIR(MAGB200_F32, MAGB200_F16) PAIR(MAGB200_F32, MAGB200_BF16)
     PAIR(MAGB200_F16, MAGB200_F32) PAIR(MAGB200_F16, MAGB200_F16) PAIR(MAGB200_F16, MAGB200_BF16)
     PAIR(MAGB200_BF16, MAGB200_F32) PAIR(MAGB200_BF16, MAGB200_F16) PAIR(MAGB200_BF16, MAGB200_BF16)

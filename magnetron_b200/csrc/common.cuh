@@ -190,7 +190,7 @@ int launch_multimem_reduce_broadcast(int dtype, const void *mc_partial, void *mc
                                      cudaStream_t stream);
 
 int launch_cast(int src_dt, int dst_dt, const void *src, void *dst, int64_t n,
-                const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream);
+                const CollapsedDims &src_dims, bool src_contig, cudaStream_t stream, bool overlapped = false);
 int launch_fill(int dt, void *dst, int64_t n, double value, cudaStream_t stream);
 // device-side repack of a 16-bit operand that TMA cannot describe (see cast.cu)
 bool tcgen05_operand_ok(const GemmProblem &p, bool is_a);

@@ -127,15 +127,29 @@ def test_back_to_back_gemms_overlap_only_when_independent(gpu):
         got2 = f(outs[2].to_bits())
         assert np.max(np.abs(got2 - r2)) <= 2.0 ** -7 * np.max(np.abs(r2)) + 1e-6
         assert np.array_equal(outs[1].to_bits(), got_on[4])                       # the last writer of out1 was x @ w4.T
-        # another operation in between (a cast) closes the run: the product behind it is ordered
+        # another operation in between (a fill of an unrelated tensor) closes the run: the product behind it is ordered
         before = L.magb200_overlapped_launch_count()
+        other = mb.Tensor(gpu, dt, (64,))
         mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[0]), C.byref(ov[0])))
-        c = tx.cast(mb.FLOAT32)
+        mb.check(L.magb200_fill(gpu, C.byref(other.view_struct()), C.c_double(1.0)))
         mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[2]), C.byref(ov[2])))
         assert L.magb200_overlapped_launch_count() == before
         mb.synchronize(gpu)
         assert np.array_equal(outs[2].to_bits(), got_on[2])
-        c.release()
+        # a contiguous cast of an uninvolved tensor behind a product joins the run; a cast of that product's result does not
+        before = L.magb200_overlapped_launch_count()
+        f32 = mb.Tensor(gpu, mb.FLOAT32, (M, K))
+        f32b = mb.Tensor(gpu, mb.FLOAT32, (M, N))
+        mb.check(L.magb200_matmul(gpu, C.byref(xv), C.byref(wv[0]), C.byref(ov[0])))
+        mb.check(L.magb200_cast(gpu, C.byref(xv), C.byref(f32.view_struct())))
+        assert L.magb200_overlapped_launch_count() == before + 1
+        mb.check(L.magb200_cast(gpu, C.byref(ov[0]), C.byref(f32b.view_struct())))
+        assert L.magb200_overlapped_launch_count() == before + 1
+        mb.synchronize(gpu)
+        assert np.array_equal(f32.to_bits(), O.cast_bits(dt, O.FLOAT32, xb))
+        assert np.array_equal(f32b.to_bits(), O.cast_bits(dt, O.FLOAT32, got_on[0]))
+        for t in (other, f32, f32b):
+            t.release()
     finally:
         mb.check(L.magb200_set_gemm_overlap(1))
     for t in [tx] + tws + outs:
