@@ -213,6 +213,15 @@ uint64_t magb200_overlapped_launch_count(void);
  * SMs work (default on; 0 keeps one CTA per tile: tests compare the two). */
 int  magb200_set_small_output_split(int on);
 
+/* What the library would do with the decode-shaped product x @ y (M <= 8 after folding), decided on the host from shapes,
+ * strides and alignment alone; nothing is launched and no device is needed (the data pointers must be the real ones only as
+ * far as their alignment goes). kind: 0 not taken by the decode kernels, 1 small projection (register loads; `warps_along_k`
+ * warps of a CTA and `cluster` CTAs split K), 2 streaming with a ring per lane, 3 streaming with row-contiguous copies,
+ * 4 N-major weights through mma.sync, 5 FFMA kernels (float32). `k_splits` > 1: K is cut into chunks of `k_chunk` across CTAs
+ * and a second kernel sums the partial results; `ctas`: grid size along the tile dimension. */
+int  magb200_decode_plan(const magb200_view_t *x, const magb200_view_t *y, int *kind, int *k_splits, int *ctas, int *warps_along_k,
+                         int *cluster, int64_t *k_chunk);
+
 /* Decode-shaped products with plenty of weight rows (lm_head, the projections of a large model) stream their weights with
  * copies of 512 contiguous bytes of one row per warp instruction (default); 0 selects the older kernel in which every lane
  * keeps to its own two rows (64 bytes from each of 8 rows per instruction). Same arithmetic, another order of the fp32 sums. */

@@ -1209,6 +1209,23 @@ int magb200_set_small_output_split(int on) {
     set_split_small(on);
     return MAGB200_OK;
 }
+int magb200_decode_plan(const magb200_view_t *x, const magb200_view_t *y, int *kind, int *k_splits, int *ctas, int *warps_along_k, int *cluster,
+                        int64_t *k_chunk) {
+    if (!x || !y || !kind || !k_splits || !ctas || !warps_along_k || !cluster || !k_chunk) { set_error("decode_plan: null argument"); return MAGB200_ERR_INVALID_ARG; }
+    int32_t rank = 0;
+    int64_t shape[MAGB200_MAX_DIMS + 2];
+    int rc = magb200_matmul_result_shape(x, y, &rank, shape);
+    if (rc) return rc;
+    magb200_view_t r;
+    memset(&r, 0, sizeof(r));
+    alignas(16) static char unused[16];
+    r.base = unused; r.dtype = x->dtype; r.rank = rank;
+    int64_t acc = 1;
+    for (int i = rank - 1; i >= 0; --i) { r.shape[i] = shape[i]; r.strides[i] = acc; acc *= shape[i]; }
+    FullProblem fp;
+    if ((rc = build_problem(x, y, &r, fp))) return rc;
+    return describe_skinny_plan(fp.g, kind, k_splits, ctas, warps_along_k, cluster, k_chunk);
+}
 int magb200_set_decode_row_streaming(int on) {
     set_decode_row_streaming(on);
     return MAGB200_OK;

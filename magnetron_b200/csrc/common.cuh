@@ -159,6 +159,7 @@ bool skinny_supported(const GemmProblem &p);
 int launch_skinny(const GemmProblem &p, cudaStream_t stream, float *splitk_scratch, size_t scratch_bytes, int *used_splitk, bool weights_settled);
 void set_split_small(int on);   // one-CTA tensor-core kernel: CTA pairs split K when the output has at most 74 tiles of 128 x 128
 void set_decode_row_streaming(int on);   // streaming decode kernel: row-contiguous copies (default) or the per-lane ring
+int describe_skinny_plan(const GemmProblem &p, int *kind, int *nsplit, int *gridx, int *warps_along_k, int *cluster, int64_t *kch);
 void set_decode_cluster_max(int max_cluster);   // 1, 2 or 4 CTAs per cluster for decode matrices with few row tiles (default 4)
 int launch_skinny_grouped(const GemmProblem *ps, int count, cudaStream_t stream, bool weights_settled);   // 1: not applicable
 bool tcgen05_supported(const GemmProblem &p);

@@ -1329,6 +1329,28 @@ int launch_skinny_grouped(const GemmProblem *ps, int count, cudaStream_t st, boo
                                     : launch_grouped_dt<MAGB200_F16>(ps, count, st, weights_settled);
 }
 
+// What the planner would do with a decode-shaped product, without launching anything (host logic only: tests pin the decisions).
+// kind: 0 not a decode-shaped product the kernels take, 1 small projections (register loads), 2 per-lane-ring streaming,
+// 3 row-contiguous streaming, 4 N-major mma.sync, 5 FFMA kernels.
+int describe_skinny_plan(const GemmProblem &p, int *kind, int *nsplit, int *gridx, int *warps_along_k, int *cluster, int64_t *kch) {
+    Plan pl;
+    bool ok = false;
+    if (p.M >= 1 && p.M <= 8) {
+        switch (p.dtype) {
+            case MAGB200_F32:  ok = make_plan<MAGB200_F32>(p, pl); break;
+            case MAGB200_F16:  ok = make_plan<MAGB200_F16>(p, pl); break;
+            case MAGB200_BF16: ok = make_plan<MAGB200_BF16>(p, pl); break;
+        }
+    }
+    *kind = !ok ? 0 : pl.nm_mma ? 4 : (pl.mma && pl.async) ? (pl.rows ? 3 : 2) : pl.mma ? 1 : 5;
+    *nsplit = ok ? pl.nsplit : 0;
+    *gridx = ok ? (int)pl.gridx : 0;
+    *warps_along_k = ok && pl.mma && !pl.async ? pl.KW : 0;
+    *cluster = ok && pl.mma && !pl.async ? pl.CL : 0;
+    *kch = ok ? pl.kch : 0;
+    return MAGB200_OK;
+}
+
 bool skinny_supported(const GemmProblem &p) {
     if (p.M < 1 || p.M > 8) return false;
     Plan pl;

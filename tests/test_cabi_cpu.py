@@ -154,3 +154,66 @@ def test_status_mapping_of_the_backend_module(tmp_path):
     got = dict(zip(rcs, (int(v) for v in res.stdout.split())))
     assert got == {rc: code[n] for rc, n in want.items()}
     assert len(set(got.values())) == len(got)          # no two causes share a status
+
+
+def _fake_view(dtype, shape, strides, base=0x7F0000000000):
+    v = mb.View()
+    v.base, v.offset, v.dtype, v.rank = base, 0, dtype, len(shape)
+    for i, (n, st) in enumerate(zip(shape, strides)):
+        v.shape[i], v.strides[i] = n, st
+    return v
+
+
+def _decode_plan(dtype, M, N, K, layout="W.T", batch=()):
+    """magb200_decode_plan for x[batch..., M, K] @ y, y = W.T view of a [N, K] weight or a contiguous [K, N] weight."""
+    L = mb.lib()
+    xs = batch + (M, K)
+    x = _fake_view(dtype, xs, mb.contiguous_strides(xs))
+    y = _fake_view(dtype, (K, N), (1, K) if layout == "W.T" else (N, 1), base=0x7F1000000000)
+    out = [C.c_int() for _ in range(5)]
+    kch = C.c_int64()
+    mb.check(L.magb200_decode_plan(C.byref(x), C.byref(y), *[C.byref(o) for o in out], C.byref(kch)))
+    kind, splits, ctas, kw, cl = (o.value for o in out)
+    return {"kind": kind, "splits": splits, "ctas": ctas, "kw": kw, "cluster": cl, "kch": kch.value}
+
+
+def test_decode_planner_decisions():
+    """The host-side planner of the decode kernels, without a device (148 SMs assumed): which kernel a shape gets, how K is cut."""
+    BF, F32 = mb.BFLOAT16, mb.FLOAT32
+    SMALL, RING, ROWS, NMAJOR, FFMA = 1, 2, 3, 4, 5
+    # Qwen3-0.6B projections: register-load kernel, 8 warps along K; the 1024-row o / down add clusters of 2 / 4 CTAs
+    q = _decode_plan(BF, 1, 2048, 1024)
+    assert (q["kind"], q["kw"], q["cluster"], q["splits"]) == (SMALL, 8, 1, 1)
+    o = _decode_plan(BF, 1, 1024, 2048)
+    assert (o["kind"], o["kw"], o["cluster"], o["ctas"]) == (SMALL, 8, 2, 128)
+    down = _decode_plan(BF, 8, 1024, 3072)
+    assert (down["kind"], down["kw"], down["cluster"], down["ctas"]) == (SMALL, 8, 4, 256)
+    # 384 row tiles (gate + up of the 0.6B model as one group has this count): 4 warps along K keep the launch within one wave
+    g = _decode_plan(BF, 1, 6144, 1024)
+    assert (g["kind"], g["kw"]) == (SMALL, 4) and g["ctas"] * (8 // g["kw"]) >= 384
+    # lm_head and the wide projections of larger models: row-contiguous streaming, one CTA per SM, no K split
+    lm = _decode_plan(BF, 1, 151936, 1024)
+    assert (lm["kind"], lm["splits"], lm["ctas"]) == (ROWS, 1, 148)
+    assert _decode_plan(BF, 8, 25600, 5120)["kind"] in (ROWS, RING)
+    assert _decode_plan(BF, 1, 25600, 5120)["kind"] == ROWS
+    # few row tiles and a long K: K split across CTAs on the per-lane-ring kernel (twice the warps balance better)
+    sq = _decode_plan(BF, 1, 5120, 5120)
+    assert sq["kind"] == RING and sq["splits"] > 1 and sq["kch"] % 256 == 0
+    # contiguous [K, N] weights: mma.sync with transposing fragment loads; float32 stays on the FFMA kernels
+    kn = _decode_plan(BF, 8, 151936, 1024, layout="KN")
+    assert (kn["kind"], kn["splits"]) == (NMAJOR, 1)
+    kn2 = _decode_plan(BF, 4, 12288, 4096, layout="KN")
+    assert kn2["kind"] == NMAJOR and kn2["splits"] > 1 and 96 * kn2["splits"] <= 148 * 16
+    assert _decode_plan(F32, 2, 4096, 4096)["kind"] == FFMA
+    assert _decode_plan(F32, 2, 4096, 4096, layout="KN")["kind"] == FFMA
+    # not decode-shaped (M > 8 after folding) or a layout the kernels do not take (weights with neither stride 1)
+    assert _decode_plan(BF, 16, 4096, 4096)["kind"] == 0
+    x = _fake_view(BF, (1, 64), (64, 1))
+    y = _fake_view(BF, (64, 32), (2, 128), base=0x7F1000000000)
+    out = [C.c_int() for _ in range(5)]
+    kch = C.c_int64()
+    mb.check(mb.lib().magb200_decode_plan(C.byref(x), C.byref(y), *[C.byref(o) for o in out], C.byref(kch)))
+    assert out[0].value == 0
+    # a batch of decode products folds into M only while it stays at or below 8 rows
+    assert _decode_plan(BF, 2, 2048, 1024, batch=(4,))["kind"] == SMALL
+    assert _decode_plan(BF, 4, 2048, 1024, batch=(4,))["kind"] == 0
