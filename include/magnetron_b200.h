@@ -213,6 +213,11 @@ uint64_t magb200_overlapped_launch_count(void);
  * SMs work (default on; 0 keeps one CTA per tile: tests compare the two). */
 int  magb200_set_small_output_split(int on);
 
+/* Which kernel x @ y would be routed to (magb200_kernel_t), decided on the host from dtype, shapes, strides and alignment
+ * alone; nothing is launched and no device is needed. `repacked` = 1: a 16-bit operand that TMA cannot describe (row pitch not
+ * a multiple of 16 bytes, inner stride 2, misaligned slice) would first be copied into a legal layout on the device. */
+int  magb200_matmul_route(const magb200_view_t *x, const magb200_view_t *y, int *kernel, int *repacked);
+
 /* What the library would do with the decode-shaped product x @ y (M <= 8 after folding), decided on the host from shapes,
  * strides and alignment alone; nothing is launched and no device is needed (the data pointers must be the real ones only as
  * far as their alignment goes). kind: 0 not taken by the decode kernels, 1 small projection (register loads; `warps_along_k`

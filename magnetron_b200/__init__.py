@@ -88,6 +88,7 @@ SIGNATURES = {
     "magb200_cat": (C.c_int, [C.c_int, C.POINTER(_VP), C.c_int, C.c_int, _VP]),
     "magb200_matmul": (C.c_int, [C.c_int, _VP, _VP, _VP]),
     "magb200_upload_2d": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "magb200_matmul_route": (C.c_int, [_VP, _VP, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "magb200_decode_plan": (C.c_int, [_VP, _VP] + [C.POINTER(C.c_int)] * 5 + [C.POINTER(C.c_int64)]),
     "magb200_set_decode_cluster": (C.c_int, [C.c_int]),
     "magb200_set_gemm_overlap": (C.c_int, [C.c_int]),

@@ -1209,6 +1209,37 @@ int magb200_set_small_output_split(int on) {
     set_split_small(on);
     return MAGB200_OK;
 }
+int magb200_matmul_route(const magb200_view_t *x, const magb200_view_t *y, int *kernel, int *repacked) {
+    if (!x || !y || !kernel || !repacked) { set_error("matmul_route: null argument"); return MAGB200_ERR_INVALID_ARG; }
+    int32_t rank = 0;
+    int64_t shape[MAGB200_MAX_DIMS + 2];
+    int rc = magb200_matmul_result_shape(x, y, &rank, shape);
+    if (rc) return rc;
+    magb200_view_t r;
+    memset(&r, 0, sizeof(r));
+    alignas(16) static char unused[16];
+    r.base = unused; r.dtype = x->dtype; r.rank = rank;
+    int64_t acc = 1;
+    for (int i = rank - 1; i >= 0; --i) { r.shape[i] = shape[i]; r.strides[i] = acc; acc *= shape[i]; }
+    FullProblem fp;
+    if ((rc = build_problem(x, y, &r, fp))) return rc;
+    if ((rc = route(fp.g, 0, kernel))) return rc;
+    *repacked = 0;
+    const GemmProblem &g = fp.g;
+    // the detour of run_packed: a 16-bit product that fell to the FFMA kernel only because TMA cannot describe an operand
+    if (*kernel == MAGB200_KERNEL_SIMT && g.dtype != MAGB200_F32 && g.M > 8 &&
+        (double)g.M * (double)g.N * (double)g.K * (double)g.batch_total >= (double)(1 << 24) &&
+        (!tcgen05_operand_ok(g, true) || !tcgen05_operand_ok(g, false))) {
+        *repacked = 1;
+        GemmProblem gp = g;
+        const int64_t kpad = (g.K + 7) / 8 * 8;
+        if (!tcgen05_operand_ok(g, true)) { gp.sAm = kpad; gp.sAk = 1; gp.A = unused; }
+        if (!tcgen05_operand_ok(g, false)) { gp.sBn = kpad; gp.sBk = 1; gp.B = unused; }
+        *kernel = tcgen05_2sm_preferred(gp) ? MAGB200_KERNEL_TCGEN05_2SM : MAGB200_KERNEL_TCGEN05;
+    }
+    return MAGB200_OK;
+}
+
 int magb200_decode_plan(const magb200_view_t *x, const magb200_view_t *y, int *kind, int *k_splits, int *ctas, int *warps_along_k, int *cluster,
                         int64_t *k_chunk) {
     if (!x || !y || !kind || !k_splits || !ctas || !warps_along_k || !cluster || !k_chunk) { set_error("decode_plan: null argument"); return MAGB200_ERR_INVALID_ARG; }

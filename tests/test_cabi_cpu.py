@@ -217,3 +217,40 @@ def test_decode_planner_decisions():
     # a batch of decode products folds into M only while it stays at or below 8 rows
     assert _decode_plan(BF, 2, 2048, 1024, batch=(4,))["kind"] == SMALL
     assert _decode_plan(BF, 4, 2048, 1024, batch=(4,))["kind"] == 0
+
+
+def _route(dtype, xshape, xstrides, yshape, ystrides, xbase=0x7F0000000000, ybase=0x7F1000000000):
+    x, y = _fake_view(dtype, xshape, xstrides, xbase), _fake_view(dtype, yshape, ystrides, ybase)
+    k, rp = C.c_int(), C.c_int()
+    mb.check(mb.lib().magb200_matmul_route(C.byref(x), C.byref(y), C.byref(k), C.byref(rp)))
+    return mb.KERNEL_NAMES[k.value], rp.value
+
+
+def test_matmul_routing_without_a_device():
+    """Which kernel the configurations of the workload go to, decided on the host."""
+    BF, F16, F32 = mb.BFLOAT16, mb.FLOAT16, mb.FLOAT32
+    lin = lambda dt, M, N, K: _route(dt, (M, K), (K, 1), (K, N), (1, K))          # x @ W.T
+    # prefill layer of the 8B model: q / o / gate / up / down on CTA pairs, k / v (64 tiles of 256 x 256) on the one-CTA kernel
+    assert lin(BF, 4096, 4096, 4096) == ("tcgen05_2sm", 0)
+    assert lin(BF, 4096, 12288, 4096) == ("tcgen05_2sm", 0)
+    assert lin(BF, 4096, 1024, 4096) == ("tcgen05", 0)
+    # the single-op workload: bf16 on the one-CTA kernel, fp32 on the split-operand tensor-core kernel, small fp32 on the FFMA kernel
+    assert lin(BF, 512, 2048, 2048) == ("tcgen05", 0)
+    assert lin(F32, 512, 2048, 2048) == ("tcgen05_f32x3", 0)
+    assert lin(F32, 96, 80, 200) == ("simt", 0)
+    assert lin(F32, 4096, 4096, 32) == ("simt", 0)                              # K below one 64-wide block
+    # decode shapes
+    assert lin(BF, 1, 151936, 1024) == ("skinny", 0)
+    assert lin(F32, 8, 4096, 4096) == ("skinny", 0)
+    assert lin(BF, 9, 4096, 4096)[0] == "tcgen05"
+    # attention: scores [B,KV,G,T,D] @ [B,KV,1,D,T] with a broadcast dim, fp16
+    B, KV, G, T, D = 8, 8, 4, 2048, 128
+    q = (B, KV, G, T, D)
+    kt = (B, KV, 1, D, T)
+    assert _route(F16, q, mb.contiguous_strides(q), kt, (KV * T * D, T * D, 0, 1, D)) == ("tcgen05_2sm", 0)
+    # operands TMA cannot describe: odd K (row pitch not a multiple of 16 bytes) is repacked on the device, then tensor cores
+    assert lin(BF, 4096, 4096, 4095) == ("tcgen05_2sm", 1)
+    assert _route(BF, (512, 1024), (2048, 2), (1024, 512), (1, 1024)) == ("tcgen05", 1)      # inner stride 2
+    assert _route(BF, (512, 1024), (1024, 1), (1024, 512), (1, 1024), xbase=0x7F0000000002) == ("tcgen05", 1)   # misaligned slice
+    assert lin(BF, 16, 24, 40) == ("tcgen05", 0)
+    assert _route(BF, (16, 40), (80, 2), (40, 24), (1, 40)) == ("simt", 0)        # too small to be worth a repack
